@@ -1,0 +1,272 @@
+// Row-wise kernels of the decoder: embedding gather, residual add fused with
+// RMSNorm (and with the reduction of split-K partial sums), rotary embedding
+// fused with the write of keys and values into cache pages, and the gated
+// activation.  Sums, norms and angles are computed in 32-bit floats whatever the
+// storage type.
+//
+// Reference counterparts (cuda/src/kernels.cu): embed_gather_kernel :1198,
+// rmsnorm_kernel :1152 with residual_add_kernel :649, rope_qk_kernel :1244 with the
+// page writes of crates/allpaca-core/src/kv_tier.rs:1101-1203, silu_mul_kernel :775.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// embedding gather: x[t, :] = table[token[t], :]   (32-bit residual stream)
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_gather_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                                    float* __restrict__ x, int H, int V) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    // The host rejects tokens outside the vocabulary; the clamp keeps a corrupted
+    // id from reading outside the table.
+    tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+    const TW* src = table + (size_t)tok * H;
+    float* dst = x + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ap_to_float(src[i]);
+}
+
+AP_EXPORT int ap_embed_gather(const int* tokens, const void* table, int table_dtype, float* x,
+                              int T, int H, int V, cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && H > 0 && V > 0, "embed_gather: bad sizes T=%d H=%d V=%d", T, H, V);
+    if (T == 0) return AP_OK;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == AP_F32)
+        embed_gather_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, x, H, V);
+    else if (table_dtype == AP_BF16)
+        embed_gather_kernel<bf16><<<T, threads, 0, stream>>>(tokens, (const bf16*)table, x, H, V);
+    else
+        AP_REQUIRE(false, "embed_gather: unknown table dtype %d", table_dtype);
+    AP_CHECK_LAUNCH("embed_gather");
+    return AP_OK;
+}
+
+// ---------------------------------------------------------------------------
+// add + RMSNorm:  v = x[row] + sum_s delta[s, row];  out = v * rsqrt(mean(v^2) + eps) * w
+//   rows == nullptr: every row t < T, and x[t] is overwritten with v.
+//   rows != nullptr: only the listed rows are normed into out[r]; x is left as it is.
+// One block per row, the row kept in shared memory between the two passes.
+// ---------------------------------------------------------------------------
+#define NORM_THREADS 256
+
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(NORM_THREADS)
+add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int S, size_t delta_stride,
+                   const TW* __restrict__ w, float eps, TO* __restrict__ out,
+                   const int* __restrict__ rows, int H) {
+    extern __shared__ float row_buf[];
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int t = rows ? rows[r] : r;
+    float* xr = x + (size_t)t * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += NORM_THREADS) {
+        float v = xr[i];
+        for (int s = 0; s < S; ++s) v += delta[(size_t)s * delta_stride + (size_t)t * H + i];
+        row_buf[i] = v;
+        ss = fmaf(v, v, ss);
+        if (!rows && S > 0) xr[i] = v;
+    }
+    ss = ap_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += NORM_THREADS)
+        o[i] = ap_from_float<TO>(row_buf[i] * inv * ap_to_float(w[i]));
+}
+
+template <typename TW, typename TO>
+static int launch_add_rmsnorm(float* x, const float* delta, int S, size_t delta_stride, const void* w,
+                              float eps, void* out, const int* rows, int R, int H, cudaStream_t stream) {
+    const size_t smem = (size_t)H * sizeof(float);
+    auto kern = add_rmsnorm_kernel<TW, TO>;
+    if (smem > 48 * 1024) {
+        AP_REQUIRE(smem <= 200 * 1024, "rmsnorm: width %d does not fit the shared-memory row buffer", H);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        AP_REQUIRE(e == cudaSuccess, "rmsnorm: cannot reserve %zu bytes of shared memory", smem);
+    }
+    kern<<<R, NORM_THREADS, smem, stream>>>(x, delta, S, delta_stride, (const TW*)w, eps, (TO*)out, rows, H);
+    AP_CHECK_LAUNCH("add_rmsnorm");
+    return AP_OK;
+}
+
+AP_EXPORT int ap_add_rmsnorm(float* x, const float* delta, int S, long long delta_stride,
+                             const void* weight, int w_dtype, float eps, void* out, int out_dtype,
+                             const int* rows, int R, int H, cudaStream_t stream) {
+    AP_REQUIRE(R >= 0 && H > 0 && S >= 0, "rmsnorm: bad sizes R=%d H=%d S=%d", R, H, S);
+    AP_REQUIRE(S == 0 || delta != nullptr, "rmsnorm: S=%d partial sums but no buffer", S);
+    if (R == 0) return AP_OK;
+    if (w_dtype == AP_F32 && out_dtype == AP_F32)
+        return launch_add_rmsnorm<float, float>(x, delta, S, delta_stride, weight, eps, out, rows, R, H, stream);
+    if (w_dtype == AP_BF16 && out_dtype == AP_BF16)
+        return launch_add_rmsnorm<bf16, bf16>(x, delta, S, delta_stride, weight, eps, out, rows, R, H, stream);
+    if (w_dtype == AP_F32 && out_dtype == AP_BF16)
+        return launch_add_rmsnorm<float, bf16>(x, delta, S, delta_stride, weight, eps, out, rows, R, H, stream);
+    if (w_dtype == AP_BF16 && out_dtype == AP_F32)
+        return launch_add_rmsnorm<bf16, float>(x, delta, S, delta_stride, weight, eps, out, rows, R, H, stream);
+    AP_REQUIRE(false, "rmsnorm: unknown dtypes w=%d out=%d", w_dtype, out_dtype);
+}
+
+// ---------------------------------------------------------------------------
+// residual add alone: x[t] += sum_s delta[s, t]   (used where no norm follows)
+// ---------------------------------------------------------------------------
+__global__ void residual_add_kernel(float* __restrict__ x, const float* __restrict__ delta, int S,
+                                    size_t delta_stride, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = x[i];
+        for (int s = 0; s < S; ++s) v += delta[(size_t)s * delta_stride + i];
+        x[i] = v;
+    }
+}
+
+AP_EXPORT int ap_residual_add(float* x, const float* delta, int S, long long delta_stride,
+                              long long n, cudaStream_t stream) {
+    AP_REQUIRE(n >= 0 && S >= 0, "residual_add: bad sizes");
+    if (n == 0 || S == 0) return AP_OK;
+    const int threads = 256;
+    long long blocks = (n + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    residual_add_kernel<<<(int)blocks, threads, 0, stream>>>(x, delta, S, (size_t)delta_stride, (size_t)n);
+    AP_CHECK_LAUNCH("residual_add");
+    return AP_OK;
+}
+
+// ---------------------------------------------------------------------------
+// rotary embedding of Q and K + write of K and V into cache pages.
+//   in:  [S, T, (nh + 2*nkv) * hd]  (S partial sums in 32-bit, or S == 1 in TI)
+//   q_out: [T, nh*hd]
+//   cache (one layer): [page][2][nkv][P][hd]; the page of a row is
+//       block_table[token_seq[t]][pos / P], its slot pos % P; cache == nullptr: store nothing
+//   inv_freq: [hd/2] 32-bit table, or nullptr for no rotation
+//   pairing 0: pairs (i, i + hd/2)   (checkpoints in the Hugging Face layout)
+//   pairing 1: pairs (2i, 2i + 1)    (checkpoints whose Q/K rows were permuted)
+// ---------------------------------------------------------------------------
+template <typename TI>
+__device__ __forceinline__ float load_partial(const TI* in, int S, size_t stride, size_t idx) {
+    float v = ap_to_float(in[idx]);
+    for (int s = 1; s < S; ++s) v += ap_to_float(in[(size_t)s * stride + idx]);
+    return v;
+}
+
+template <typename TI, typename TO>
+__global__ void rope_kv_store_kernel(const TI* __restrict__ in, int S, size_t in_stride,
+                                     TO* __restrict__ q_out, TO* __restrict__ cache,
+                                     const int* __restrict__ positions,
+                                     const int* __restrict__ token_seq,
+                                     const int* __restrict__ block_table, int max_blocks,
+                                     const float* __restrict__ inv_freq, int pairing,
+                                     int nh, int nkv, int hd, int P, size_t page_stride) {
+    const int t = blockIdx.x;
+    const int half = hd >> 1;
+    const int width = (nh + 2 * nkv) * hd;
+    const size_t row = (size_t)t * width;
+    const int ipos = positions[t];
+    const float pos = (float)ipos;
+    int page = -1, off = 0;
+    if (cache) {
+        page = block_table[(size_t)token_seq[t] * max_blocks + ipos / P];
+        off = ipos % P;
+    }
+    const int slot = page;   // < 0: this row stores nothing
+    const int rot_pairs = (nh + nkv) * half;
+    for (int p = threadIdx.x; p < rot_pairs; p += blockDim.x) {
+        const int head = p / half, i = p - head * half;
+        const int ia = pairing == 0 ? i : 2 * i;
+        const int ib = pairing == 0 ? i + half : 2 * i + 1;
+        const size_t base = row + (size_t)head * hd;
+        // partial sums are rounded to the storage type once they are complete
+        float a = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + ia)));
+        float b = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + ib)));
+        float ra = a, rb = b;
+        if (inv_freq) {
+            float sn, cs;
+            sincosf(pos * inv_freq[i], &sn, &cs);
+            ra = a * cs - b * sn;
+            rb = a * sn + b * cs;
+        }
+        if (head < nh) {
+            TO* q = q_out + (size_t)t * nh * hd + (size_t)head * hd;
+            q[ia] = ap_from_float<TO>(ra);
+            q[ib] = ap_from_float<TO>(rb);
+        } else if (slot >= 0) {
+            const int kh = head - nh;
+            TO* k = cache + (size_t)page * page_stride + ((size_t)kh * P + off) * hd;
+            k[ia] = ap_from_float<TO>(ra);
+            k[ib] = ap_from_float<TO>(rb);
+        }
+    }
+    if (slot >= 0) {
+        const int nv = nkv * hd;
+        const size_t vbase = row + (size_t)(nh + nkv) * hd;
+        for (int e = threadIdx.x; e < nv; e += blockDim.x) {
+            const int kh = e / hd, d = e - kh * hd;
+            const float v = load_partial(in, S, in_stride, vbase + e);
+            cache[(size_t)page * page_stride + (size_t)nkv * P * hd + ((size_t)kh * P + off) * hd + d] =
+                ap_from_float<TO>(v);
+        }
+    }
+}
+
+AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in_stride, void* q_out,
+                               void* cache, int act_dtype, const int* positions, const int* token_seq,
+                               const int* block_table, int max_blocks, const float* inv_freq, int pairing, int T, int nh, int nkv, int hd, int P,
+                               long long page_stride, cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && nh > 0 && nkv >= 0 && hd > 0 && (hd % 2) == 0 && S >= 1,
+               "rope_kv_store: bad sizes T=%d heads=%d kv_heads=%d head_dim=%d S=%d", T, nh, nkv, hd, S);
+    AP_REQUIRE(pairing == 0 || pairing == 1, "rope_kv_store: unknown pairing %d", pairing);
+    AP_REQUIRE(cache == nullptr || (P > 0 && page_stride >= 2LL * nkv * P * hd),
+               "rope_kv_store: page stride %lld is below one page of keys and values", page_stride);
+    AP_REQUIRE(cache == nullptr || (token_seq && block_table && max_blocks > 0),
+               "rope_kv_store: storing needs the block table and the rows' sequences");
+    if (T == 0) return AP_OK;
+    const int threads = 128;
+#define LAUNCH(TI, TO)                                                                              \
+    rope_kv_store_kernel<TI, TO><<<T, threads, 0, stream>>>(                                        \
+        (const TI*)in, S, (size_t)in_stride, (TO*)q_out, (TO*)cache, positions, token_seq,         \
+        block_table, max_blocks, inv_freq,                                                          \
+        pairing, nh, nkv, hd, P, (size_t)page_stride)
+    if (in_dtype == AP_F32 && act_dtype == AP_F32) LAUNCH(float, float);
+    else if (in_dtype == AP_F32 && act_dtype == AP_BF16) LAUNCH(float, bf16);
+    else if (in_dtype == AP_BF16 && act_dtype == AP_BF16) {
+        AP_REQUIRE(S == 1, "rope_kv_store: partial sums must be 32-bit");
+        LAUNCH(bf16, bf16);
+    } else AP_REQUIRE(false, "rope_kv_store: unsupported dtypes in=%d act=%d", in_dtype, act_dtype);
+#undef LAUNCH
+    AP_CHECK_LAUNCH("rope_kv_store");
+    return AP_OK;
+}
+
+// ---------------------------------------------------------------------------
+// gated activation: out[t, j] = silu(g) * u,  g = in[t, j], u = in[t, I + j]
+// ---------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void swiglu_kernel(const TI* __restrict__ in, int S, size_t in_stride, TO* __restrict__ out,
+                              int T, int I) {
+    const size_t n = (size_t)T * I;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / I, j = e - t * I;
+        const size_t base = t * 2 * (size_t)I;
+        const float g = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + j)));
+        const float u = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + I + j)));
+        const float a = g / (1.0f + expf(-g));
+        out[e] = ap_from_float<TO>(a * u);
+    }
+}
+
+AP_EXPORT int ap_swiglu(const void* in, int in_dtype, int S, long long in_stride, void* out, int out_dtype,
+                        int T, int I, cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && I > 0 && S >= 1, "swiglu: bad sizes T=%d I=%d S=%d", T, I, S);
+    if (T == 0) return AP_OK;
+    const int threads = 256;
+    long long blocks = ((long long)T * I + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+#define LAUNCH(TI, TO) \
+    swiglu_kernel<TI, TO><<<(int)blocks, threads, 0, stream>>>((const TI*)in, S, (size_t)in_stride, (TO*)out, T, I)
+    if (in_dtype == AP_F32 && out_dtype == AP_F32) LAUNCH(float, float);
+    else if (in_dtype == AP_F32 && out_dtype == AP_BF16) LAUNCH(float, bf16);
+    else if (in_dtype == AP_BF16 && out_dtype == AP_BF16) {
+        AP_REQUIRE(S == 1, "swiglu: partial sums must be 32-bit");
+        LAUNCH(bf16, bf16);
+    } else AP_REQUIRE(false, "swiglu: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+#undef LAUNCH
+    AP_CHECK_LAUNCH("swiglu");
+    return AP_OK;
+}

@@ -1,0 +1,17 @@
+from .batch import BatchEntry, StepBatch
+from .scheduler import (AdmissionError, FinishReason, Request, RequestStatus, ScheduledRows,
+                        Scheduler, SchedulerOutput)
+
+__all__ = ["BatchEntry", "StepBatch", "AdmissionError", "FinishReason", "Request",
+           "RequestStatus", "ScheduledRows", "Scheduler", "SchedulerOutput", "ModelRunner",
+           "StepError", "LLM", "RequestOutput"]
+
+
+def __getattr__(name):
+    if name in ("ModelRunner", "StepError"):
+        from . import runner
+        return getattr(runner, name)
+    if name in ("LLM", "RequestOutput"):
+        from . import llm
+        return getattr(llm, name)
+    raise AttributeError(name)

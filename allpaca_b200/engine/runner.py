@@ -1,0 +1,233 @@
+"""The step function: run one batch of (request, its next tokens) through the model.
+
+``ModelRunner`` owns the model, the cache manager with its device storage, and the
+staging buffers.  ``step(entries)`` takes portions of prompts beside single decoded
+tokens, cut anywhere, runs only those rows against what earlier steps left in the
+cache, and returns 32-bit logits for the rows asked for.  ``finish(request)`` gives a
+request's pages and state slot back.  Generation and trace replay both go through it.
+
+Role in the reference: ``forward_batch`` over ``SeqRows``
+(crates/allpaca-core/src/model.rs:8839-8885) with page growth by ``ensure_pages``
+(model.rs:13452-13480) and release on drop (crates/allpaca-core/src/engine.rs:409-432).
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, GroupLayout, GroupStorage, OutOfPages, StateStorage, FREED
+from ..config import EngineConfig
+from ..models import DecoderModel, load_config
+from ..parts import BuildEnv, Workspace
+from ..weights import load_checkpoint
+from .batch import BatchEntry, StepBatch
+
+
+class StepError(ValueError):
+    """A batch the step function cannot run (caller's mistake); nothing was changed."""
+
+
+class ModelRunner:
+    def __init__(self, model_path: Optional[str], engine: EngineConfig, model: Optional[DecoderModel] = None,
+                 model_config=None):
+        """Load the model folder at ``model_path`` (or take a ready ``model`` whose weights
+        are loaded) and set up caches for it."""
+        engine.validate()
+        self.engine = engine
+        if not torch.cuda.is_available():
+            raise RuntimeError("allpaca_b200 needs a CUDA device (sm_100a); none is visible")
+        self.device = torch.device(engine.device)
+        torch.cuda.set_device(self.device)
+        self.workspace = Workspace(self.device)
+        self.env = BuildEnv(dtype=engine.dtype, device=self.device, workspace=self.workspace,
+                            page_size=engine.page_size, max_seqs=engine.max_num_seqs)
+        if model is None:
+            arch, cfg = load_config(model_path)
+            model = DecoderModel(arch.spec_builder(cfg), self.env)
+            load_checkpoint(model, model_path, engine.dtype, self.device)
+            model_config = cfg
+        self.model = model
+        self.model_config = model_config
+        self.vocab_size = model.spec.vocab_size
+        self.max_model_len = engine.max_model_len or model.spec.max_position_embeddings
+        self._setup_caches()
+        self._staging_cap = 0
+        self._host = None
+        self._dev = None
+
+    # ---- caches ---------------------------------------------------------
+    def _setup_caches(self) -> None:
+        e = self.engine
+        self.cache_plan = self.model.cache_plan()
+        elt = torch.empty((), dtype=e.dtype).element_size()
+        page_bytes = [len(g.runs) * 2 * g.need.num_kv_heads * e.page_size * g.need.head_dim * elt
+                      for g in self.cache_plan]
+        if e.num_pages is not None:
+            num_pages = e.num_pages
+        elif e.max_cache_tokens is not None:
+            num_pages = -(-e.max_cache_tokens // e.page_size)
+        else:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            budget = int(free * e.gpu_memory_fraction)
+            num_pages = max(1, budget // max(1, sum(page_bytes)))
+            # no more than every sequence slot at full length needs
+            num_pages = min(num_pages, e.max_num_seqs * -(-self.max_model_len // e.page_size))
+        self.num_pages = int(num_pages)
+        layouts = [GroupLayout(e.page_size, self.num_pages, g.need.window) for g in self.cache_plan]
+        self.cache = CacheManager(layouts, e.max_num_seqs)
+        self.storages = [GroupStorage(len(g.runs), self.num_pages, g.need.num_kv_heads, e.page_size,
+                                      g.need.head_dim, e.dtype, self.device) for g in self.cache_plan]
+        self.states = [StateStorage(e.max_num_seqs, b, self.device) if b > 0 else None
+                       for b in self.model.state_bytes()]
+        self.model.bind_caches(self.cache_plan, self.storages, self.states)
+
+    # ---- requests -------------------------------------------------------
+    def has(self, request: Hashable) -> bool:
+        return self.cache.has(request)
+
+    def finish(self, request: Hashable) -> None:
+        """Give back what the request holds (pages of every group, its state slot)."""
+        self.cache.free(request)
+
+    def can_run(self, entries: Sequence[BatchEntry]) -> bool:
+        """Whether the pools can supply the pages this batch needs."""
+        reserve = [0] * len(self.cache.groups)
+        new = 0
+        for en in entries:
+            req = en.request if self.cache.has(en.request) else None
+            if req is None:
+                new += 1
+            miss = self.cache.pages_missing(req, len(en.tokens))
+            for g, m in enumerate(miss):
+                reserve[g] += m
+        if new > self.engine.max_num_seqs - self.cache.num_running():
+            return False
+        return all(reserve[g] <= self.cache.num_free_pages(g) for g in range(len(reserve)))
+
+    # ---- the step -------------------------------------------------------
+    def step(self, entries: Sequence[BatchEntry]) -> torch.Tensor:
+        """Run the rows of ``entries`` as one batch; returns ``[wanted, vocab]`` float32 logits
+        in the order of the entries and of their ``want`` lists.  The tensor is a view of a
+        buffer that the next step overwrites."""
+        batch = self.prepare(entries)
+        logits = self.model.forward(batch)
+        for en in entries:
+            self.cache.release_passed(en.request)
+        return logits
+
+    def prepare(self, entries: Sequence[BatchEntry]) -> StepBatch:
+        """Check the batch, allocate its pages and upload its metadata."""
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        T = 0
+        for en in entries:
+            if en.request in seen:
+                raise StepError(f"request {en.request!r} appears twice in one step")
+            seen.add(en.request)
+            n = len(en.tokens)
+            if n == 0:
+                raise StepError(f"request {en.request!r} brings no tokens")
+            arr = np.asarray(en.tokens, dtype=np.int64)
+            if arr.min() < 0 or arr.max() >= self.vocab_size:
+                # crates/allpaca-core/src/model.rs:8215-8219
+                bad = int(arr[(arr < 0) | (arr >= self.vocab_size)][0])
+                raise StepError(f"token {bad} out of vocab {self.vocab_size}")
+            for w in en.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"request {en.request!r} wants row {w} of {n}")
+            held = self.cache.num_tokens(en.request) if self.cache.has(en.request) else 0
+            if held + n > self.max_model_len:
+                raise StepError(f"request {en.request!r} would hold {held + n} tokens, "
+                                f"the model takes {self.max_model_len}")
+            T += n
+        if T > self.engine.max_num_batched_tokens:
+            raise StepError(f"{T} rows exceed max_num_batched_tokens {self.engine.max_num_batched_tokens}")
+        if not self.can_run(entries):
+            raise OutOfPages("the cache pools cannot hold this step's tokens")
+
+        nseq = len(entries)
+        firsts: List[int] = []
+        for en in entries:
+            if not self.cache.has(en.request):
+                self.cache.begin(en.request)
+            firsts.append(self.cache.append(en.request, len(en.tokens)))
+
+        groups = range(len(self.cache.groups))
+        widths = [max(len(self.cache.block_table(en.request, g)) for en in entries) for g in groups]
+        R = sum(len(en.want) for en in entries)
+        total = 3 * T + (nseq + 1) + 2 * nseq + R + sum(nseq * w for w in widths)
+        host, dev = self._staging(total)
+        o = 0
+
+        def region(n):
+            nonlocal o
+            a, b = o, o + n
+            o = b
+            return a, b
+
+        r_tok, r_pos, r_seq = region(T), region(T), region(T)
+        r_start, r_ctx, r_slot, r_rows = region(nseq + 1), region(nseq), region(nseq), region(R)
+        r_tables = [region(nseq * w) for w in widths]
+
+        row = 0
+        out_row = 0
+        max_q = max_ctx = 0
+        starts = [0]
+        for s, en in enumerate(entries):
+            n = len(en.tokens)
+            host[r_tok[0] + row:r_tok[0] + row + n] = np.asarray(en.tokens, dtype=np.int32)
+            host[r_pos[0] + row:r_pos[0] + row + n] = np.arange(firsts[s], firsts[s] + n, dtype=np.int32)
+            host[r_seq[0] + row:r_seq[0] + row + n] = s
+            for w in en.want:
+                host[r_rows[0] + out_row] = row + int(w)
+                out_row += 1
+            host[r_ctx[0] + s] = firsts[s] + n
+            host[r_slot[0] + s] = self.cache.state_slot(en.request)
+            for g in groups:
+                table = self.cache.block_table(en.request, g)
+                base = r_tables[g][0] + s * widths[g]
+                host[base:base + len(table)] = np.asarray(table, dtype=np.int32)
+                host[base + len(table):base + widths[g]] = FREED
+            row += n
+            starts.append(row)
+            max_q = max(max_q, n)
+            max_ctx = max(max_ctx, firsts[s] + n)
+        host[r_start[0]:r_start[1]] = np.asarray(starts, dtype=np.int32)
+
+        dev[:total].copy_(self._host_tensor[:total], non_blocking=True)
+        self._copied.record()
+
+        def view(r):
+            return dev[r[0]:r[1]]
+
+        return StepBatch(
+            num_tokens=T, num_seqs=nseq, num_logit_rows=R,
+            token_ids=view(r_tok), positions=view(r_pos), token_seq=view(r_seq),
+            seq_start=view(r_start), context_lens=view(r_ctx), state_slots=view(r_slot),
+            logit_rows=view(r_rows),
+            block_tables=[view(r_tables[g]).view(nseq, widths[g]) for g in groups],
+            host_seq_start=starts, host_first_position=firsts,
+            host_state_slots=[self.cache.state_slot(en.request) for en in entries],
+            max_query_len=max_q, max_context_len=max_ctx)
+
+    def _staging(self, n: int):
+        if n > self._staging_cap:
+            # a step's metadata is read by kernels still in flight: wait before replacing it
+            torch.cuda.current_stream().synchronize()
+            cap = max(n, 2 * self._staging_cap, 4096)
+            self._host_tensor = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            self._host = self._host_tensor.numpy()
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self._staging_cap = cap
+            self._copied = torch.cuda.Event()
+        else:
+            # the previous step's copy out of the pinned buffer must have finished
+            self._copied.synchronize()
+        return self._host, self._dev
+
+    def memory_report(self) -> Dict[str, int]:
+        return {"cache_bytes": sum(s.bytes() for s in self.storages),
+                "workspace_bytes": self.workspace.bytes(), "num_pages": self.num_pages}

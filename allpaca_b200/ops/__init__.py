@@ -1,0 +1,248 @@
+"""Python faces of the CUDA kernels: argument checks, then one C call each.
+
+Every function works on CUDA tensors in place or into a given output; none has
+a CPU branch.  Partial sums: a matrix product that was split along K hands its
+consumer a 32-bit tensor ``[S, T, N]``; consumers add the S slices in order.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import library
+from .library import KernelError, call, core, stream_handle
+
+AP_F32, AP_BF16 = 0, 1
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return AP_F32
+    if dt == torch.bfloat16:
+        return AP_BF16
+    raise KernelError(f"dtype {dt} is not one the kernels take (float32, bfloat16)")
+
+
+def _check(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, is {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dimensions, has shape {tuple(t.shape)}")
+
+
+def _partials(t: torch.Tensor, name: str):
+    """(pointer, dtype code, S, stride between slices, T, N) of ``[S,T,N]`` or ``[T,N]``."""
+    _check(t, name)
+    if t.dim() == 3:
+        if t.dtype != torch.float32:
+            raise KernelError(f"{name}: partial sums must be float32")
+        return t.data_ptr(), AP_F32, t.shape[0], t.shape[1] * t.shape[2], t.shape[1], t.shape[2]
+    if t.dim() == 2:
+        return t.data_ptr(), dtype_code(t.dtype), 1, t.numel(), t.shape[0], t.shape[1]
+    raise KernelError(f"{name} must be [T,N] or [S,T,N], has shape {tuple(t.shape)}")
+
+
+def embed_gather(tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor) -> None:
+    """``x[t] = table[tokens[t]]`` into the 32-bit residual stream ``x [T,H]``."""
+    _check(tokens, "tokens", torch.int32, 1)
+    _check(table, "table", dims=2)
+    _check(x, "x", torch.float32, 2)
+    T, H = x.shape
+    if tokens.shape[0] != T or table.shape[1] != H:
+        raise KernelError(f"embed_gather: shapes disagree: tokens {tuple(tokens.shape)}, "
+                          f"table {tuple(table.shape)}, x {tuple(x.shape)}")
+    call(core(), "ap_embed_gather", tokens.data_ptr(), table.data_ptr(), dtype_code(table.dtype),
+         x.data_ptr(), T, H, table.shape[0], stream_handle())
+
+
+def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """``v = x + sum(delta); out = rmsnorm(v) * weight``.
+
+    Without ``rows`` every row is normed and ``x`` is overwritten with ``v``.  With
+    ``rows`` (int32 indices) only those rows are normed into ``out[r]`` and ``x`` stays.
+    """
+    _check(x, "x", torch.float32, 2)
+    _check(weight, "weight", dims=1)
+    _check(out, "out", dims=2)
+    T, H = x.shape
+    if weight.shape[0] != H or out.shape[1] != H:
+        raise KernelError("add_rmsnorm: widths disagree")
+    S, dptr, dstride = 0, 0, 0
+    if delta is not None:
+        dptr, code, S, dstride, dT, dN = _partials(delta, "delta")
+        if code != AP_F32 or dT != T or dN != H:
+            raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} {delta.dtype} does not match x {tuple(x.shape)}")
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+        R = rows.shape[0]
+    else:
+        R = T
+    if out.shape[0] < R:
+        raise KernelError("add_rmsnorm: out has too few rows")
+    call(core(), "ap_add_rmsnorm", x.data_ptr(), dptr, S, dstride, weight.data_ptr(),
+         dtype_code(weight.dtype), float(eps), out.data_ptr(), dtype_code(out.dtype),
+         rows.data_ptr() if rows is not None else 0, R, H, stream_handle())
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+    """``x += sum(delta)`` in 32-bit."""
+    _check(x, "x", torch.float32, 2)
+    dptr, code, S, dstride, dT, dN = _partials(delta, "delta")
+    if code != AP_F32 or (dT, dN) != tuple(x.shape):
+        raise KernelError("residual_add: delta does not match x")
+    call(core(), "ap_residual_add", x.data_ptr(), dptr, S, dstride, x.numel(), stream_handle())
+
+
+def rope_kv_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[torch.Tensor],
+                  positions: torch.Tensor, token_seq: Optional[torch.Tensor],
+                  block_table: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                  pairing: int, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """Rotate Q and K of ``qkv [T, (nh+2nkv)*hd]`` and store K, V into cache pages.
+
+    ``cache_layer`` is one layer's pages ``[pages, 2, nkv, P, hd]``; a row's page is
+    ``block_table[token_seq[t], pos // P]`` and its slot ``pos % P``.  ``inv_freq`` None: no
+    rotation.  With ``cache_layer`` None nothing is stored; with ``num_kv_heads`` 0 the input
+    holds queries only.
+    """
+    ptr, code, S, stride, T, N = _partials(qkv, "qkv")
+    if N != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError(f"rope_kv_store: qkv width {N} is not (heads + 2 kv_heads) * head_dim")
+    _check(q_out, "q_out", dims=2)
+    if q_out.shape[0] < T or q_out.shape[1] != num_heads * head_dim:
+        raise KernelError("rope_kv_store: q_out shape does not match")
+    _check(positions, "positions", torch.int32, 1)
+    P, page_stride, cptr, tsptr, btptr, maxb = 1, 0, 0, 0, 0, 0
+    if cache_layer is not None:
+        _check(cache_layer, "cache_layer", q_out.dtype, 5)
+        _, two, nkv, P, hd = cache_layer.shape
+        if two != 2 or nkv != num_kv_heads or hd != head_dim:
+            raise KernelError(f"rope_kv_store: cache layer {tuple(cache_layer.shape)} does not match the heads")
+        page_stride = cache_layer.stride(0)
+        cptr = cache_layer.data_ptr()
+        if token_seq is None or block_table is None:
+            raise KernelError("rope_kv_store: storing needs token_seq and block_table")
+        _check(token_seq, "token_seq", torch.int32, 1)
+        _check(block_table, "block_table", torch.int32, 2)
+        tsptr, btptr, maxb = token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1]
+    if inv_freq is not None:
+        _check(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] != head_dim // 2:
+            raise KernelError("rope_kv_store: inv_freq must have head_dim/2 entries")
+    call(core(), "ap_rope_kv_store", ptr, code, S, stride, q_out.data_ptr(), cptr,
+         dtype_code(q_out.dtype), positions.data_ptr(), tsptr, btptr, maxb,
+         inv_freq.data_ptr() if inv_freq is not None else 0, int(pairing), T, num_heads,
+         num_kv_heads, head_dim, P, page_stride, stream_handle())
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]``."""
+    ptr, code, S, stride, T, N = _partials(gate_up, "gate_up")
+    _check(out, "out", dims=2)
+    if N != 2 * out.shape[1] or out.shape[0] != T:
+        raise KernelError("swiglu: out must be [T, I] for gate_up [T, 2I]")
+    call(core(), "ap_swiglu", ptr, code, S, stride, out.data_ptr(), dtype_code(out.dtype), T,
+         out.shape[1], stream_handle())
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[M,N] = a[M,K] @ w[N,K]^T`` on the CUDA cores with 32-bit accumulation."""
+    _check(a, "a", dims=2)
+    _check(w, "w", dims=2)
+    _check(out, "out", dims=2)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    call(core(), "ap_gemm_simt", a.data_ptr(), dtype_code(a.dtype), w.data_ptr(), dtype_code(w.dtype),
+         out.data_ptr(),
+         dtype_code(out.dtype), M, N, K, K, K, N, stream_handle())
+
+
+def tensor_core_gemm_available() -> bool:
+    return hasattr(core(), "ap_gemm_tc")
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1) -> None:
+    """bfloat16 ``a[M,K] @ w[N,K]^T`` on the tcgen05 tensor cores.
+
+    ``out`` is ``[M,N]`` (bfloat16 or float32) for ``nsplit == 1`` and float32
+    ``[nsplit, M, N]`` partial sums otherwise.
+    """
+    _check(a, "a", torch.bfloat16, 2)
+    _check(w, "w", torch.bfloat16, 2)
+    _check(out, "out")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError("gemm_tc: inner sizes disagree")
+    if nsplit == 1:
+        if tuple(out.shape) != (M, N):
+            raise KernelError("gemm_tc: out must be [M,N]")
+        stride = 0
+    else:
+        if tuple(out.shape) != (nsplit, M, N) or out.dtype != torch.float32:
+            raise KernelError("gemm_tc: partial sums must be float32 [nsplit,M,N]")
+        stride = M * N
+    call(core(), "ap_gemm_tc", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+         M, N, K, K, K, N, nsplit, stride, stream_handle())
+
+
+def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
+              block_table: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
+              num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+              window: int = 0) -> None:
+    """Causal attention of every row of ``q [T, nh*hd]`` over its sequence's cached keys."""
+    _check(q, "q", dims=2)
+    _check(out, "out", q.dtype, 2)
+    _check(cache_layer, "cache_layer", q.dtype, 5)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(token_seq, "token_seq", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    T = token_seq.shape[0]
+    if q.shape[0] < T or q.shape[1] != num_heads * head_dim or out.shape != q.shape:
+        raise KernelError("attention: q/out shape does not match the heads")
+    _, two, nkv, P, hd = cache_layer.shape
+    if two != 2 or nkv != num_kv_heads or hd != head_dim:
+        raise KernelError("attention: cache layer does not match the heads")
+    lib = library.attention(head_dim)
+    call(lib, "ap_attention_rows", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
+         dtype_code(q.dtype), block_table.data_ptr(), block_table.shape[1], token_seq.data_ptr(),
+         positions.data_ptr(), T, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0),
+         float(scale), int(window or 0), stream_handle())
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """First maximum of every row of 32-bit ``logits [R,V]`` into int32 ``out [R]``."""
+    _check(logits, "logits", torch.float32, 2)
+    _check(out, "out", torch.int32, 1)
+    R, V = logits.shape
+    call(core(), "ap_argmax", logits.data_ptr(), V, R, V, out.data_ptr(), stream_handle())
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:
+    """One token per row: greedy where temperature <= 1e-5, else temperature/top-k/top-p."""
+    _check(logits, "logits", torch.float32, 2)
+    R, V = logits.shape
+    for t, n, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
+                     (top_p, "top_p", torch.float32), (uniform, "uniform", torch.float32),
+                     (out, "out", torch.int32)):
+        _check(t, n, dt, 1)
+        if t.shape[0] < R:
+            raise KernelError(f"sample: {n} has fewer than {R} entries")
+    call(core(), "ap_sample", logits.data_ptr(), V, R, V, temperature.data_ptr(), top_k.data_ptr(),
+         top_p.data_ptr(), uniform.data_ptr(), out.data_ptr(), stream_handle())
+
+
+def gemm_tc_splits(M: int, N: int, K: int) -> int:
+    """How many K-slices the tensor-core kernel wants for this shape (1: no split)."""
+    lib = core()
+    if not hasattr(lib, "ap_gemm_tc_plan"):
+        return 1
+    return max(1, int(lib.ap_gemm_tc_plan(int(M), int(N), int(K))))

@@ -1,0 +1,115 @@
+"""Loads the CUDA kernel libraries and exposes their C entry points.
+
+The libraries are plain shared objects with `extern "C"` functions that take
+device pointers, sizes and a stream; they are called through ctypes with the
+pointers of torch tensors.  There is no CPU implementation behind these calls:
+if nvcc or a CUDA device is missing the load fails with a clear error.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_void_p, c_int, c_float, c_longlong, c_char_p
+from typing import Dict
+
+from ..csrc import build as _build
+
+
+class KernelError(RuntimeError):
+    """A kernel entry point refused its arguments or could not be launched."""
+
+
+_P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
+
+_CORE_SIGNATURES = {
+    "ap_embed_gather": [_P, _P, _I, _P, _I, _I, _I, _P],
+    "ap_add_rmsnorm": [_P, _P, _I, _L, _P, _I, _F, _P, _I, _P, _I, _I, _P],
+    "ap_residual_add": [_P, _P, _I, _L, _L, _P],
+    "ap_rope_kv_store": [_P, _I, _I, _L, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _L, _P],
+    "ap_swiglu": [_P, _I, _I, _L, _P, _I, _I, _I, _P],
+    "ap_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _L, _L, _L, _P],
+    "ap_argmax": [_P, _L, _I, _I, _P, _P],
+    "ap_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
+}
+_OPTIONAL_CORE_SIGNATURES = {
+    # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, stream)
+    "ap_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _L, _P],
+    "ap_gemm_tc_plan": [_I, _I, _I],
+}
+_ATTN_SIGNATURES = {
+    "ap_attention_rows": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P],
+}
+
+_lock = threading.Lock()
+_core = None
+_attn: Dict[int, ctypes.CDLL] = {}
+
+
+def _declare(lib: ctypes.CDLL, signatures, optional=False) -> None:
+    for name, args in signatures.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            if optional:
+                continue
+            raise
+        fn.argtypes = args
+        fn.restype = c_int
+    lib.ap_last_error.restype = c_char_p
+    lib.ap_last_error.argtypes = []
+
+
+def _require_cuda() -> None:
+    import torch
+    if not torch.cuda.is_available():
+        raise KernelError(
+            "no CUDA device is visible: allpaca_b200 runs only on a GPU (sm_100a); "
+            "there is no CPU implementation of its kernels")
+
+
+def core() -> ctypes.CDLL:
+    """The library of size-independent kernels, built on first use."""
+    global _core
+    if _core is None:
+        with _lock:
+            if _core is None:
+                path = _build.build_core()
+                lib = ctypes.CDLL(path)
+                _declare(lib, _CORE_SIGNATURES)
+                _declare(lib, _OPTIONAL_CORE_SIGNATURES, optional=True)
+                _core = lib
+    return _core
+
+
+def attention(head_dim: int) -> ctypes.CDLL:
+    """The attention library specialised for one head size, built on first use."""
+    lib = _attn.get(head_dim)
+    if lib is None:
+        with _lock:
+            lib = _attn.get(head_dim)
+            if lib is None:
+                path = _build.build_attention(head_dim)
+                lib = ctypes.CDLL(path)
+                _declare(lib, _ATTN_SIGNATURES)
+                for name, args in _OPTIONAL_ATTN_SIGNATURES.items():
+                    if hasattr(lib, name):
+                        getattr(lib, name).argtypes = args
+                        getattr(lib, name).restype = c_int
+                _attn[head_dim] = lib
+    return lib
+
+
+_OPTIONAL_ATTN_SIGNATURES: Dict[str, list] = {}
+
+
+def call(lib: ctypes.CDLL, name: str, *args) -> None:
+    """Call an entry point and raise with the library's own message on failure."""
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        msg = lib.ap_last_error()
+        raise KernelError(f"{name} failed (status {rc}): {msg.decode() if msg else 'no message'}")
+
+
+def stream_handle() -> int:
+    import torch
+    return torch.cuda.current_stream().cuda_stream

@@ -1,0 +1,104 @@
+"""Grouped-query causal attention over a paged cache.
+
+Steps, as the reference computes them (crates/allpaca-core/src/model.rs:8528-8667):
+``q = Wq h``, ``k = Wk h``, ``v = Wv h`` without bias (:8528-8560); Q and K (not V) of every
+head are rotated at the token's absolute position (:8573-8604); K and V go into the
+page ``pos / P`` at slot ``pos % P`` (:8606-8614); query head ``h`` reads KV head
+``h / (heads/kv_heads)``, scores are ``(q.k) / sqrt(head_dim)`` over the keys at or before the
+row's position (crates/allpaca-cpu/src/kernels.rs:318-336), soft-maxed and applied to the
+values (:338-352); then ``Wo`` (model.rs:8667).  The three projections are one matrix
+product here: their weights are stacked ``[Wq; Wk; Wv]`` at load.
+
+A ``window`` keeps only the last ``window`` keys visible, and lets the cache manager take
+back pages the window has passed.  ``shares_kv`` makes the layer read keys and values that
+another run of the order wrote: it then has no K/V weights.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from .. import ops
+from .base import (BuildEnv, KVNeed, LayerCache, Mixer, PartSpec, WeightSpec, build, register)
+from .linear import Linear
+
+
+@register("mixer", "gqa_attention")
+class GroupedQueryAttention(Mixer):
+    """Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``,
+    ``position`` (a :class:`PartSpec` of kind ``position`` or None), ``window`` (None or
+    tokens), ``scale`` (None: ``1/sqrt(head_dim)``), ``shares_kv`` (False)."""
+
+    def __init__(self, params, env: BuildEnv):
+        super().__init__(params, env)
+        self.require("hidden_size", "num_heads", "num_kv_heads", "head_dim")
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.nh = int(p["num_heads"])
+        self.nkv = int(p["num_kv_heads"])
+        self.hd = int(p["head_dim"])
+        if self.nh % self.nkv:
+            raise ValueError(f"{self.nh} heads are not a multiple of {self.nkv} KV heads")
+        self.window = p.get("window") or None
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
+        self.shares_kv = bool(p.get("shares_kv", False))
+        pos = p.get("position")
+        self.position = build("position", pos, env) if pos is not None else None
+        self.q_size = self.nh * self.hd
+        self.kv_size = 0 if self.shares_kv else self.nkv * self.hd
+        self.qkv = Linear(env, self.q_size + 2 * self.kv_size, self.hidden)
+        self.o = Linear(env, self.hidden, self.q_size)
+
+    # ---- weights --------------------------------------------------------
+    def weights(self) -> Dict[str, WeightSpec]:
+        w = {"q_proj.weight": WeightSpec((self.q_size, self.hidden)),
+             "o_proj.weight": WeightSpec((self.hidden, self.q_size))}
+        if not self.shares_kv:
+            w["k_proj.weight"] = WeightSpec((self.kv_size, self.hidden))
+            w["v_proj.weight"] = WeightSpec((self.kv_size, self.hidden))
+        return w
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        parts = [tensors["q_proj.weight"]]
+        if not self.shares_kv:
+            parts += [tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        self.qkv.load(torch.cat(parts, dim=0) if len(parts) > 1 else parts[0])
+        self.o.load(tensors["o_proj.weight"])
+
+    # ---- cache ----------------------------------------------------------
+    def kv_need(self) -> Optional[KVNeed]:
+        return KVNeed(self.nkv, self.hd, self.window)
+
+    # ---- one step -------------------------------------------------------
+    def forward(self, h: torch.Tensor, step, cache: LayerCache) -> torch.Tensor:
+        T = h.shape[0]
+        ws = self.env.workspace
+        qkv = self.qkv.forward(h, "attn.qkv", "either")
+        q = ws.get("attn.q", (T, self.q_size), self.env.dtype)
+        table = self.position.rotary_table() if self.position is not None else None
+        writes = cache.writes and not self.shares_kv
+        if self.position is not None and table is None:
+            # an encoding that is not a plain rotation: let it act on views, then store
+            qkv = self._materialise(qkv, T)
+            qv = qkv[:, :self.q_size].unflatten(1, (self.nh, self.hd))
+            kv = qkv[:, self.q_size:self.q_size + self.kv_size].unflatten(1, (-1, self.hd)) \
+                if self.kv_size else None
+            self.position.apply(qv, kv, step.positions)
+        inv_freq, pairing = table if table is not None else (None, 0)
+        ops.rope_kv_store(
+            qkv, q, cache.kv if writes else None, step.positions, step.token_seq,
+            step.block_tables[cache.group] if writes else None, inv_freq, pairing,
+            self.nh, self.nkv if not self.shares_kv else 0, self.hd)
+        attn = ws.get("attn.out", (T, self.q_size), self.env.dtype)
+        ops.attention(q, attn, cache.kv, step.block_tables[cache.group], step.token_seq,
+                      step.positions, self.nh, self.nkv, self.hd, self.scale,
+                      self.window or 0)
+        return self.o.forward(attn, "attn.o", "delta")
+
+    def _materialise(self, qkv: torch.Tensor, T: int) -> torch.Tensor:
+        """Partial sums -> one tensor in the activation type (rare path)."""
+        if qkv.dim() == 2:
+            return qkv
+        return qkv.sum(dim=0).to(self.env.dtype)

@@ -1,0 +1,45 @@
+"""SwiGLU feed-forward: ``down( silu(gate h) * (up h) )``.
+
+``silu(z) = z / (1 + exp(-z))`` (crates/allpaca-cpu/src/kernels.rs:869-871); gate and up
+are separate tensors in the checkpoint (crates/allpaca-core/src/model.rs:5664-5705) and one
+stacked matrix ``[Wgate; Wup]`` here, so one product yields ``[T, 2I]`` and the activation
+kernel reads both halves of a row.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping
+
+import torch
+
+from .. import ops
+from .base import BuildEnv, FeedForward, WeightSpec, register
+from .linear import Linear
+
+
+@register("feed_forward", "swiglu")
+class SwiGLU(FeedForward):
+    """Parameters: ``hidden_size``, ``intermediate_size``."""
+
+    def __init__(self, params, env: BuildEnv):
+        super().__init__(params, env)
+        self.require("hidden_size", "intermediate_size")
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.gate_up = Linear(env, 2 * self.inter, self.hidden)
+        self.down = Linear(env, self.hidden, self.inter)
+
+    def weights(self) -> Dict[str, WeightSpec]:
+        return {"gate_proj.weight": WeightSpec((self.inter, self.hidden)),
+                "up_proj.weight": WeightSpec((self.inter, self.hidden)),
+                "down_proj.weight": WeightSpec((self.hidden, self.inter))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.gate_up.load(torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0))
+        self.down.load(tensors["down_proj.weight"])
+
+    def forward(self, h: torch.Tensor, step) -> torch.Tensor:
+        T = h.shape[0]
+        gu = self.gate_up.forward(h, "ffn.gate_up", "either")
+        act = self.env.workspace.get("ffn.act", (T, self.inter), self.env.dtype)
+        ops.swiglu(gu, act)
+        return self.down.forward(act, "ffn.down", "delta")
