@@ -102,9 +102,11 @@ def test_replay_first_tokens_and_single_token_prompt(tmp_path):
     toks = helpers.random_tokens(12, config["vocab_size"], 9)
     tb = TraceBuilder()
     tb.step([("one", toks[:1], [0])])
-    tb.step([("one", toks[1:2], [0]), ("two", toks[:2], [0, 1])])
-    for i in range(2, 12, 2):
-        tb.step([("one", toks[i:i + 1], [0]), ("two", toks[i:i + 2], [0, 1])])
+    for k in range(1, 12):
+        entries = [("one", toks[k:k + 1], [0])]
+        if 2 * (k - 1) < 12:
+            entries.append(("two", toks[2 * (k - 1):2 * k], [0, 1]))
+        tb.step(entries)
     outputs = helpers.run_trace(model, "float32", str(tmp_path / "out"), tb.steps, 128)
     plain = helpers.plain_logits(model, toks, "float32")
     helpers.compare(outputs, tb, {"one": plain, "two": plain}, TOL["float32"], "first tokens")

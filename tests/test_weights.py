@@ -1,0 +1,132 @@
+"""Safetensors reading and writing, weight errors, random-weights mode."""
+import json
+import os
+import struct
+
+import pytest
+import torch
+
+from allpaca_b200.models import DecoderModel, resolve
+from allpaca_b200.parts import BuildEnv, Workspace
+from allpaca_b200.weights import (Checkpoint, SafetensorsError, SafetensorsFile, WeightError,
+                                  check_names, storage_dtype, write_safetensors)
+from allpaca_b200.weights.random_model import write_random_model
+from helpers import TINY_A, TINY_B
+
+
+def cpu_model(config):
+    arch = resolve(config)
+    cfg = arch.config_class.from_dict(config)
+    env = BuildEnv(torch.float32, torch.device("cpu"), Workspace(torch.device("cpu")))
+    return DecoderModel(arch.spec_builder(cfg), env)
+
+
+def test_round_trip_matches_the_safetensors_package(tmp_path):
+    from safetensors.torch import load_file, save_file
+    t = {"a": torch.randn(3, 5), "b": torch.randn(7).to(torch.bfloat16),
+         "c": torch.arange(6, dtype=torch.int64).view(2, 3), "d": torch.randn(2, 2).to(torch.float16)}
+    p = str(tmp_path / "x.safetensors")
+    write_safetensors(p, t, {"k": "v"})
+    theirs = load_file(p)
+    ours = SafetensorsFile(p)
+    assert ours.metadata == {"k": "v"}
+    for n in t:
+        assert torch.equal(theirs[n], t[n]) and torch.equal(ours.tensor(n), t[n])
+        assert ours.info(n) == (t[n].dtype, tuple(t[n].shape))
+    q = str(tmp_path / "y.safetensors")
+    save_file(t, q)
+    assert all(torch.equal(SafetensorsFile(q).tensor(n), t[n]) for n in t)
+
+
+def test_broken_files_are_named(tmp_path):
+    p = tmp_path / "short.safetensors"
+    p.write_bytes(b"abc")
+    with pytest.raises(SafetensorsError, match="too short"):
+        SafetensorsFile(str(p))
+    p.write_bytes(struct.pack("<Q", 1000) + b"{}")
+    with pytest.raises(SafetensorsError, match="overruns"):
+        SafetensorsFile(str(p))
+    p.write_bytes(struct.pack("<Q", 4) + b"{{{{")
+    with pytest.raises(SafetensorsError, match="not JSON"):
+        SafetensorsFile(str(p))
+    h = json.dumps({"t": {"dtype": "F8", "shape": [1], "data_offsets": [0, 1]}}).encode()
+    p.write_bytes(struct.pack("<Q", len(h)) + h + b"x")
+    with pytest.raises(SafetensorsError, match="unsupported dtype"):
+        SafetensorsFile(str(p))
+    h = json.dumps({"t": {"dtype": "F32", "shape": [2], "data_offsets": [0, 4]}}).encode()
+    p.write_bytes(struct.pack("<Q", len(h)) + h + b"xxxx")
+    with pytest.raises(SafetensorsError, match="needs 8 bytes"):
+        SafetensorsFile(str(p))
+    h = json.dumps({"t": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}}).encode()
+    p.write_bytes(struct.pack("<Q", len(h)) + h + b"xxxx")
+    with pytest.raises(SafetensorsError, match="outside"):
+        SafetensorsFile(str(p))
+    with pytest.raises(SafetensorsError, match="no model folder"):
+        Checkpoint(str(tmp_path / "nowhere"))
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    with pytest.raises(SafetensorsError, match="no .safetensors"):
+        Checkpoint(str(empty))
+
+
+def test_sharded_checkpoint_and_duplicates(tmp_path):
+    write_safetensors(str(tmp_path / "s1.safetensors"), {"a": torch.ones(2)})
+    write_safetensors(str(tmp_path / "s2.safetensors"), {"b": torch.zeros(3)})
+    with pytest.raises(SafetensorsError, match="several"):
+        Checkpoint(str(tmp_path))
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(
+        {"weight_map": {"a": "s1.safetensors", "b": "s2.safetensors"}}))
+    c = Checkpoint(str(tmp_path))
+    assert sorted(c.names()) == ["a", "b"] and c.tensor("b").shape == (3,)
+    write_safetensors(str(tmp_path / "s2.safetensors"), {"a": torch.zeros(3)})
+    with pytest.raises(SafetensorsError, match="appears in both"):
+        Checkpoint(str(tmp_path))
+
+
+def test_one_error_lists_missing_unexpected_and_wrong_shapes():
+    model = cpu_model(TINY_A)
+    targets = model.weight_targets()
+    have = {n: ws.shape for n, (ws, _, _) in targets.items()}
+    del have["model.layers.1.mlp.up_proj.weight"]
+    del have["model.norm.weight"]
+    have["model.layers.0.self_attn.q_proj.bias"] = (64,)
+    have["model.layers.0.self_attn.k_proj.weight"] = (64, 64)
+    with pytest.raises(WeightError) as e:
+        check_names(targets, have)
+    msg = str(e.value)
+    assert "missing tensors (2)" in msg and "model.norm.weight" in msg and "up_proj" in msg
+    assert "unexpected tensors (1)" in msg and "q_proj.bias" in msg
+    assert "wrong shapes (1)" in msg and "has [64, 64], expected [32, 64]" in msg
+
+
+def test_lm_head_may_be_absent_only_as_tying():
+    model = cpu_model(TINY_B)
+    targets = model.weight_targets()
+    have = {n: ws.shape for n, (ws, _, _) in targets.items() if n != "lm_head.weight"}
+    check_names(targets, have)        # tied by absence: fine
+
+
+def test_storage_types():
+    assert storage_dtype(torch.bfloat16, torch.bfloat16) == torch.bfloat16
+    assert storage_dtype(torch.float16, torch.bfloat16) == torch.bfloat16
+    assert storage_dtype(torch.float32, torch.bfloat16) == torch.float32   # stays 32-bit
+    assert storage_dtype(torch.int64, torch.bfloat16) == torch.int32
+
+
+def test_random_weights_are_seeded_and_shaped(tmp_path):
+    a, b, c = (str(tmp_path / x) for x in "abc")
+    write_random_model(a, TINY_B, 1, "float32", norm_std=0.02)
+    write_random_model(b, TINY_B, 1, "float32", norm_std=0.02)
+    write_random_model(c, TINY_B, 2, "bfloat16")
+    ca, cb, cc = Checkpoint(a), Checkpoint(b), Checkpoint(c)
+    assert "lm_head.weight" not in ca                     # tied
+    assert all(torch.equal(ca.tensor(n), cb.tensor(n)) for n in ca.names())
+    assert not torch.equal(ca.tensor("model.embed_tokens.weight").to(torch.bfloat16),
+                           cc.tensor("model.embed_tokens.weight"))
+    w = ca.tensor("model.layers.2.mlp.down_proj.weight")
+    assert w.shape == (96, 256) and abs(float(w.std()) - 0.02) < 0.002
+    n = ca.tensor("model.layers.0.input_layernorm.weight")
+    assert abs(float(n.mean()) - 1.0) < 0.02 and float(n.std()) > 0.005
+    assert torch.equal(cc.tensor("model.norm.weight"), torch.ones(96, dtype=torch.bfloat16))
+    assert json.load(open(os.path.join(c, "config.json")))["torch_dtype"] == "bfloat16"
+    check_names(cpu_model(TINY_B).weight_targets(), {n: ca.info(n)[1] for n in ca.names()})
