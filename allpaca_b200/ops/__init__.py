@@ -246,3 +246,18 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
     if not hasattr(lib, "ap_gemm_tc_plan"):
         return 1
     return max(1, int(lib.ap_gemm_tc_plan(int(M), int(N), int(K))))
+
+
+def gemm_tc_status() -> int:
+    """0 while every tensor-core product ran to its end; else the code of the pipeline wait
+    that expired.  Synchronises the device."""
+    lib = core()
+    return int(lib.ap_gemm_tc_status()) if hasattr(lib, "ap_gemm_tc_status") else 0
+
+
+def check_kernel_status() -> None:
+    """Raise if a kernel reported that it gave up (a bounded wait inside it expired)."""
+    code = gemm_tc_status()
+    if code != 0:
+        raise KernelError(f"the tensor-core matrix product gave up waiting (code {code}: "
+                          f"1 free stage, 2 operands, 3 accumulator); its results are void")

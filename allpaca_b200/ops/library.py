@@ -35,6 +35,8 @@ _OPTIONAL_CORE_SIGNATURES = {
     # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, stream)
     "ap_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _L, _P],
     "ap_gemm_tc_plan": [_I, _I, _I],
+    "ap_gemm_tc_status": [],
+    "ap_gemm_tc_reset_status": [],
 }
 _ATTN_SIGNATURES = {
     "ap_attention_rows": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _L, _F, _I, _P],

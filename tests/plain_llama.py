@@ -231,11 +231,13 @@ def sample_plain(logits: torch.Tensor, temperature: float, top_k: int, top_p: fl
     reference's candidate order.
     """
     l = logits.to(torch.float32).clone()
-    V = l.numel()
+    if not bool(torch.isfinite(l).any()):
+        return 0                              # sampling.rs:37-39
     if temperature <= 1e-5:
         return int(torch.argmax(l))          # torch.argmax returns the first maximum
     l = l / max(temperature, 1e-5)
-    ids = list(range(V))
+    ids = [i for i in range(l.numel()) if bool(torch.isfinite(l[i]))]   # sampling.rs:236-244
+    V = len(ids)
     order = sorted(ids, key=lambda i: (-float(l[i]), i))
     keep = order
     if top_k and top_k < V:
