@@ -106,7 +106,9 @@ _OPTIONAL_ATTN_SIGNATURES: Dict[str, list] = {}
 
 def call(lib: ctypes.CDLL, name: str, *args) -> None:
     """Call an entry point and raise with the library's own message on failure."""
+    global _launches
     rc = getattr(lib, name)(*args)
+    _launches += 1
     if rc != 0:
         msg = lib.ap_last_error()
         raise KernelError(f"{name} failed (status {rc}): {msg.decode() if msg else 'no message'}")
@@ -115,3 +117,11 @@ def call(lib: ctypes.CDLL, name: str, *args) -> None:
 def stream_handle() -> int:
     import torch
     return torch.cuda.current_stream().cuda_stream
+
+
+_launches = 0
+
+
+def launch_count() -> int:
+    """Calls into the kernel libraries so far (each launches one kernel)."""
+    return _launches
