@@ -1,0 +1,536 @@
+// bfloat16 causal grouped-query attention over paged keys and values on the tensor
+// cores, for one head size fixed at compile time (-DAP_HEAD_DIM=...).
+//
+// The query heads that share a KV head are packed into the rows of the MMA tile, so a
+// tile of K and V loaded once serves all of them:
+//
+//   tile kernel   (prompt portions and mixed batches): a CTA owns up to 64 rows
+//                 = tokens x heads-of-one-KV-head of one sequence; its 4 warps take 16
+//                 rows each and walk the same 64-key tiles of the sequence.
+//   split kernel  (decode: one row per sequence): a CTA owns the <= 16 heads of one KV
+//                 head of one row and one slice of the keys; its 4 warps take 16 keys of
+//                 every 64-key tile each and merge at the end; slices of several CTAs are
+//                 written as partial results (value, running maximum, sum) to scratch
+//                 memory and combined by attention_merge_kernel.
+//
+// Keys and values come through the block table straight from the pages (cp.async into
+// padded shared-memory rows, double buffered); pages that were given back (id < 0) and
+// keys outside a row's window are never read.  Scores, softmax statistics and the output
+// accumulate in 32-bit; probabilities are rounded to bfloat16 for the second product.
+//
+// Reference counterparts (cuda/src/kernels.cu): attention_qtile_kernel :1801,
+// attention_split_gqa_kernel :1874, attention_merge_kernel :1997, causal rule :1583-1585.
+#include "common.cuh"
+#include <float.h>
+#include <math.h>
+
+#ifndef AP_HEAD_DIM
+#error "compile with -DAP_HEAD_DIM=<head size>"
+#endif
+
+#define HD AP_HEAD_DIM
+#define BKV 64                         // keys per shared-memory tile
+#define ROW_BYTES (HD * 2 + 16)        // padded row: conflict-free ldmatrix for any HD % 16 == 0
+#define TILE_BYTES (BKV * ROW_BYTES)
+#define KSTEPS (HD / 16)
+#define DTILES (HD / 8)
+#define CHUNKS_PER_ROW (HD / 8)        // 16-byte chunks in a row
+#define ATC_THREADS 128
+#define LOG2E 1.4426950408889634f
+
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
+
+struct AttnTcParams {
+    const bf16* q;
+    bf16* out;
+    const bf16* cache;
+    const int* block_table;
+    const int* seq_start;
+    const int* positions;
+    float* part_o;       // [nsplit][T][nh][HD]
+    float* part_ml;      // [nsplit][T][nh][2]
+    size_t page_stride;
+    int max_blocks, nseq, T, nh, nkv, P, window;
+    int tokens_per_tile, heads_per_chunk, n_chunks, nsplit;
+    float scale_log2;    // softmax scale * log2(e)
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Shared memory of both kernels: two stages of (K tile, V tile) and the row pointers of
+// the tile being fetched.
+struct SmemLayout {
+    static constexpr int kStage = 2 * TILE_BYTES;
+    static constexpr int kPtrs = 2 * kStage;
+    static constexpr int kTotal = kPtrs + BKV * 8;
+};
+
+// Fetch keys k0 .. k0+63 of one KV head into a stage.  Keys outside [kmin, kmax] (or in a
+// page that was given back) become zero rows.
+__device__ __forceinline__ void fetch_tile(uint8_t* smem, int stage, int k0, int kmin, int kmax,
+                                           const bf16* cache, const int* table, int P, size_t page_stride,
+                                           size_t head_off, size_t v_off) {
+    const bf16** ptrs = reinterpret_cast<const bf16**>(smem + SmemLayout::kPtrs);
+    if (threadIdx.x < BKV) {
+        const int kpos = k0 + threadIdx.x;
+        const bf16* p = nullptr;
+        if (kpos >= kmin && kpos <= kmax) {
+            const int page = table[kpos / P];
+            if (page >= 0) p = cache + (size_t)page * page_stride + head_off + (size_t)(kpos % P) * HD;
+        }
+        ptrs[threadIdx.x] = p;
+    }
+    __syncthreads();
+    uint8_t* ks = smem + stage * SmemLayout::kStage;
+    uint8_t* vs = ks + TILE_BYTES;
+    for (int c = threadIdx.x; c < BKV * CHUNKS_PER_ROW; c += ATC_THREADS) {
+        const int key = c / CHUNKS_PER_ROW, ch = c - key * CHUNKS_PER_ROW;
+        const bf16* p = ptrs[key];
+        const uint32_t off = key * ROW_BYTES + ch * 16;
+        if (p) {
+            cp_async16((uint32_t)__cvta_generic_to_shared(ks + off), p + ch * 8);
+            cp_async16((uint32_t)__cvta_generic_to_shared(vs + off), p + v_off + ch * 8);
+        } else {
+            *reinterpret_cast<uint4*>(ks + off) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vs + off) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// One warp's share of a tile: NT n-tiles of 8 keys starting at key `key0` of the tile.
+// Updates the running maximum (log2 domain), the per-thread partial sums and the output.
+template <int NT>
+__device__ __forceinline__ void process_keys(const uint8_t* ks, const uint8_t* vs, int key0, int k0,
+                                             const uint32_t (&qf)[KSTEPS][4], float (&o)[DTILES][4],
+                                             float (&m)[2], float (&l)[2], const int (&qpos)[2],
+                                             const bool (&rvalid)[2], int window, float scale_log2) {
+    const int lane = threadIdx.x & 31;
+    const int mi = lane >> 3, r8 = lane & 7;
+    float s[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(ks);
+    const uint32_t vs_base = (uint32_t)__cvta_generic_to_shared(vs);
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+            uint32_t b[4];
+            const int key = key0 + np * 16 + (mi >> 1) * 8 + r8;
+            ldmatrix_x4(b, ks_base + key * ROW_BYTES + (kk * 2 + (mi & 1)) * 16);
+            mma_16816(s[2 * np], qf[kk], b[0], b[1]);
+            mma_16816(s[2 * np + 1], qf[kk], b[2], b[3]);
+        }
+    }
+    // scale, mask, running maximum
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            const int kpos = k0 + key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+            const bool ok = rvalid[h] && kpos <= qpos[h] && (window <= 0 || qpos[h] - kpos < window);
+            const float v = ok ? s[j][e] * scale_log2 : -INFINITY;
+            s[j][e] = v;
+            mx[h] = fmaxf(mx[h], v);
+        }
+    }
+    float alpha[2], muse[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float mnew = fmaxf(m[h], mx[h]);
+        muse[h] = mnew == -INFINITY ? 0.f : mnew;       // no visible key yet: keep everything at zero
+        alpha[h] = exp2f(m[h] - muse[h]);               // m = -inf gives 0
+        m[h] = mnew;
+        l[h] *= alpha[h];
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float p = exp2f(s[j][e] - muse[e >> 1]);
+            s[j][e] = p;
+            l[e >> 1] += p;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < DTILES; ++j) {
+        o[j][0] *= alpha[0];
+        o[j][1] *= alpha[0];
+        o[j][2] *= alpha[1];
+        o[j][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int ksx = 0; ksx < NT / 2; ++ksx) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * ksx][0], s[2 * ksx][1]);
+        a[1] = pack_bf16(s[2 * ksx][2], s[2 * ksx][3]);
+        a[2] = pack_bf16(s[2 * ksx + 1][0], s[2 * ksx + 1][1]);
+        a[3] = pack_bf16(s[2 * ksx + 1][2], s[2 * ksx + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) {
+            uint32_t b[4];
+            const int key = key0 + ksx * 16 + (mi & 1) * 8 + r8;
+            ldmatrix_x4_trans(b, vs_base + key * ROW_BYTES + (dp * 2 + (mi >> 1)) * 16);
+            mma_16816(o[2 * dp], a, b[0], b[1]);
+            mma_16816(o[2 * dp + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+__device__ __forceinline__ void load_q_frags(uint32_t (&qf)[KSTEPS][4], const bf16* qa, const bf16* qb) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+        const int c = kk * 16 + (lane & 3) * 2;
+        qf[kk][0] = qa ? *reinterpret_cast<const uint32_t*>(qa + c) : 0u;
+        qf[kk][1] = qb ? *reinterpret_cast<const uint32_t*>(qb + c) : 0u;
+        qf[kk][2] = qa ? *reinterpret_cast<const uint32_t*>(qa + c + 8) : 0u;
+        qf[kk][3] = qb ? *reinterpret_cast<const uint32_t*>(qb + c + 8) : 0u;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// tile kernel: grid (query tiles over all sequences, nkv * n_chunks)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(ATC_THREADS)
+attention_tile_kernel(const AttnTcParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ int s_seq, s_tile;
+    if (threadIdx.x == 0) {
+        int t = blockIdx.x, found = -1;
+        for (int s = 0; s < p.nseq; ++s) {
+            const int n = p.seq_start[s + 1] - p.seq_start[s];
+            const int nt = (n + p.tokens_per_tile - 1) / p.tokens_per_tile;
+            if (t < nt) { found = s; break; }
+            t -= nt;
+        }
+        s_seq = found;
+        s_tile = t;
+    }
+    __syncthreads();
+    if (s_seq < 0) return;
+    const int seq = s_seq;
+    const int row0 = p.seq_start[seq] + s_tile * p.tokens_per_tile;
+    const int ntok = min(p.tokens_per_tile, p.seq_start[seq + 1] - row0);
+    const int reps = p.nh / p.nkv;
+    const int kvh = blockIdx.y / p.n_chunks, chunk = blockIdx.y - kvh * p.n_chunks;
+    const int HC = p.heads_per_chunk;
+    const int head0 = kvh * reps + chunk * HC;
+    const int nheads = min(HC, reps - chunk * HC);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    int qpos[2];
+    bool rvalid[2];
+    const bf16* qptr[2];
+    bf16* optr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = warp * 16 + (lane >> 2) + h * 8;
+        const int tok = r / HC, hq = r - tok * HC;
+        rvalid[h] = tok < ntok && hq < nheads;
+        const int row = row0 + (rvalid[h] ? tok : 0);
+        qpos[h] = p.positions[row];
+        const size_t off = ((size_t)row * p.nh + head0 + (rvalid[h] ? hq : 0)) * HD;
+        qptr[h] = rvalid[h] ? p.q + off : nullptr;
+        optr[h] = rvalid[h] ? p.out + off : nullptr;
+    }
+    uint32_t qf[KSTEPS][4];
+    load_q_frags(qf, qptr[0], qptr[1]);
+
+    const int kmax = p.positions[row0 + ntok - 1];
+    const int first = p.positions[row0];
+    const int kmin = (p.window > 0 && first - p.window + 1 > 0) ? first - p.window + 1 : 0;
+    const int* table = p.block_table + (size_t)seq * p.max_blocks;
+    const size_t head_off = (size_t)kvh * p.P * HD;
+    const size_t v_off = (size_t)p.nkv * p.P * HD;
+
+    float o[DTILES][4];
+#pragma unroll
+    for (int j = 0; j < DTILES; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    // the last position any row of this warp holds (-1: the warp has no valid row)
+    int wm = max(rvalid[0] ? qpos[0] : -1, rvalid[1] ? qpos[1] : -1);
+    wm = max(wm, __shfl_xor_sync(0xffffffffu, wm, 4));
+    wm = max(wm, __shfl_xor_sync(0xffffffffu, wm, 8));
+    wm = max(wm, __shfl_xor_sync(0xffffffffu, wm, 16));
+
+    const int t_lo = kmin / BKV, t_hi = kmax / BKV;
+    fetch_tile(smem, 0, t_lo * BKV, kmin, kmax, p.cache, table, p.P, p.page_stride, head_off, v_off);
+    cp_async_commit();
+    for (int t = t_lo; t <= t_hi; ++t) {
+        const int cur = (t - t_lo) & 1;
+        if (t < t_hi)
+            fetch_tile(smem, cur ^ 1, (t + 1) * BKV, kmin, kmax, p.cache, table, p.P, p.page_stride, head_off, v_off);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint8_t* ks = smem + cur * SmemLayout::kStage;
+        // a warp whose rows all sit before this tile has nothing to add (causal)
+        if (wm >= t * BKV)
+            process_keys<8>(ks, ks + TILE_BYTES, 0, t * BKV, qf, o, m, l, qpos, rvalid, p.window, p.scale_log2);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (!optr[h]) continue;
+        const float inv = l[h] > 0.f ? 1.0f / l[h] : 0.f;
+#pragma unroll
+        for (int j = 0; j < DTILES; ++j) {
+            const int d = j * 8 + (lane & 3) * 2;
+            *reinterpret_cast<uint32_t*>(optr[h] + d) = pack_bf16(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// split kernel: grid (rows, nkv * n_chunks, nsplit); every sequence brings one row
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(ATC_THREADS)
+attention_split_kernel(const AttnTcParams p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int row = blockIdx.x;              // row == sequence index
+    const int reps = p.nh / p.nkv;
+    const int kvh = blockIdx.y / p.n_chunks, chunk = blockIdx.y - kvh * p.n_chunks;
+    const int HC = p.heads_per_chunk;       // <= 16
+    const int head0 = kvh * reps + chunk * HC;
+    const int nheads = min(HC, reps - chunk * HC);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = p.positions[row];
+
+    int qpos[2] = {pos, pos};
+    bool rvalid[2];
+    const bf16* qptr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = (lane >> 2) + h * 8;
+        rvalid[h] = r < nheads;
+        qptr[h] = rvalid[h] ? p.q + ((size_t)row * p.nh + head0 + r) * HD : nullptr;
+    }
+    uint32_t qf[KSTEPS][4];
+    load_q_frags(qf, qptr[0], qptr[1]);
+
+    const int kmax = pos;
+    const int kmin = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int* table = p.block_table + (size_t)row * p.max_blocks;
+    const size_t head_off = (size_t)kvh * p.P * HD;
+    const size_t v_off = (size_t)p.nkv * p.P * HD;
+    const int t_first = kmin / BKV, t_last = kmax / BKV;
+    const int ntiles = t_last - t_first + 1;
+    const int per = (ntiles + p.nsplit - 1) / p.nsplit;
+    const int t_lo = t_first + blockIdx.z * per;
+    const int t_hi = min(t_last, t_lo + per - 1);
+
+    float o[DTILES][4];
+#pragma unroll
+    for (int j = 0; j < DTILES; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    if (t_lo <= t_hi) {
+        fetch_tile(smem, 0, t_lo * BKV, kmin, kmax, p.cache, table, p.P, p.page_stride, head_off, v_off);
+        cp_async_commit();
+        for (int t = t_lo; t <= t_hi; ++t) {
+            const int cur = (t - t_lo) & 1;
+            if (t < t_hi)
+                fetch_tile(smem, cur ^ 1, (t + 1) * BKV, kmin, kmax, p.cache, table, p.P, p.page_stride, head_off,
+                           v_off);
+            cp_async_commit();
+            cp_async_wait<1>();
+            __syncthreads();
+            const uint8_t* ks = smem + cur * SmemLayout::kStage;
+            if (t * BKV + warp * 16 <= kmax)
+                process_keys<2>(ks, ks + TILE_BYTES, warp * 16, t * BKV, qf, o, m, l, qpos, rvalid, p.window,
+                                p.scale_log2);
+            __syncthreads();
+        }
+        cp_async_wait<0>();
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    // merge the four warps (each saw a quarter of the keys) through shared memory
+    __syncthreads();
+    float* so = reinterpret_cast<float*>(smem);                 // [4][16][HD]
+    float* sm = so + 4 * 16 * HD;                               // [4][16]
+    float* sl = sm + 4 * 16;                                    // [4][16]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = (lane >> 2) + h * 8;
+        float* dst = so + ((size_t)warp * 16 + r) * HD;
+#pragma unroll
+        for (int j = 0; j < DTILES; ++j) {
+            const int d = j * 8 + (lane & 3) * 2;
+            dst[d] = o[j][2 * h];
+            dst[d + 1] = o[j][2 * h + 1];
+        }
+        if ((lane & 3) == 0) {
+            sm[warp * 16 + r] = m[h];
+            sl[warp * 16 + r] = l[h];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nheads * HD; idx += ATC_THREADS) {
+        const int r = idx / HD, d = idx - r * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + r]);
+        float L = 0.f, O = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = exp2f(sm[w * 16 + r] - M);
+                L += sl[w * 16 + r] * f;
+                O += so[((size_t)w * 16 + r) * HD + d] * f;
+            }
+        }
+        const float val = L > 0.f ? O / L : 0.f;
+        const size_t orow = (size_t)row * p.nh + head0 + r;
+        if (p.nsplit == 1) {
+            p.out[orow * HD + d] = __float2bfloat16_rn(val);
+        } else {
+            const size_t prow = (size_t)blockIdx.z * p.T * p.nh + orow;
+            p.part_o[prow * HD + d] = val;
+            if (d == 0) {
+                p.part_ml[prow * 2] = M;
+                p.part_ml[prow * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// combine the slices of the split kernel: grid (rows, heads)
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       bf16* __restrict__ out, int T, int nh, int nsplit) {
+    const size_t orow = (size_t)blockIdx.x * nh + blockIdx.y;
+    float M = -INFINITY;
+    for (int z = 0; z < nsplit; ++z) M = fmaxf(M, part_ml[((size_t)z * T * nh + orow) * 2]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float L = 0.f, O = 0.f;
+        if (M != -INFINITY) {
+            for (int z = 0; z < nsplit; ++z) {
+                const size_t prow = (size_t)z * T * nh + orow;
+                const float lz = part_ml[prow * 2 + 1];
+                if (lz <= 0.f) continue;
+                const float f = lz * exp2f(part_ml[prow * 2] - M);
+                L += f;
+                O += part_o[prow * HD + d] * f;
+            }
+        }
+        out[orow * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+}
+
+static int configure_smem(const void* kern, int bytes) {
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) {
+            ap_set_error("attention: cannot reserve %d bytes of shared memory: %s", bytes, cudaGetErrorString(e));
+            return AP_ERR_LAUNCH;
+        }
+    }
+    return AP_OK;
+}
+
+// mode 0: tile kernel over `total_tiles` query tiles (prompt portions, mixed batches);
+// mode 1: split kernel, one row per sequence, `nsplit` key slices; part_o/part_ml are
+//         scratch of nsplit*T*nh*HD and nsplit*T*nh*2 floats (unused for nsplit == 1).
+AP_EXPORT int ap_attention_tc(const void* q, void* out, const void* cache, const int* block_table,
+                              int max_blocks, const int* seq_start, const int* positions, int nseq, int T,
+                              int nh, int nkv, int hd, int P, long long page_stride, float scale, int window,
+                              int mode, int total_tiles, int nsplit, float* part_o, float* part_ml,
+                              cudaStream_t stream) {
+    AP_REQUIRE(hd == HD, "attention: this library was compiled for head size %d, not %d", HD, hd);
+    AP_REQUIRE(T >= 0 && nseq >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0 && P > 0 && max_blocks > 0,
+               "attention: bad sizes T=%d heads=%d kv_heads=%d page=%d", T, nh, nkv, P);
+    if (T == 0 || nseq == 0) return AP_OK;
+    AttnTcParams p;
+    p.q = (const bf16*)q; p.out = (bf16*)out; p.cache = (const bf16*)cache;
+    p.block_table = block_table; p.seq_start = seq_start; p.positions = positions;
+    p.part_o = part_o; p.part_ml = part_ml; p.page_stride = (size_t)page_stride;
+    p.max_blocks = max_blocks; p.nseq = nseq; p.T = T; p.nh = nh; p.nkv = nkv; p.P = P; p.window = window;
+    p.scale_log2 = scale * LOG2E;
+    const int reps = nh / nkv;
+    static bool configured = false;
+    const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
+    const int smem_bytes = SmemLayout::kTotal > merge_bytes ? SmemLayout::kTotal : merge_bytes;
+    if (!configured) {
+        int rc = configure_smem((const void*)attention_tile_kernel, smem_bytes);
+        if (rc != AP_OK) return rc;
+        rc = configure_smem((const void*)attention_split_kernel, smem_bytes);
+        if (rc != AP_OK) return rc;
+        configured = true;
+    }
+    if (mode == 0) {
+        p.heads_per_chunk = reps < 64 ? reps : 64;
+        p.n_chunks = (reps + p.heads_per_chunk - 1) / p.heads_per_chunk;
+        p.tokens_per_tile = 64 / p.heads_per_chunk;
+        p.nsplit = 1;
+        AP_REQUIRE(total_tiles > 0, "attention: the tile kernel needs the number of query tiles");
+        AP_REQUIRE(nkv * p.n_chunks <= 65535, "attention: too many KV heads for the grid");
+        dim3 grid(total_tiles, nkv * p.n_chunks);
+        attention_tile_kernel<<<grid, ATC_THREADS, smem_bytes, stream>>>(p);
+        AP_CHECK_LAUNCH("attention_tile");
+        return AP_OK;
+    }
+    AP_REQUIRE(mode == 1, "attention: unknown mode %d", mode);
+    AP_REQUIRE(nseq == T, "attention: the split kernel takes one row per sequence (T=%d, nseq=%d)", T, nseq);
+    AP_REQUIRE(nsplit >= 1 && nsplit <= 65535, "attention: bad number of key slices %d", nsplit);
+    AP_REQUIRE(nsplit == 1 || (part_o && part_ml), "attention: key slices need scratch memory");
+    p.heads_per_chunk = reps < 16 ? reps : 16;
+    p.n_chunks = (reps + p.heads_per_chunk - 1) / p.heads_per_chunk;
+    p.tokens_per_tile = 1;
+    p.nsplit = nsplit;
+    AP_REQUIRE(nkv * p.n_chunks <= 65535, "attention: too many KV heads for the grid");
+    dim3 grid(T, nkv * p.n_chunks, nsplit);
+    attention_split_kernel<<<grid, ATC_THREADS, smem_bytes, stream>>>(p);
+    AP_CHECK_LAUNCH("attention_split");
+    if (nsplit > 1) {
+        dim3 mgrid(T, nh);
+        attention_merge_kernel<<<mgrid, HD < 128 ? 64 : 128, 0, stream>>>(part_o, part_ml, (bf16*)out, T, nh, nsplit);
+        AP_CHECK_LAUNCH("attention_merge");
+    }
+    return AP_OK;
+}
+
+// how many query rows of one sequence a tile of the tile kernel holds
+AP_EXPORT int ap_attention_tc_tokens_per_tile(int nh, int nkv) {
+    const int reps = nh / nkv;
+    const int hc = reps < 64 ? reps : 64;
+    return 64 / hc;
+}

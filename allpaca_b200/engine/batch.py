@@ -41,6 +41,7 @@ class StepBatch:
     block_tables: List[torch.Tensor]   # per cache group: [nseq, max_pages] int32
     # host copies for parts that walk sequences themselves
     host_seq_start: List[int] = field(default_factory=list)
+    host_query_lens: List[int] = field(default_factory=list)
     host_first_position: List[int] = field(default_factory=list)
     host_state_slots: List[int] = field(default_factory=list)
     max_query_len: int = 0

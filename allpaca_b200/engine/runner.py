@@ -210,6 +210,7 @@ class ModelRunner:
             logit_rows=view(r_rows),
             block_tables=[view(r_tables[g]).view(nseq, widths[g]) for g in groups],
             host_seq_start=starts, host_first_position=firsts,
+            host_query_lens=[len(en.tokens) for en in entries],
             host_state_slots=[self.cache.state_slot(en.request) for en in entries],
             max_query_len=max_q, max_context_len=max_ctx)
 

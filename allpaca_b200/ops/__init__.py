@@ -6,7 +6,7 @@ consumer a 32-bit tensor ``[S, T, N]``; consumers add the S slices in order.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -196,8 +196,16 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1
 def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
               block_table: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-              window: int = 0) -> None:
-    """Causal attention of every row of ``q [T, nh*hd]`` over its sequence's cached keys."""
+              window: int = 0, seq_start: Optional[torch.Tensor] = None,
+              query_lens: Optional[Sequence[int]] = None, max_context: int = 0,
+              scratch=None) -> None:
+    """Causal attention of every row of ``q [T, nh*hd]`` over its sequence's cached keys.
+
+    float32 runs the general CUDA-core kernel (the true 32-bit path).  bfloat16 runs on the
+    tensor cores when ``seq_start`` (device, ``[nseq+1]``) and ``query_lens`` (host) are
+    given: the split kernel when every sequence brings one row, else the tile kernel.
+    ``scratch(name, shape, dtype)`` supplies the partial-result buffers of the split kernel.
+    """
     _check(q, "q", dims=2)
     _check(out, "out", q.dtype, 2)
     _check(cache_layer, "cache_layer", q.dtype, 5)
@@ -211,10 +219,46 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
     if two != 2 or nkv != num_kv_heads or hd != head_dim:
         raise KernelError("attention: cache layer does not match the heads")
     lib = library.attention(head_dim)
+    if q.dtype == torch.bfloat16 and seq_start is not None and query_lens is not None \
+            and hasattr(lib, "ap_attention_tc"):
+        _check(seq_start, "seq_start", torch.int32, 1)
+        nseq = len(query_lens)
+        if seq_start.shape[0] != nseq + 1 or sum(query_lens) != T:
+            raise KernelError("attention: seq_start/query_lens do not describe the rows")
+        if all(n == 1 for n in query_lens):
+            nsplit = decode_splits(T, num_heads, num_kv_heads, max_context, window)
+            po = pm = 0
+            if nsplit > 1:
+                if scratch is None:
+                    raise KernelError("attention: key slices need a scratch provider")
+                po = scratch("attn.part_o", (nsplit, T, num_heads, head_dim), torch.float32).data_ptr()
+                pm = scratch("attn.part_ml", (nsplit, T, num_heads, 2), torch.float32).data_ptr()
+            mode, tiles = 1, 0
+        else:
+            tpt = int(lib.ap_attention_tc_tokens_per_tile(num_heads, num_kv_heads))
+            tiles = sum(-(-n // tpt) for n in query_lens)
+            mode, nsplit, po, pm = 0, 1, 0, 0
+        call(lib, "ap_attention_tc", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
+             block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(), positions.data_ptr(),
+             nseq, T, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0), float(scale),
+             int(window or 0), mode, tiles, nsplit, po, pm, stream_handle())
+        return
     call(lib, "ap_attention_rows", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
          dtype_code(q.dtype), block_table.data_ptr(), block_table.shape[1], token_seq.data_ptr(),
          positions.data_ptr(), T, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0),
          float(scale), int(window or 0), stream_handle())
+
+
+def decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: int, window: int = 0) -> int:
+    """Key slices for the split kernel: enough CTAs to fill the GPU about three times over,
+    but no slice shorter than two 64-key tiles."""
+    reps = num_heads // num_kv_heads
+    chunks = -(-reps // min(reps, 16))
+    ctas = max(1, rows * num_kv_heads * chunks)
+    keys = max_context if not window else min(max_context, window)
+    tiles = max(1, -(-max(keys, 1) // 64))
+    want = -(-444 // ctas)
+    return int(max(1, min(want, tiles // 2 if tiles >= 2 else 1, 64)))
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -101,7 +101,10 @@ def attention(head_dim: int) -> ctypes.CDLL:
     return lib
 
 
-_OPTIONAL_ATTN_SIGNATURES: Dict[str, list] = {}
+_OPTIONAL_ATTN_SIGNATURES: Dict[str, list] = {
+    "ap_attention_tc": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _L, _F, _I, _I, _I, _I, _P, _P, _P],
+    "ap_attention_tc_tokens_per_tile": [_I, _I],
+}
 
 
 def call(lib: ctypes.CDLL, name: str, *args) -> None:

@@ -94,7 +94,8 @@ class GroupedQueryAttention(Mixer):
         attn = ws.get("attn.out", (T, self.q_size), self.env.dtype)
         ops.attention(q, attn, cache.kv, step.block_tables[cache.group], step.token_seq,
                       step.positions, self.nh, self.nkv, self.hd, self.scale,
-                      self.window or 0)
+                      self.window or 0, seq_start=step.seq_start, query_lens=step.host_query_lens,
+                      max_context=step.max_context_len, scratch=ws.get)
         return self.o.forward(attn, "attn.o", "delta")
 
     def _materialise(self, qkv: torch.Tensor, T: int) -> torch.Tensor:

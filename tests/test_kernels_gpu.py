@@ -282,3 +282,150 @@ def test_sample_distribution(ops):
     assert counts[p == 0].sum() == 0
     chi2 = float((((counts - n * p) ** 2)[p > 0] / (n * p[p > 0])).sum())
     assert chi2 < 30.0            # 7 degrees of freedom: P(chi2 > 30) ~ 1e-4
+
+
+# ---------------------------------------------------------------- attention over pages
+def paged_case(seqs, nh, nkv, hd, P, dtype, seed, freed_before=None):
+    """Random queries and a paged cache for sequences given as (context length, query rows).
+    Pages are handed out in a shuffled order so that neighbours in a sequence are far apart
+    in memory.  `freed_before[s]`: pages wholly before that position are marked given back."""
+    g = torch.Generator().manual_seed(seed)
+    max_pages = max(-(-c // P) for c, _ in seqs)
+    total_pages = sum(-(-c // P) for c, _ in seqs) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    cache = torch.randn(total_pages, 2, nkv, P, hd, generator=g).to(dtype)   # junk in unused slots
+    table = torch.full((len(seqs), max_pages), -1, dtype=torch.int32)
+    ks, vs, rows_q, token_seq, positions, seq_start = [], [], [], [], [], [0]
+    for s, (ctx, qn) in enumerate(seqs):
+        k = torch.randn(ctx, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(ctx, nkv, hd, generator=g).to(dtype)
+        for j in range(-(-ctx // P)):
+            page = perm.pop()
+            n = min(P, ctx - j * P)
+            if freed_before and j * P + P <= freed_before[s]:
+                continue                                            # given back: stays -1
+            table[s, j] = page
+            cache[page, 0, :, :n] = k[j * P:j * P + n].transpose(0, 1)
+            cache[page, 1, :, :n] = v[j * P:j * P + n].transpose(0, 1)
+        ks.append(k), vs.append(v)
+        rows_q.append(torch.randn(qn, nh, hd, generator=g).to(dtype))
+        token_seq += [s] * qn
+        positions += list(range(ctx - qn, ctx))
+        seq_start.append(seq_start[-1] + qn)
+    q = torch.cat(rows_q).reshape(-1, nh * hd)
+    return dict(q=q, cache=cache, table=table, token_seq=torch.tensor(token_seq, dtype=torch.int32),
+                positions=torch.tensor(positions, dtype=torch.int32),
+                seq_start=torch.tensor(seq_start, dtype=torch.int32), ks=ks, vs=vs, rows_q=rows_q,
+                query_lens=[qn for _, qn in seqs])
+
+
+def reference_attention(case, seqs, nh, hd, window, scale=None):
+    outs = []
+    for s, (ctx, qn) in enumerate(seqs):
+        qfull = torch.zeros(ctx, nh, hd, dtype=torch.float64)
+        qfull[ctx - qn:] = case["rows_q"][s].double()
+        o = plain_llama.causal_attention(qfull, case["ks"][s].double(), case["vs"][s].double(),
+                                         window=window, scale=scale)
+        outs.append(o[ctx - qn:])
+    return torch.cat(outs).reshape(-1, nh * hd)
+
+
+def run_attention(ops, case, nh, nkv, hd, scale, window, tensor_cores):
+    q = dev(case["q"])
+    out = torch.empty_like(q)
+    bufs = {}
+
+    def scratch(name, shape, dtype):
+        bufs[name] = torch.empty(shape, dtype=dtype, device="cuda")
+        return bufs[name]
+    kw = {}
+    if tensor_cores:
+        kw = dict(seq_start=dev(case["seq_start"]), query_lens=case["query_lens"],
+                  max_context=int(case["positions"].max()) + 1, scratch=scratch)
+    ops.attention(q, out, dev(case["cache"]), dev(case["table"]), dev(case["token_seq"]),
+                  dev(case["positions"]), nh, nkv, hd, scale, window, **kw)
+    return out.cpu()
+
+
+ATT_SHAPES = [  # heads, kv heads, head size, page size
+    (4, 2, 16, 16), (3, 1, 32, 8), (6, 3, 48, 4), (8, 8, 64, 16), (8, 2, 128, 16), (5, 1, 80, 32),
+    (20, 1, 16, 16)]
+MIXED = [(700, 1), (129, 129), (64, 2), (333, 40), (1, 1), (65, 65), (200, 1)]
+DECODE = [(700, 1), (129, 1), (64, 1), (1, 1), (65, 1), (1500, 1)]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,P", ATT_SHAPES)
+@pytest.mark.parametrize("window", [0, 37])
+def test_attention_float32(ops, nh, nkv, hd, P, window):
+    seqs = MIXED[:5]
+    case = paged_case(seqs, nh, nkv, hd, P, torch.float32, seed=hd + P)
+    scale = 1.0 / math.sqrt(hd)
+    got = run_attention(ops, case, nh, nkv, hd, scale, window, tensor_cores=False)
+    ref = reference_attention(case, seqs, nh, hd, window or None)
+    assert rel_err(got, ref) < 2e-5
+
+
+@pytest.mark.parametrize("nh,nkv,hd,P", ATT_SHAPES)
+@pytest.mark.parametrize("window", [0, 37, 200])
+@pytest.mark.parametrize("mode", ["mixed", "decode", "rows"])
+def test_attention_bfloat16(ops, nh, nkv, hd, P, window, mode):
+    seqs = DECODE if mode == "decode" else MIXED
+    case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=hd + P + 1)
+    scale = 0.7 / math.sqrt(hd)
+    got = run_attention(ops, case, nh, nkv, hd, scale, window, tensor_cores=(mode != "rows"))
+    ref = reference_attention(case, seqs, nh, hd, window or None, scale=scale)
+    assert rel_err(got, ref) < 1.5e-2
+
+
+@pytest.mark.parametrize("dtype,tensor_cores", [(torch.float32, False), (torch.bfloat16, False),
+                                                (torch.bfloat16, True)])
+@pytest.mark.parametrize("far", [0, 3, 15, 16, 63, 64, 127, 128, 500, 1023])
+def test_attention_finds_one_far_key(ops, dtype, tensor_cores, far):
+    """One key among a thousand is made to win the softmax; its value must come out.  A key
+    that a kernel skips (a page's edge, a tile's edge, the first or last key) shows at once."""
+    nh, nkv, hd, P = 4, 2, 32, 16
+    ctx = 1024
+    for seqs in ([(ctx, 1)], [(ctx, 5)]):
+        case = paged_case(seqs, nh, nkv, hd, P, dtype, seed=far)
+        k, v = case["ks"][0], case["vs"][0]
+        qrow = case["rows_q"][0][-1]                       # the last row sees every key
+        for h in range(nkv):
+            k[far, h] = (qrow[h * 2].float() * 40.0 / qrow[h * 2].float().norm()).to(dtype)
+            v[far, h] = torch.full((hd,), 3.0 + h).to(dtype)
+        page = int(case["table"][0, far // P])
+        case["cache"][page, 0, :, far % P] = k[far]
+        case["cache"][page, 1, :, far % P] = v[far]
+        # make the query long enough that the chosen key dominates
+        for h in range(nkv):
+            case["rows_q"][0][-1, h * 2] = (qrow[h * 2].float() * 3.0).to(dtype)
+        case["q"] = torch.cat(case["rows_q"]).reshape(-1, nh * hd)
+        got = run_attention(ops, case, nh, nkv, hd, 1.0, 0, tensor_cores).view(-1, nh, hd)[-1]
+        ref = reference_attention(case, seqs, nh, hd, None, scale=1.0).view(-1, nh, hd)[-1]
+        for h in range(nkv):
+            assert abs(float(ref[h * 2].mean()) - (3.0 + h)) < 0.05       # the construction works
+            assert float((got[h * 2].double() - ref[h * 2]).abs().max()) < (1e-4 if dtype == torch.float32 else 0.05)
+
+
+@pytest.mark.parametrize("tensor_cores", [False, True])
+def test_attention_window_edge_and_freed_pages(ops, tensor_cores):
+    """Keys just inside and just outside the window, with the pages before the window given
+    back (their table entries are -1 and must never be read)."""
+    nh, nkv, hd, P, window = 2, 1, 16, 8, 20
+    seqs = [(100, 1), (61, 3)]
+    # the first visible key of a sequence's first query row is pos - window + 1
+    freed = [100 - 1 - window + 1, 61 - 3 - window + 1]
+    case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=3, freed_before=freed)
+    for s, (ctx, qn) in enumerate(seqs):
+        inside, outside = ctx - window, ctx - window - 1
+        for pos, val in ((inside, 5.0), (outside, -7.0)):
+            case["ks"][s][pos, 0] = (case["rows_q"][s][-1, 0].float() * 30 /
+                                     case["rows_q"][s][-1, 0].float().norm()).bfloat16()
+            case["vs"][s][pos, 0] = val
+            page = int(case["table"][s, pos // P])
+            if page >= 0:
+                case["cache"][page, 0, :, pos % P] = case["ks"][s][pos]
+                case["cache"][page, 1, :, pos % P] = case["vs"][s][pos]
+    got = run_attention(ops, case, nh, nkv, hd, 1.0, window, tensor_cores)
+    ref = reference_attention(case, seqs, nh, hd, window, scale=1.0)
+    assert rel_err(got, ref) < 1.5e-2
+    assert float(ref.view(-1, nh, hd)[0, 0].mean()) > 4.0     # the key at the window's edge is seen
