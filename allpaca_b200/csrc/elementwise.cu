@@ -46,30 +46,49 @@ AP_EXPORT int ap_embed_gather(const int* tokens, const void* table, int table_dt
 //   rows != nullptr: only the listed rows are normed into out[r]; x is left as it is.
 // One block per row, the row kept in shared memory between the two passes.
 // ---------------------------------------------------------------------------
-#define NORM_THREADS 256
-
-template <typename TW, typename TO>
-__global__ void __launch_bounds__(NORM_THREADS)
+// The block is sized to the row (up to 1024 threads) and works on float4 when the width
+// allows, so that a decode step's few rows still have many loads in flight.
+template <typename TW, typename TO, int VEC>
+__global__ void __launch_bounds__(1024)
 add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int S, size_t delta_stride,
                    const TW* __restrict__ w, float eps, TO* __restrict__ out,
                    const int* __restrict__ rows, int H) {
-    extern __shared__ float row_buf[];
+    extern __shared__ __align__(16) float row_buf[];
     __shared__ float red[32];
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
     float* xr = x + (size_t)t * H;
+    const float* dr = delta + (size_t)t * H;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += NORM_THREADS) {
-        float v = xr[i];
-        for (int s = 0; s < S; ++s) v += delta[(size_t)s * delta_stride + (size_t)t * H + i];
-        row_buf[i] = v;
-        ss = fmaf(v, v, ss);
-        if (!rows && S > 0) xr[i] = v;
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        float v[VEC];
+        if (VEC == 4) {
+            const float4 a = *reinterpret_cast<const float4*>(xr + i);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+#pragma unroll 4
+            for (int s = 0; s < S; ++s) {
+                const float4 d = *reinterpret_cast<const float4*>(dr + (size_t)s * delta_stride + i);
+                v[0] += d.x; v[1] += d.y; v[2] += d.z; v[3] += d.w;
+            }
+        } else {
+            v[0] = xr[i];
+#pragma unroll 4
+            for (int s = 0; s < S; ++s) v[0] += dr[(size_t)s * delta_stride + i];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            row_buf[i + e] = v[e];
+            ss = fmaf(v[e], v[e], ss);
+        }
+        if (!rows && S > 0) {
+            if (VEC == 4) *reinterpret_cast<float4*>(xr + i) = make_float4(v[0], v[1], v[2], v[3]);
+            else xr[i] = v[0];
+        }
     }
     ss = ap_block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
     TO* o = out + (size_t)r * H;
-    for (int i = threadIdx.x; i < H; i += NORM_THREADS)
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
         o[i] = ap_from_float<TO>(row_buf[i] * inv * ap_to_float(w[i]));
 }
 
@@ -77,13 +96,18 @@ template <typename TW, typename TO>
 static int launch_add_rmsnorm(float* x, const float* delta, int S, size_t delta_stride, const void* w,
                               float eps, void* out, const int* rows, int R, int H, cudaStream_t stream) {
     const size_t smem = (size_t)H * sizeof(float);
-    auto kern = add_rmsnorm_kernel<TW, TO>;
+    const bool vec = (H % 4 == 0) && (((uintptr_t)x & 15) == 0) && (((uintptr_t)delta & 15) == 0) &&
+                     (delta_stride % 4 == 0);
+    auto kern = vec ? add_rmsnorm_kernel<TW, TO, 4> : add_rmsnorm_kernel<TW, TO, 1>;
     if (smem > 48 * 1024) {
         AP_REQUIRE(smem <= 200 * 1024, "rmsnorm: width %d does not fit the shared-memory row buffer", H);
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         AP_REQUIRE(e == cudaSuccess, "rmsnorm: cannot reserve %zu bytes of shared memory", smem);
     }
-    kern<<<R, NORM_THREADS, smem, stream>>>(x, delta, S, delta_stride, (const TW*)w, eps, (TO*)out, rows, H);
+    const int per = vec ? 4 : 1;
+    int threads = ((H + per - 1) / per + 31) / 32 * 32;
+    threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+    kern<<<R, threads, smem, stream>>>(x, delta, S, delta_stride, (const TW*)w, eps, (TO*)out, rows, H);
     AP_CHECK_LAUNCH("add_rmsnorm");
     return AP_OK;
 }
@@ -135,80 +159,99 @@ AP_EXPORT int ap_residual_add(float* x, const float* delta, int S, long long del
 //   q_out: [T, nh*hd]
 //   cache (one layer): [page][2][nkv][P][hd]; the page of a row is
 //       block_table[token_seq[t]][pos / P], its slot pos % P; cache == nullptr: store nothing
-//   inv_freq: [hd/2] 32-bit table, or nullptr for no rotation
+//   cos_sin: [T][hd/2] (cos, sin) pairs from rope_table_kernel, or nullptr for no rotation
 //   pairing 0: pairs (i, i + hd/2)   (checkpoints in the Hugging Face layout)
 //   pairing 1: pairs (2i, 2i + 1)    (checkpoints whose Q/K rows were permuted)
 // ---------------------------------------------------------------------------
 template <typename TI>
 __device__ __forceinline__ float load_partial(const TI* in, int S, size_t stride, size_t idx) {
     float v = ap_to_float(in[idx]);
+#pragma unroll 4
     for (int s = 1; s < S; ++s) v += ap_to_float(in[(size_t)s * stride + idx]);
     return v;
 }
 
+// cos and sin of pos * inv_freq[i] for every row of the step, computed once and shared by
+// all layers with the same rotation: table[t][i] = (cos, sin).  The angle is a 32-bit
+// product; sincosf is the accurate (not the fast-math) routine.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ table, int half) {
+    const int t = blockIdx.x;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf(pos * inv_freq[i], &sn, &cs);
+        table[(size_t)t * half + i] = make_float2(cs, sn);
+    }
+}
+
+AP_EXPORT int ap_rope_table(const int* positions, const float* inv_freq, float* table, int T, int half,
+                            cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && half > 0, "rope_table: bad sizes T=%d half=%d", T, half);
+    if (T == 0) return AP_OK;
+    rope_table_kernel<<<T, half < 128 ? 64 : 128, 0, stream>>>(positions, inv_freq, (float2*)table, half);
+    AP_CHECK_LAUNCH("rope_table");
+    return AP_OK;
+}
+
+// One thread per pair of elements: (nh + nkv) * half rotated pairs, then nkv * half pairs of V.
+#define ROPE_THREADS 256
 template <typename TI, typename TO>
-__global__ void rope_kv_store_kernel(const TI* __restrict__ in, int S, size_t in_stride,
-                                     TO* __restrict__ q_out, TO* __restrict__ cache,
-                                     const int* __restrict__ positions,
-                                     const int* __restrict__ token_seq,
-                                     const int* __restrict__ block_table, int max_blocks,
-                                     const float* __restrict__ inv_freq, int pairing,
-                                     int nh, int nkv, int hd, int P, size_t page_stride) {
+__global__ void __launch_bounds__(ROPE_THREADS)
+rope_kv_store_kernel(const TI* __restrict__ in, int S, size_t in_stride,
+                     TO* __restrict__ q_out, TO* __restrict__ cache,
+                     const int* __restrict__ positions,
+                     const int* __restrict__ token_seq,
+                     const int* __restrict__ block_table, int max_blocks,
+                     const float2* __restrict__ cos_sin, int pairing,
+                     int nh, int nkv, int hd, int P, size_t page_stride) {
     const int t = blockIdx.x;
     const int half = hd >> 1;
-    const int width = (nh + 2 * nkv) * hd;
-    const size_t row = (size_t)t * width;
-    const int ipos = positions[t];
-    const float pos = (float)ipos;
+    const int item = blockIdx.y * ROPE_THREADS + threadIdx.x;
+    const int rot_pairs = (nh + nkv) * half;
+    const int v_pairs = cache ? nkv * half : 0;
+    if (item >= rot_pairs + v_pairs) return;
+    const size_t row = (size_t)t * (nh + 2 * nkv) * hd;
     int page = -1, off = 0;
     if (cache) {
+        const int ipos = positions[t];
         page = block_table[(size_t)token_seq[t] * max_blocks + ipos / P];
         off = ipos % P;
     }
-    const int slot = page;   // < 0: this row stores nothing
-    const int rot_pairs = (nh + nkv) * half;
-    for (int p = threadIdx.x; p < rot_pairs; p += blockDim.x) {
-        const int head = p / half, i = p - head * half;
+    if (item < rot_pairs) {
+        const int head = item / half, i = item - head * half;
+        if (head >= nh && page < 0) return;
         const int ia = pairing == 0 ? i : 2 * i;
         const int ib = pairing == 0 ? i + half : 2 * i + 1;
         const size_t base = row + (size_t)head * hd;
         // partial sums are rounded to the storage type once they are complete
-        float a = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + ia)));
-        float b = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + ib)));
+        const float a = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + ia)));
+        const float b = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + ib)));
         float ra = a, rb = b;
-        if (inv_freq) {
-            float sn, cs;
-            sincosf(pos * inv_freq[i], &sn, &cs);
-            ra = a * cs - b * sn;
-            rb = a * sn + b * cs;
+        if (cos_sin) {
+            const float2 cs = cos_sin[(size_t)t * half + i];
+            ra = a * cs.x - b * cs.y;
+            rb = a * cs.y + b * cs.x;
         }
-        if (head < nh) {
-            TO* q = q_out + (size_t)t * nh * hd + (size_t)head * hd;
-            q[ia] = ap_from_float<TO>(ra);
-            q[ib] = ap_from_float<TO>(rb);
-        } else if (slot >= 0) {
-            const int kh = head - nh;
-            TO* k = cache + (size_t)page * page_stride + ((size_t)kh * P + off) * hd;
-            k[ia] = ap_from_float<TO>(ra);
-            k[ib] = ap_from_float<TO>(rb);
-        }
-    }
-    if (slot >= 0) {
-        const int nv = nkv * hd;
-        const size_t vbase = row + (size_t)(nh + nkv) * hd;
-        for (int e = threadIdx.x; e < nv; e += blockDim.x) {
-            const int kh = e / hd, d = e - kh * hd;
-            const float v = load_partial(in, S, in_stride, vbase + e);
-            cache[(size_t)page * page_stride + (size_t)nkv * P * hd + ((size_t)kh * P + off) * hd + d] =
-                ap_from_float<TO>(v);
-        }
+        TO* dst = head < nh ? q_out + (size_t)t * nh * hd + (size_t)head * hd
+                            : cache + (size_t)page * page_stride + ((size_t)(head - nh) * P + off) * hd;
+        dst[ia] = ap_from_float<TO>(ra);
+        dst[ib] = ap_from_float<TO>(rb);
+    } else if (page >= 0) {
+        const int e = (item - rot_pairs) * 2;              // hd is even: a pair never straddles heads
+        const int kh = e / hd, d = e - kh * hd;
+        const size_t vbase = row + (size_t)(nh + nkv) * hd + e;
+        TO* dst = cache + (size_t)page * page_stride + (size_t)nkv * P * hd + ((size_t)kh * P + off) * hd + d;
+        dst[0] = ap_from_float<TO>(load_partial(in, S, in_stride, vbase));
+        dst[1] = ap_from_float<TO>(load_partial(in, S, in_stride, vbase + 1));
     }
 }
 
 AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in_stride, void* q_out,
                                void* cache, int act_dtype, const int* positions, const int* token_seq,
-                               const int* block_table, int max_blocks, const float* inv_freq, int pairing, int T, int nh, int nkv, int hd, int P,
-                               long long page_stride, cudaStream_t stream) {
+                               const int* block_table, int max_blocks, const float* cos_sin, int pairing,
+                               int T, int nh, int nkv, int hd, int P, long long page_stride,
+                               cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && nh > 0 && nkv >= 0 && hd > 0 && (hd % 2) == 0 && S >= 1,
                "rope_kv_store: bad sizes T=%d heads=%d kv_heads=%d head_dim=%d S=%d", T, nh, nkv, hd, S);
     AP_REQUIRE(pairing == 0 || pairing == 1, "rope_kv_store: unknown pairing %d", pairing);
@@ -217,12 +260,13 @@ AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in
     AP_REQUIRE(cache == nullptr || (token_seq && block_table && max_blocks > 0),
                "rope_kv_store: storing needs the block table and the rows' sequences");
     if (T == 0) return AP_OK;
-    const int threads = 128;
+    const int items = (nh + nkv) * (hd / 2) + (cache ? nkv * (hd / 2) : 0);
+    dim3 grid(T, (items + ROPE_THREADS - 1) / ROPE_THREADS);
+    AP_REQUIRE(grid.y <= 65535, "rope_kv_store: too many heads for the grid");
 #define LAUNCH(TI, TO)                                                                              \
-    rope_kv_store_kernel<TI, TO><<<T, threads, 0, stream>>>(                                        \
+    rope_kv_store_kernel<TI, TO><<<grid, ROPE_THREADS, 0, stream>>>(                                \
         (const TI*)in, S, (size_t)in_stride, (TO*)q_out, (TO*)cache, positions, token_seq,         \
-        block_table, max_blocks, inv_freq,                                                          \
-        pairing, nh, nkv, hd, P, (size_t)page_stride)
+        block_table, max_blocks, (const float2*)cos_sin, pairing, nh, nkv, hd, P, (size_t)page_stride)
     if (in_dtype == AP_F32 && act_dtype == AP_F32) LAUNCH(float, float);
     else if (in_dtype == AP_F32 && act_dtype == AP_BF16) LAUNCH(float, bf16);
     else if (in_dtype == AP_BF16 && act_dtype == AP_BF16) {

@@ -44,5 +44,6 @@ class StepBatch:
     host_query_lens: List[int] = field(default_factory=list)
     host_first_position: List[int] = field(default_factory=list)
     host_state_slots: List[int] = field(default_factory=list)
+    shared: dict = field(default_factory=dict)    # per-step values parts share (cleared per forward)
     max_query_len: int = 0
     max_context_len: int = 0

@@ -22,6 +22,7 @@ from ..config import EngineConfig
 from ..models import DecoderModel, load_config
 from ..parts import BuildEnv, Workspace
 from ..weights import load_checkpoint
+from ..ops import library
 from .batch import BatchEntry, StepBatch
 
 
@@ -49,6 +50,7 @@ class ModelRunner:
             load_checkpoint(model, model_path, engine.dtype, self.device)
             model_config = cfg
         self.model = model
+        self.workspace = model.env.workspace      # the buffers the model's parts use
         self.model_config = model_config
         self.vocab_size = model.spec.vocab_size
         self.max_model_len = engine.max_model_len or model.spec.max_position_embeddings
@@ -56,6 +58,7 @@ class ModelRunner:
         self._staging_cap = 0
         self._host = None
         self._dev = None
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
 
     # ---- caches ---------------------------------------------------------
     def _setup_caches(self) -> None:
@@ -111,14 +114,55 @@ class ModelRunner:
         """Run the rows of ``entries`` as one batch; returns ``[wanted, vocab]`` float32 logits
         in the order of the entries and of their ``want`` lists.  The tensor is a view of a
         buffer that the next step overwrites."""
-        batch = self.prepare(entries)
-        logits = self.model.forward(batch)
+        if self._graphable(entries):
+            logits = self._graph_step(entries)
+        else:
+            batch = self.prepare(entries)
+            logits = self.model.forward(batch)
         for en in entries:
             self.cache.release_passed(en.request)
         return logits
 
-    def prepare(self, entries: Sequence[BatchEntry]) -> StepBatch:
-        """Check the batch, allocate its pages and upload its metadata."""
+    # ---- decode steps as CUDA graphs ------------------------------------
+    def _graphable(self, entries: Sequence[BatchEntry]) -> bool:
+        """A pure decode step (one row per request, every row's logits wanted) of a size
+        graphs are kept for."""
+        return (self.engine.use_cuda_graphs and 0 < len(entries) <= self.engine.max_num_seqs
+                and all(len(en.tokens) == 1 and list(en.want) == [0] for en in entries))
+
+    def _graph_step(self, entries: Sequence[BatchEntry]) -> torch.Tensor:
+        """Replay (or first capture) the graph of a decode step with ``len(entries)`` rows.
+
+        The graph's kernels read their metadata from buffers at fixed addresses with a
+        block-table row as wide as the longest sequence the model takes, so only the
+        contents change between replays.  A graph is captured again when a workspace
+        buffer it points to has been replaced."""
+        B = len(entries)
+        gs = self._graphs.get(B)
+        if gs is None:
+            gs = self._graphs[B] = _DecodeGraph(self, B)
+        batch = self.prepare(entries, staging=gs, widths=gs.widths)
+        batch.max_context_len = self.max_model_len       # fixes the number of key slices
+        if gs.graph is not None and gs.generation == self.workspace.generation:
+            gs.graph.replay()
+            library.add_launches(gs.num_kernels)
+            return gs.logits
+        # first use (or buffers moved): run eagerly, which also sizes every buffer, then record
+        logits = self.model.forward(batch)
+        torch.cuda.current_stream().synchronize()
+        before = library.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            gs.logits = self.model.forward(batch)
+        gs.num_kernels = library.launch_count() - before
+        library.add_launches(-gs.num_kernels)            # recorded, not run
+        gs.graph = graph
+        gs.generation = self.workspace.generation
+        return logits
+
+    def prepare(self, entries: Sequence[BatchEntry], staging=None, widths=None) -> StepBatch:
+        """Check the batch, allocate its pages and upload its metadata (into ``staging``'s
+        fixed buffers with the given block-table widths, when given)."""
         if not entries:
             raise StepError("a step needs at least one entry")
         seen = set()
@@ -156,10 +200,16 @@ class ModelRunner:
             firsts.append(self.cache.append(en.request, len(en.tokens)))
 
         groups = range(len(self.cache.groups))
-        widths = [max(len(self.cache.block_table(en.request, g)) for en in entries) for g in groups]
+        if widths is None:
+            widths = [max(len(self.cache.block_table(en.request, g)) for en in entries) for g in groups]
         R = sum(len(en.want) for en in entries)
         total = 3 * T + (nseq + 1) + 2 * nseq + R + sum(nseq * w for w in widths)
-        host, dev = self._staging(total)
+        if staging is None:
+            host, dev = self._staging(total)
+            host_tensor, copied = self._host_tensor, self._copied
+        else:
+            staging.copied.synchronize()
+            host, dev, host_tensor, copied = staging.host, staging.dev, staging.host_tensor, staging.copied
         o = 0
 
         def region(n):
@@ -197,8 +247,8 @@ class ModelRunner:
             max_ctx = max(max_ctx, firsts[s] + n)
         host[r_start[0]:r_start[1]] = np.asarray(starts, dtype=np.int32)
 
-        dev[:total].copy_(self._host_tensor[:total], non_blocking=True)
-        self._copied.record()
+        dev[:total].copy_(host_tensor[:total], non_blocking=True)
+        copied.record()
 
         def view(r):
             return dev[r[0]:r[1]]
@@ -232,3 +282,20 @@ class ModelRunner:
     def memory_report(self) -> Dict[str, int]:
         return {"cache_bytes": sum(s.bytes() for s in self.storages),
                 "workspace_bytes": self.workspace.bytes(), "num_pages": self.num_pages}
+
+
+class _DecodeGraph:
+    """Fixed metadata buffers and the captured graph of a decode step with ``B`` rows."""
+
+    def __init__(self, runner: ModelRunner, B: int):
+        self.widths = [-(-runner.max_model_len // g.page_size) for g in runner.cache.groups]
+        total = 3 * B + (B + 1) + 2 * B + B + sum(B * w for w in self.widths)
+        self.host_tensor = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        self.host = self.host_tensor.numpy()
+        self.dev = torch.empty(total, dtype=torch.int32, device=runner.device)
+        self.copied = torch.cuda.Event()
+        self.copied.record()
+        self.graph = None
+        self.logits = None
+        self.generation = -1
+        self.num_kernels = 0

@@ -129,6 +129,7 @@ class DecoderModel:
         T = step.num_tokens
         ws = self.env.workspace
         s = self.spec
+        step.shared.clear()
         x = ws.get("model.residual", (T, s.hidden_size), torch.float32)
         ops.embed_gather(step.token_ids, self.embedding, x)
         delta = None

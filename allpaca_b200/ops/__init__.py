@@ -101,13 +101,13 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
 
 def rope_kv_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[torch.Tensor],
                   positions: torch.Tensor, token_seq: Optional[torch.Tensor],
-                  block_table: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
+                  block_table: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
                   pairing: int, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
     """Rotate Q and K of ``qkv [T, (nh+2nkv)*hd]`` and store K, V into cache pages.
 
     ``cache_layer`` is one layer's pages ``[pages, 2, nkv, P, hd]``; a row's page is
-    ``block_table[token_seq[t], pos // P]`` and its slot ``pos % P``.  ``inv_freq`` None: no
-    rotation.  With ``cache_layer`` None nothing is stored; with ``num_kv_heads`` 0 the input
+    ``block_table[token_seq[t], pos // P]`` and its slot ``pos % P``.  ``cos_sin`` is the
+    ``[T, hd/2, 2]`` table of :func:`rope_table`; None: no rotation.  With ``cache_layer`` None nothing is stored; with ``num_kv_heads`` 0 the input
     holds queries only.
     """
     ptr, code, S, stride, T, N = _partials(qkv, "qkv")
@@ -130,14 +130,26 @@ def rope_kv_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[
         _check(token_seq, "token_seq", torch.int32, 1)
         _check(block_table, "block_table", torch.int32, 2)
         tsptr, btptr, maxb = token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1]
-    if inv_freq is not None:
-        _check(inv_freq, "inv_freq", torch.float32, 1)
-        if inv_freq.shape[0] != head_dim // 2:
-            raise KernelError("rope_kv_store: inv_freq must have head_dim/2 entries")
+    if cos_sin is not None:
+        _check(cos_sin, "cos_sin", torch.float32, 3)
+        if cos_sin.shape[0] < T or tuple(cos_sin.shape[1:]) != (head_dim // 2, 2):
+            raise KernelError("rope_kv_store: cos_sin must be [T, head_dim/2, 2]")
     call(core(), "ap_rope_kv_store", ptr, code, S, stride, q_out.data_ptr(), cptr,
          dtype_code(q_out.dtype), positions.data_ptr(), tsptr, btptr, maxb,
-         inv_freq.data_ptr() if inv_freq is not None else 0, int(pairing), T, num_heads,
+         cos_sin.data_ptr() if cos_sin is not None else 0, int(pairing), T, num_heads,
          num_kv_heads, head_dim, P, page_stride, stream_handle())
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor) -> None:
+    """``table[t, i] = (cos, sin)(positions[t] * inv_freq[i])`` with a 32-bit angle."""
+    _check(positions, "positions", torch.int32, 1)
+    _check(inv_freq, "inv_freq", torch.float32, 1)
+    _check(table, "table", torch.float32, 3)
+    T, half = positions.shape[0], inv_freq.shape[0]
+    if tuple(table.shape) != (T, half, 2):
+        raise KernelError("rope_table: table must be [T, head_dim/2, 2]")
+    call(core(), "ap_rope_table", positions.data_ptr(), inv_freq.data_ptr(), table.data_ptr(), T, half,
+         stream_handle())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:

@@ -26,6 +26,7 @@ _CORE_SIGNATURES = {
     "ap_add_rmsnorm": [_P, _P, _I, _L, _P, _I, _F, _P, _I, _P, _I, _I, _P],
     "ap_residual_add": [_P, _P, _I, _L, _L, _P],
     "ap_rope_kv_store": [_P, _I, _I, _L, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _L, _P],
+    "ap_rope_table": [_P, _P, _P, _I, _I, _P],
     "ap_swiglu": [_P, _I, _I, _L, _P, _I, _I, _I, _P],
     "ap_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "ap_argmax": [_P, _L, _I, _I, _P, _P],
@@ -128,3 +129,9 @@ _launches = 0
 def launch_count() -> int:
     """Calls into the kernel libraries so far (each launches one kernel)."""
     return _launches
+
+
+def add_launches(n: int) -> None:
+    """Account for kernels launched by replaying a captured graph."""
+    global _launches
+    _launches += n

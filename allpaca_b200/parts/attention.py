@@ -77,7 +77,7 @@ class GroupedQueryAttention(Mixer):
         ws = self.env.workspace
         qkv = self.qkv.forward(h, "attn.qkv", "either")
         q = ws.get("attn.q", (T, self.q_size), self.env.dtype)
-        table = self.position.rotary_table() if self.position is not None else None
+        table = self.position.rotation_for(step) if self.position is not None else None
         writes = cache.writes and not self.shares_kv
         if self.position is not None and table is None:
             # an encoding that is not a plain rotation: let it act on views, then store
@@ -86,10 +86,10 @@ class GroupedQueryAttention(Mixer):
             kv = qkv[:, self.q_size:self.q_size + self.kv_size].unflatten(1, (-1, self.hd)) \
                 if self.kv_size else None
             self.position.apply(qv, kv, step.positions)
-        inv_freq, pairing = table if table is not None else (None, 0)
+        cos_sin, pairing = table if table is not None else (None, 0)
         ops.rope_kv_store(
             qkv, q, cache.kv if writes else None, step.positions, step.token_seq,
-            step.block_tables[cache.group] if writes else None, inv_freq, pairing,
+            step.block_tables[cache.group] if writes else None, cos_sin, pairing,
             self.nh, self.nkv if not self.shares_kv else 0, self.hd)
         attn = ws.get("attn.out", (T, self.q_size), self.env.dtype)
         ops.attention(q, attn, cache.kv, step.block_tables[cache.group], step.token_seq,

@@ -85,6 +85,7 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._buffers: Dict[str, torch.Tensor] = {}
+        self.generation = 0          # grows whenever a buffer is replaced (its address changes)
 
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -96,6 +97,7 @@ class Workspace:
             grow = max(n, 1)
             buf = torch.empty(grow, dtype=dtype, device=self.device)
             self._buffers[key] = buf
+            self.generation += 1
         return buf[:n].view(*shape)
 
     def bytes(self) -> int:
@@ -168,12 +170,13 @@ class Norm(Part):
 class PositionEncoding(Part):
     """Injects positions into queries and keys.
 
-    ``rotary_table()`` returns ``(inv_freq [head_dim/2] float32, pairing)`` when the encoding is
-    a rotation the fused rotate-and-store kernel can apply, else None; then ``apply`` is called
-    on ``q [T, heads, hd]`` and ``k [T, kv_heads, hd]`` views in place before keys are stored.
+    ``rotation_for(step)`` returns ``(cos_sin [T, head_dim/2, 2] float32, pairing)`` when the
+    encoding is a rotation the fused rotate-and-store kernel can apply, else None; then
+    ``apply`` is called on ``q [T, heads, hd]`` and ``k [T, kv_heads, hd]`` views in place
+    before keys are stored.
     """
 
-    def rotary_table(self):
+    def rotation_for(self, step):
         return None
 
     def apply(self, q, k, positions) -> None:

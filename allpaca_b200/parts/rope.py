@@ -13,7 +13,7 @@ model.rs:181-274).  With ``factor f``, ``low_freq_factor lo``, ``high_freq_facto
 are blended with weight ``s = (n0/wavelength - lo) / (hi - lo)``.
 
 The table of frequencies is computed once in float64 and kept in float32; the angle is a
-32-bit product formed in the kernel that rotates and stores.
+32-bit product, and its cosine and sine are computed once per step for all layers.
 """
 from __future__ import annotations
 
@@ -22,6 +22,7 @@ from typing import Mapping, Optional
 
 import torch
 
+from .. import ops
 from .base import BuildEnv, PartError, PositionEncoding, register
 
 PAIRING = {"half": 0, "adjacent": 1}
@@ -69,5 +70,17 @@ class RotaryEmbedding(PositionEncoding):
         self.inv_freq = inverse_frequencies(self.head_dim, float(params["theta"]), scaling) \
             .to(torch.float32).to(env.device)
 
-    def rotary_table(self):
-        return self.inv_freq, self.pairing
+        self._key = ("rope", self.head_dim, float(params["theta"]), self.pairing,
+                     tuple(sorted(scaling.items())) if scaling else None)
+
+    def rotation_for(self, step):
+        """``([T, head_dim/2, 2] cos/sin of this step's positions, pairing)``; layers with the
+        same rotation share one table per step."""
+        table = step.shared.get(self._key)
+        if table is None:
+            T = step.num_tokens
+            table = self.env.workspace.get(f"rope.table.{len(step.shared)}",
+                                           (T, self.head_dim // 2, 2), torch.float32)
+            ops.rope_table(step.positions, self.inv_freq, table)
+            step.shared[self._key] = table
+        return table, self.pairing

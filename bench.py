@@ -126,6 +126,7 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--seed", type=int, default=2)
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profilers)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -161,7 +162,8 @@ def main() -> int:
     engine = EngineConfig(dtype="bfloat16", page_size=args.page_size,
                           max_cache_tokens=max_batch * (args.context + args.page_size) + args.prefill_tokens + 64,
                           max_num_seqs=max_batch, max_num_batched_tokens=max(args.prefill_tokens, max_batch),
-                          prefill_chunk=args.prefill_tokens, max_model_len=max_len, seed=args.seed)
+                          prefill_chunk=args.prefill_tokens, max_model_len=max_len, seed=args.seed,
+                          use_cuda_graphs=not args.no_graphs)
     engine.validate()
     env = BuildEnv(dtype=engine.dtype, device=device, workspace=Workspace(device),
                    page_size=engine.page_size, max_seqs=engine.max_num_seqs)

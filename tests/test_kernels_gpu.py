@@ -99,8 +99,10 @@ def test_rope_kv_store(ops, dtype, nh, nkv, hd, P):
     cache = torch.zeros(n_pages, 2, nkv, P, hd, dtype=dtype)
     cd = dev(cache)
     q_out = torch.empty(T, nh * hd, dtype=dtype, device="cuda")
+    cos_sin = torch.empty(T, hd // 2, 2, device="cuda")
+    ops.rope_table(dev(positions), dev(inv.float()), cos_sin)
     ops.rope_kv_store(dev(inp), q_out, cd, dev(positions), dev(token_seq), dev(table),
-                      dev(inv.float()), 0, nh, nkv, hd)
+                      cos_sin, 0, nh, nkv, hd)
     full = (qkv.sum(0) if dtype == torch.float32 else inp.float()).double()
     q = full[:, :nh * hd].view(T, nh, hd)
     k = full[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
@@ -128,7 +130,9 @@ def test_rope_adjacent_pairing_and_no_rotation(ops):
     positions = torch.tensor([0, 5, 9], dtype=torch.int32)
     inv = plain_llama.rope_inverse_frequencies(hd, 10000.0, None)
     out = torch.empty(T, nh * hd, device="cuda")
-    ops.rope_kv_store(dev(x), out, None, dev(positions), None, None, dev(inv.float()), 1, nh, 0, hd)
+    cos_sin = torch.empty(T, hd // 2, 2, device="cuda")
+    ops.rope_table(dev(positions), dev(inv.float()), cos_sin)
+    ops.rope_kv_store(dev(x), out, None, dev(positions), None, None, cos_sin, 1, nh, 0, hd)
     xv = x.double().view(T, nh, hd // 2, 2)
     ang = positions.double()[:, None] * inv[None, :]
     c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
