@@ -534,3 +534,75 @@ AP_EXPORT int ap_attention_tc_tokens_per_tile(int nh, int nkv) {
     const int hc = reps < 64 ? reps : 64;
     return 64 / hc;
 }
+
+// ---------------------------------------------------------------------------
+// The split kernel for callers that cannot allocate: its scratch is a fixed array in this
+// library (see attention_noalloc.h for who needs this and what they must observe).
+// ---------------------------------------------------------------------------
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float g_static_scratch[AP_ATTENTION_STATIC_SCRATCH_FLOATS];
+
+#define AP_MAX_DEVICES 64
+// Device address of g_static_scratch per device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use, so the address is looked up.
+static float* g_static_scratch_addr[AP_MAX_DEVICES];
+
+AP_EXPORT int ap_attention_decode_static(const void* q, void* out, const void* cache, const int* block_table,
+                                         int max_blocks, const int* positions, int T, int num_heads,
+                                         int num_kv_heads, int head_dim, int page_size, long long page_stride,
+                                         float scale, int window, int nsplit, cudaStream_t stream) {
+    AP_REQUIRE(head_dim == HD, "attention: this library was compiled for head size %d, not %d", HD, head_dim);
+    AP_REQUIRE(T >= 0 && num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && page_size > 0 &&
+                   max_blocks > 0 && nsplit >= 1 && nsplit <= 65535,
+               "attention: bad sizes T=%d heads=%d kv_heads=%d page=%d slices=%d", T, num_heads, num_kv_heads,
+               page_size, nsplit);
+    if (T == 0) return AP_OK;
+    const long long need = nsplit > 1 ? (long long)nsplit * T * num_heads * (HD + 2) : 0;
+    AP_REQUIRE(need <= AP_ATTENTION_STATIC_SCRATCH_FLOATS,
+               "attention: %d slices of %d rows x %d heads need %lld floats of scratch, the built-in array "
+               "holds %d; use fewer slices or the entry point that takes scratch from the caller",
+               nsplit, T, num_heads, need, AP_ATTENTION_STATIC_SCRATCH_FLOATS);
+    int device = -1;
+    AP_REQUIRE(cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < AP_MAX_DEVICES,
+               "attention: cannot tell the current device");
+    if (!g_static_scratch_addr[device]) {
+        // first call on this device: not inside a stream capture, please
+        float* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+        AP_REQUIRE(e == cudaSuccess && p != nullptr, "attention: cannot find the built-in scratch array: %s",
+                   cudaGetErrorString(e));
+        const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
+        const int smem_bytes = SmemLayout::kTotal > merge_bytes ? SmemLayout::kTotal : merge_bytes;
+        int rc = configure_smem((const void*)attention_split_kernel, smem_bytes);
+        if (rc != AP_OK) return rc;
+        g_static_scratch_addr[device] = p;
+    }
+    float* scratch = g_static_scratch_addr[device];
+    const int reps = num_heads / num_kv_heads;
+    AttnTcParams p;
+    p.q = (const bf16*)q; p.out = (bf16*)out; p.cache = (const bf16*)cache;
+    p.block_table = block_table; p.seq_start = nullptr; p.positions = positions;
+    p.part_o = scratch;
+    p.part_ml = scratch + (size_t)nsplit * T * num_heads * HD;
+    p.page_stride = (size_t)page_stride;
+    p.max_blocks = max_blocks; p.nseq = T; p.T = T; p.nh = num_heads; p.nkv = num_kv_heads; p.P = page_size;
+    p.window = window; p.scale_log2 = scale * LOG2E;
+    p.heads_per_chunk = reps < 16 ? reps : 16;
+    p.n_chunks = (reps + p.heads_per_chunk - 1) / p.heads_per_chunk;
+    p.tokens_per_tile = 1;
+    p.nsplit = nsplit;
+    AP_REQUIRE(num_kv_heads * p.n_chunks <= 65535, "attention: too many KV heads for the grid");
+    const int merge_bytes = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
+    const int smem_bytes = SmemLayout::kTotal > merge_bytes ? SmemLayout::kTotal : merge_bytes;
+    dim3 grid(T, num_kv_heads * p.n_chunks, nsplit);
+    attention_split_kernel<<<grid, ATC_THREADS, smem_bytes, stream>>>(p);
+    AP_CHECK_LAUNCH("attention_split (built-in scratch)");
+    if (nsplit > 1) {
+        dim3 mgrid(T, num_heads);
+        attention_merge_kernel<<<mgrid, HD < 128 ? 64 : 128, 0, stream>>>(p.part_o, p.part_ml, (bf16*)out, T,
+                                                                           num_heads, nsplit);
+        AP_CHECK_LAUNCH("attention_merge (built-in scratch)");
+    }
+    return AP_OK;
+}
