@@ -84,7 +84,8 @@ def random_tensor(name: str, spec: WeightSpec, seed: int, dtype: torch.dtype,
     """One tensor drawn from the generator keyed by ``(seed, name)`` on ``device``."""
     gen = torch.Generator(device=device)
     gen.manual_seed(_seed_for(seed, name))
-    t = torch.empty(spec.shape, dtype=torch.float32 if device.type == "cpu" else dtype, device=device)
+    # always drawn in 32-bit, then rounded: the bfloat16 model is the rounding of the 32-bit one
+    t = torch.empty(spec.shape, dtype=torch.float32, device=device)
     if spec.role == "norm":
         if norm_std > 0:
             t.normal_(0.0, norm_std, generator=gen).add_(1.0)

@@ -1,0 +1,76 @@
+"""Two layers of the Llama-3.1-8B shape in true 32-bit against the plain implementation, whole
+and cut into portions; and bfloat16 on the same weights (the sizes the benchmark runs)."""
+import pytest
+import torch
+
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+
+
+def test_two_layers_of_the_8b_shape(tmp_path):
+    from allpaca_b200.config import EngineConfig
+    from allpaca_b200.config.presets import preset_config
+    from allpaca_b200.engine.batch import BatchEntry
+    from allpaca_b200.engine.runner import ModelRunner
+    from allpaca_b200.parts import BuildEnv, Workspace
+    from allpaca_b200.weights.random_model import random_model_on_device
+
+    raw = preset_config("llama-3.1-8b")
+    raw["num_hidden_layers"] = 2
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(0)
+    tokens = torch.randint(0, raw["vocab_size"], (150,), generator=g).tolist()
+    want_rows = [0, 1, 63, 64, 127, 128, 149]
+    w = None
+    for dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 3e-2)):
+        env = BuildEnv(dtype, dev, Workspace(dev), page_size=16, max_seqs=2)
+        cfg, model = random_model_on_device(raw, 2, env)
+        if w is None:
+            # weights are drawn on the GPU in 32-bit (bfloat16 is their rounding): the plain
+            # implementation gets the same ones
+            w = {}
+            for block, prefix in zip(model.blocks, model.spec.layer_prefixes):
+                qkv = block.mixer.qkv.weight
+                Q, KV = cfg.q_size, cfg.kv_size
+                w[prefix + "self_attn.q_proj.weight"] = qkv[:Q]
+                w[prefix + "self_attn.k_proj.weight"] = qkv[Q:Q + KV]
+                w[prefix + "self_attn.v_proj.weight"] = qkv[Q + KV:]
+                w[prefix + "self_attn.o_proj.weight"] = block.mixer.o.weight
+                gu = block.feed_forward.gate_up.weight
+                w[prefix + "mlp.gate_proj.weight"] = gu[:cfg.intermediate_size]
+                w[prefix + "mlp.up_proj.weight"] = gu[cfg.intermediate_size:]
+                w[prefix + "mlp.down_proj.weight"] = block.feed_forward.down.weight
+                w[prefix + "input_layernorm.weight"] = block.mixer_norm.weight
+                w[prefix + "post_attention_layernorm.weight"] = block.feed_forward_norm.weight
+            w["model.embed_tokens.weight"] = model.embedding
+            w["lm_head.weight"] = model.head.weight
+            w["model.norm.weight"] = model.final_norm.weight
+            w = {k: v.cpu() for k, v in w.items()}
+        if dtype == torch.float32:
+            plain = plain_llama.llama_forward(raw, w, tokens, torch.float32)[want_rows].double()
+        else:
+            plain = plain_llama.llama_forward(raw, {k: v.bfloat16() for k, v in w.items()}, tokens,
+                                              torch.float32, round_to=torch.bfloat16)[want_rows].double()
+        runner = ModelRunner(None, EngineConfig(dtype=dtype, page_size=16, max_cache_tokens=512, max_num_seqs=2,
+                                                max_num_batched_tokens=256, use_cuda_graphs=False), model=model)
+        whole = runner.step([BatchEntry("w", tokens, want_rows)]).double().cpu()
+        err = float((whole - plain).abs().max() / plain.abs().max())
+        assert err < tol, (dtype, "whole", err)
+        # portions 64 + 1 + 63 + 22 beside a second request decoding
+        got = []
+        at = 0
+        for n in (64, 1, 63, 22):
+            want = [r - at for r in want_rows if at <= r < at + n]
+            entries = [BatchEntry("p", tokens[at:at + n], want)]
+            if at > 0:
+                entries.append(BatchEntry("other", tokens[at:at + 1], []))
+            else:
+                entries.append(BatchEntry("other", tokens[:9], []))
+            out = runner.step(entries)
+            got.append(out[:len(want)].double().cpu())
+            at += n
+        err = float((torch.cat(got) - plain).abs().max() / plain.abs().max())
+        assert err < tol, (dtype, "portions", err)
+        del runner, model
+        torch.cuda.empty_cache()
