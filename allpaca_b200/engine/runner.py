@@ -190,6 +190,10 @@ class ModelRunner:
         if T > self.engine.max_num_batched_tokens:
             raise StepError(f"{T} rows exceed max_num_batched_tokens {self.engine.max_num_batched_tokens}")
         if not self.can_run(entries):
+            new = sum(1 for en in entries if not self.cache.has(en.request))
+            if new > self.engine.max_num_seqs - self.cache.num_running():
+                raise OutOfPages(f"{new} new requests beside {self.cache.num_running()} running ones exceed "
+                                 f"max_num_seqs {self.engine.max_num_seqs}")
             raise OutOfPages("the cache pools cannot hold this step's tokens")
 
         nseq = len(entries)

@@ -57,6 +57,7 @@ def test_two_layers_of_the_8b_shape(tmp_path):
         whole = runner.step([BatchEntry("w", tokens, want_rows)]).double().cpu()
         err = float((whole - plain).abs().max() / plain.abs().max())
         assert err < tol, (dtype, "whole", err)
+        runner.finish("w")
         # portions 64 + 1 + 63 + 22 beside a second request decoding
         got = []
         at = 0
