@@ -42,6 +42,43 @@ void ap_set_error(const char* fmt, ...);
 
 typedef __nv_bfloat16 bf16;
 
+// ---- programmatic dependent launch ---------------------------------------------------
+// Kernels of the decode path are launched so that a kernel may start while the one before
+// it on the stream is still running.  Such a kernel does only work that depends on nothing
+// the earlier kernels write (set-up, prefetch of weights) until ap_pdl_wait() returns,
+// which is when every earlier kernel has finished and its writes are visible; and it calls
+// ap_pdl_trigger() once the kernel after it may start the same way.  Launched without the
+// attribute both are no-ops.
+__device__ __forceinline__ void ap_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void ap_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool ap_pdl_enabled();     // false when the environment sets ALLPACA_PDL=0
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ap_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ap_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#define AP_CHECK_PDL_LAUNCH(name, call)                                        \
+    do {                                                                       \
+        cudaError_t e__ = (call);                                              \
+        if (e__ != cudaSuccess) {                                              \
+            ap_set_error("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+            return AP_ERR_LAUNCH;                                              \
+        }                                                                      \
+    } while (0)
+
 __device__ __forceinline__ float ap_to_float(float v) { return v; }
 __device__ __forceinline__ float ap_to_float(bf16 v) { return __bfloat162float(v); }
 

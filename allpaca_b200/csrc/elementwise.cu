@@ -16,6 +16,8 @@ template <typename TW>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                                     float* __restrict__ x, int H, int V) {
     const int t = blockIdx.x;
+    ap_pdl_trigger();
+    ap_pdl_wait();
     int tok = tokens[t];
     // The host rejects tokens outside the vocabulary; the clamp keeps a corrupted
     // id from reading outside the table.
@@ -31,12 +33,13 @@ AP_EXPORT int ap_embed_gather(const int* tokens, const void* table, int table_dt
     if (T == 0) return AP_OK;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == AP_F32)
-        embed_gather_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, x, H, V);
+        AP_CHECK_PDL_LAUNCH("embed_gather", ap_launch_pdl(embed_gather_kernel<float>, dim3(T), dim3(threads), 0,
+                                                          stream, tokens, (const float*)table, x, H, V));
     else if (table_dtype == AP_BF16)
-        embed_gather_kernel<bf16><<<T, threads, 0, stream>>>(tokens, (const bf16*)table, x, H, V);
+        AP_CHECK_PDL_LAUNCH("embed_gather", ap_launch_pdl(embed_gather_kernel<bf16>, dim3(T), dim3(threads), 0,
+                                                          stream, tokens, (const bf16*)table, x, H, V));
     else
         AP_REQUIRE(false, "embed_gather: unknown table dtype %d", table_dtype);
-    AP_CHECK_LAUNCH("embed_gather");
     return AP_OK;
 }
 
@@ -56,6 +59,8 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int S
     extern __shared__ __align__(16) float row_buf[];
     __shared__ float red[32];
     const int r = blockIdx.x;
+    ap_pdl_trigger();
+    ap_pdl_wait();
     const int t = rows ? rows[r] : r;
     float* xr = x + (size_t)t * H;
     const float* dr = delta + (size_t)t * H;
@@ -88,6 +93,20 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int S
     ss = ap_block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
     TO* o = out + (size_t)r * H;
+    if (VEC == 4 && sizeof(TO) == 2 && sizeof(TW) == 2 && (((uintptr_t)o | (uintptr_t)w) & 7) == 0) {
+        // four bfloat16 results per thread in one 8-byte store
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row_buf + i);
+            const uint2 wv = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(w) + i);
+            const float2 w01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv.x));
+            const float2 w23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv.y));
+            uint2 ov;
+            *reinterpret_cast<__nv_bfloat162*>(&ov.x) = __floats2bfloat162_rn(v.x * inv * w01.x, v.y * inv * w01.y);
+            *reinterpret_cast<__nv_bfloat162*>(&ov.y) = __floats2bfloat162_rn(v.z * inv * w23.x, v.w * inv * w23.y);
+            *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(o) + i) = ov;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x)
         o[i] = ap_from_float<TO>(row_buf[i] * inv * ap_to_float(w[i]));
 }
@@ -107,8 +126,8 @@ static int launch_add_rmsnorm(float* x, const float* delta, int S, size_t delta_
     const int per = vec ? 4 : 1;
     int threads = ((H + per - 1) / per + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
-    kern<<<R, threads, smem, stream>>>(x, delta, S, delta_stride, (const TW*)w, eps, (TO*)out, rows, H);
-    AP_CHECK_LAUNCH("add_rmsnorm");
+    AP_CHECK_PDL_LAUNCH("add_rmsnorm", ap_launch_pdl(kern, dim3(R), dim3(threads), smem, stream, x, delta, S,
+                                                     delta_stride, (const TW*)w, eps, (TO*)out, rows, H));
     return AP_OK;
 }
 
@@ -177,6 +196,8 @@ __device__ __forceinline__ float load_partial(const TI* in, int S, size_t stride
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float2* __restrict__ table, int half) {
     const int t = blockIdx.x;
+    ap_pdl_trigger();
+    ap_pdl_wait();
     const float pos = (float)positions[t];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float sn, cs;
@@ -189,8 +210,8 @@ AP_EXPORT int ap_rope_table(const int* positions, const float* inv_freq, float* 
                             cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && half > 0, "rope_table: bad sizes T=%d half=%d", T, half);
     if (T == 0) return AP_OK;
-    rope_table_kernel<<<T, half < 128 ? 64 : 128, 0, stream>>>(positions, inv_freq, (float2*)table, half);
-    AP_CHECK_LAUNCH("rope_table");
+    AP_CHECK_PDL_LAUNCH("rope_table", ap_launch_pdl(rope_table_kernel, dim3(T), dim3(half < 128 ? 64 : 128), 0,
+                                                    stream, positions, inv_freq, (float2*)table, half));
     return AP_OK;
 }
 
@@ -208,6 +229,8 @@ rope_kv_store_kernel(const TI* __restrict__ in, int S, size_t in_stride,
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int item = blockIdx.y * ROPE_THREADS + threadIdx.x;
+    ap_pdl_trigger();
+    ap_pdl_wait();
     const int rot_pairs = (nh + nkv) * half;
     const int v_pairs = cache ? nkv * half : 0;
     if (item >= rot_pairs + v_pairs) return;
@@ -247,6 +270,63 @@ rope_kv_store_kernel(const TI* __restrict__ in, int S, size_t in_stride,
     }
 }
 
+// bfloat16, single input slice, half-split pairing: one thread rotates 8 pairs (elements
+// i..i+7 with i+half..i+half+7) or copies 8 elements of V, in 16-byte accesses.
+__global__ void __launch_bounds__(ROPE_THREADS)
+rope_kv_store_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ q_out, bf16* __restrict__ cache,
+                            const int* __restrict__ positions, const int* __restrict__ token_seq,
+                            const int* __restrict__ block_table, int max_blocks,
+                            const float2* __restrict__ cos_sin, int nh, int nkv, int hd, int P,
+                            size_t page_stride) {
+    const int t = blockIdx.x;
+    const int half = hd >> 1, h8 = half >> 3;             // groups of 8 pairs per head
+    const int item = blockIdx.y * ROPE_THREADS + threadIdx.x;
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    const int rot_items = (nh + nkv) * h8;
+    const int v_items = cache ? nkv * (hd >> 3) : 0;
+    if (item >= rot_items + v_items) return;
+    const size_t row = (size_t)t * (nh + 2 * nkv) * hd;
+    int page = -1, off = 0;
+    if (cache) {
+        const int ipos = positions[t];
+        page = block_table[(size_t)token_seq[t] * max_blocks + ipos / P];
+        off = ipos % P;
+    }
+    if (item < rot_items) {
+        const int head = item / h8, i = (item - head * h8) * 8;
+        if (head >= nh && page < 0) return;
+        const bf16* src = in + row + (size_t)head * hd;
+        const uint4 a4 = *reinterpret_cast<const uint4*>(src + i);
+        const uint4 b4 = *reinterpret_cast<const uint4*>(src + i + half);
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a4);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b4);
+        uint4 ra4 = a4, rb4 = b4;
+        if (cos_sin) {
+            __nv_bfloat162* ra2 = reinterpret_cast<__nv_bfloat162*>(&ra4);
+            __nv_bfloat162* rb2 = reinterpret_cast<__nv_bfloat162*>(&rb4);
+            const float4* cs = reinterpret_cast<const float4*>(cos_sin + (size_t)t * half + i);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float4 c = cs[k];                   // (cos, sin) of pairs 2k and 2k+1
+                const float2 a = __bfloat1622float2(a2[k]), b = __bfloat1622float2(b2[k]);
+                ra2[k] = __floats2bfloat162_rn(a.x * c.x - b.x * c.y, a.y * c.z - b.y * c.w);
+                rb2[k] = __floats2bfloat162_rn(a.x * c.y + b.x * c.x, a.y * c.w + b.y * c.z);
+            }
+        }
+        bf16* dst = head < nh ? q_out + (size_t)t * nh * hd + (size_t)head * hd
+                              : cache + (size_t)page * page_stride + ((size_t)(head - nh) * P + off) * hd;
+        *reinterpret_cast<uint4*>(dst + i) = ra4;
+        *reinterpret_cast<uint4*>(dst + i + half) = rb4;
+    } else if (page >= 0) {
+        const int e = (item - rot_items) * 8;
+        const int kh = e / hd, d = e - kh * hd;
+        const uint4 v4 = *reinterpret_cast<const uint4*>(in + row + (size_t)(nh + nkv) * hd + e);
+        *reinterpret_cast<uint4*>(cache + (size_t)page * page_stride + (size_t)nkv * P * hd +
+                                  ((size_t)kh * P + off) * hd + d) = v4;
+    }
+}
+
 AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in_stride, void* q_out,
                                void* cache, int act_dtype, const int* positions, const int* token_seq,
                                const int* block_table, int max_blocks, const float* cos_sin, int pairing,
@@ -260,13 +340,26 @@ AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in
     AP_REQUIRE(cache == nullptr || (token_seq && block_table && max_blocks > 0),
                "rope_kv_store: storing needs the block table and the rows' sequences");
     if (T == 0) return AP_OK;
+    if (in_dtype == AP_BF16 && act_dtype == AP_BF16 && S == 1 && pairing == 0 && hd % 16 == 0 &&
+        ((uintptr_t)in & 15) == 0 && ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)cache & 15) == 0 &&
+        page_stride % 8 == 0 && ((uintptr_t)cos_sin & 15) == 0) {
+        const int items8 = (nh + nkv) * (hd / 16) + (cache ? nkv * (hd / 8) : 0);
+        dim3 grid8(T, (items8 + ROPE_THREADS - 1) / ROPE_THREADS);
+        AP_REQUIRE(grid8.y <= 65535, "rope_kv_store: too many heads for the grid");
+        AP_CHECK_PDL_LAUNCH("rope_kv_store", ap_launch_pdl(
+            rope_kv_store_bf16x8_kernel, grid8, dim3(ROPE_THREADS), 0, stream, (const bf16*)in, (bf16*)q_out,
+            (bf16*)cache, positions, token_seq, block_table, max_blocks, (const float2*)cos_sin, nh, nkv, hd, P,
+            (size_t)page_stride));
+        return AP_OK;
+    }
     const int items = (nh + nkv) * (hd / 2) + (cache ? nkv * (hd / 2) : 0);
     dim3 grid(T, (items + ROPE_THREADS - 1) / ROPE_THREADS);
     AP_REQUIRE(grid.y <= 65535, "rope_kv_store: too many heads for the grid");
 #define LAUNCH(TI, TO)                                                                              \
-    rope_kv_store_kernel<TI, TO><<<grid, ROPE_THREADS, 0, stream>>>(                                \
+    AP_CHECK_PDL_LAUNCH("rope_kv_store", ap_launch_pdl(                                             \
+        rope_kv_store_kernel<TI, TO>, grid, dim3(ROPE_THREADS), 0, stream,                          \
         (const TI*)in, S, (size_t)in_stride, (TO*)q_out, (TO*)cache, positions, token_seq,         \
-        block_table, max_blocks, (const float2*)cos_sin, pairing, nh, nkv, hd, P, (size_t)page_stride)
+        block_table, max_blocks, (const float2*)cos_sin, pairing, nh, nkv, hd, P, (size_t)page_stride))
     if (in_dtype == AP_F32 && act_dtype == AP_F32) LAUNCH(float, float);
     else if (in_dtype == AP_F32 && act_dtype == AP_BF16) LAUNCH(float, bf16);
     else if (in_dtype == AP_BF16 && act_dtype == AP_BF16) {
@@ -274,7 +367,6 @@ AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in
         LAUNCH(bf16, bf16);
     } else AP_REQUIRE(false, "rope_kv_store: unsupported dtypes in=%d act=%d", in_dtype, act_dtype);
 #undef LAUNCH
-    AP_CHECK_LAUNCH("rope_kv_store");
     return AP_OK;
 }
 
@@ -285,6 +377,8 @@ template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ in, int S, size_t in_stride, TO* __restrict__ out,
                               int T, int I) {
     const size_t n = (size_t)T * I;
+    ap_pdl_trigger();
+    ap_pdl_wait();
     for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
         const size_t t = e / I, j = e - t * I;
         const size_t base = t * 2 * (size_t)I;
@@ -295,6 +389,28 @@ __global__ void swiglu_kernel(const TI* __restrict__ in, int S, size_t in_stride
     }
 }
 
+// bfloat16 in and out, 8 elements (16 bytes) per thread
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int T, int I) {
+    const size_t n8 = (size_t)T * (I / 8);
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n8; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / (I / 8), j = (e - t * (I / 8)) * 8;
+        const uint4 g4 = *reinterpret_cast<const uint4*>(in + t * 2 * (size_t)I + j);
+        const uint4 u4 = *reinterpret_cast<const uint4*>(in + t * 2 * (size_t)I + I + j);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+        uint4 o4;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+            o2[k] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+        }
+        *reinterpret_cast<uint4*>(out + t * (size_t)I + j) = o4;
+    }
+}
+
 AP_EXPORT int ap_swiglu(const void* in, int in_dtype, int S, long long in_stride, void* out, int out_dtype,
                         int T, int I, cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && I > 0 && S >= 1, "swiglu: bad sizes T=%d I=%d S=%d", T, I, S);
@@ -302,8 +418,17 @@ AP_EXPORT int ap_swiglu(const void* in, int in_dtype, int S, long long in_stride
     const int threads = 256;
     long long blocks = ((long long)T * I + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
+    if (in_dtype == AP_BF16 && out_dtype == AP_BF16 && S == 1 && I % 8 == 0 && ((uintptr_t)in & 15) == 0 &&
+        ((uintptr_t)out & 15) == 0) {
+        long long b8 = ((long long)T * (I / 8) + threads - 1) / threads;
+        if (b8 > 148 * 32) b8 = 148 * 32;
+        AP_CHECK_PDL_LAUNCH("swiglu", ap_launch_pdl(swiglu_bf16x8_kernel, dim3((unsigned)b8), dim3(threads), 0, stream,
+                                                    (const bf16*)in, (bf16*)out, T, I));
+        return AP_OK;
+    }
 #define LAUNCH(TI, TO) \
-    swiglu_kernel<TI, TO><<<(int)blocks, threads, 0, stream>>>((const TI*)in, S, (size_t)in_stride, (TO*)out, T, I)
+    AP_CHECK_PDL_LAUNCH("swiglu", ap_launch_pdl(swiglu_kernel<TI, TO>, dim3((unsigned)blocks), dim3(threads), 0, stream, \
+                                                (const TI*)in, S, (size_t)in_stride, (TO*)out, T, I))
     if (in_dtype == AP_F32 && out_dtype == AP_F32) LAUNCH(float, float);
     else if (in_dtype == AP_F32 && out_dtype == AP_BF16) LAUNCH(float, bf16);
     else if (in_dtype == AP_BF16 && out_dtype == AP_BF16) {
@@ -311,6 +436,5 @@ AP_EXPORT int ap_swiglu(const void* in, int in_dtype, int S, long long in_stride
         LAUNCH(bf16, bf16);
     } else AP_REQUIRE(false, "swiglu: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
 #undef LAUNCH
-    AP_CHECK_LAUNCH("swiglu");
     return AP_OK;
 }

@@ -29,21 +29,31 @@
 #define TC_ERR_ACCUM_WAIT 3
 
 static __device__ int g_tc_status;
+static long long g_l2_prefetch_budget = 0;      // bytes; set by ap_gemm_tc_set_l2_prefetch
 
-template <int BN> struct TileCfg {
-    static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 4);
+template <int BN, bool CLUSTER = false> struct TileCfg {
+    // 64 rows in a cluster: three stages, so that two CTAs with their reduction buffers share an SM
+    static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : ((CLUSTER && BN == 64) ? 3 : 4));
     static constexpr int kBBytes = BN * TILE_K * 2;
     static constexpr int kStageBytes = A_TILE_BYTES + kBBytes;
     static constexpr int kTmemCols = BN < 32 ? 32 : BN;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int kBarrierBytes = 256;
+    // cluster reduction buffer: [slices][BN][rows per slice], at most 136 rows in all
+    static constexpr int kReduceBytes = (TILE_W + 8) * BN * 4;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + kBarrierBytes;
+    static constexpr int kSmemBytesCluster = kSmemBytes + kReduceBytes;
 };
 
-template <int BN, typename TO>
+// CLUSTER: the gridDim.z K-slices of one output tile form a thread-block cluster and add
+// their partial tiles through distributed shared memory, each CTA finishing a band of the
+// 128 weight rows; `out` is then the finished [M, N] matrix.  Otherwise slice z writes its
+// partial sums to out + z * split_stride.
+template <int BN, typename TO, bool CLUSTER>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                TO* __restrict__ out, int M, int N, int K, long long ldc, int kb_per_split,
-               long long split_stride) {
-    using Cfg = TileCfg<BN>;
+               long long split_stride, int l2_prefetch_tiles) {
+    using Cfg = TileCfg<BN, CLUSTER>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -54,17 +64,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     uint64_t* accum = empty + STAGES;
     uint32_t* tmem_slot = (uint32_t*)(accum + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* reduce = (float*)(smem + STAGES * Cfg::kStageBytes + Cfg::kBarrierBytes);
 
-    // once a wait has expired anywhere, later CTAs do nothing: the product is void anyway
-    if (*(volatile int*)&g_tc_status != 0) return;
+    // once a wait has expired anywhere, later CTAs do nothing: the product is void anyway.
+    // (In a cluster every CTA still walks to the cluster barrier, or its peers would wait.)
+    const bool skip = *(volatile int*)&g_tc_status != 0;
+    if (!CLUSTER && skip) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * TILE_W;
     const int m0 = blockIdx.y * BN;
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     const int kb0 = blockIdx.z * kb_per_split;
     const int kb1 = min(kb_total, kb0 + kb_per_split);
-    const int nkb = max(0, kb1 - kb0);
-    out += (size_t)blockIdx.z * split_stride;
+    const int nkb = skip ? 0 : max(0, kb1 - kb0);
+    if (!CLUSTER) out += (size_t)blockIdx.z * split_stride;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -82,11 +95,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // A grid that fits the GPU in one wave lets the next kernel start at once (it will only
+    // prefetch until this one is done); a larger grid keeps the SMs to itself until its end.
+    const bool one_wave = gridDim.x * gridDim.y * gridDim.z <= 2 * 148;
+    if (one_wave) ap_pdl_trigger();
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
-            for (int i = 0; i < nkb; ++i) {
+            // The weight does not depend on earlier kernels: fill the ring with weight tiles
+            // first, then wait for the kernels that produce the activations.
+            const int pre = min(nkb, STAGES);
+            for (int i = 0; i < pre; ++i) {
+                tc::mbar_expect_tx(&full[i], Cfg::kStageBytes);
+                tc::tma_load_2d(w_tiles + i * A_TILE_BYTES, &tmap_w, (kb0 + i) * TILE_K, n0, &full[i]);
+            }
+            // ... and ask L2 for the rest of this CTA's weight slice, so that HBM keeps streaming
+            // while the kernels before this one finish
+            if (l2_prefetch_tiles > 0) {
+                const int last = min(nkb, pre + l2_prefetch_tiles);
+                for (int i = pre; i < last; ++i) tc::tma_prefetch_l2_2d(&tmap_w, (kb0 + i) * TILE_K, n0);
+            }
+            ap_pdl_wait();
+            for (int i = 0; i < pre; ++i)
+                tc::tma_load_2d(a_tiles + i * Cfg::kBBytes, &tmap_a, (kb0 + i) * TILE_K, m0, &full[i]);
+            int issued = pre;
+            for (int i = pre; i < nkb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t ph = (i / STAGES) & 1;
                 if (*abort_flag) break;
@@ -135,7 +168,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     } else {
         // epilogue: warp q reads lanes 32q..32q+31 = weight rows n0 + 32q + lane
         const int q = warp & 3;
-        const int n = n0 + q * 32 + lane;
+        const int row = q * 32 + lane;
+        const int n = n0 + row;
+        ap_pdl_wait();          // `out` may still be read by an earlier kernel
         bool have = nkb > 0;
         if (have) {
             if (!tc::mbar_wait(accum, 0)) {
@@ -147,7 +182,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             }
             tc::fence_after_sync();
         }
-        if (have) {
+        if (CLUSTER) {
+            // hand this row's partial sums to the CTA that finishes its band of rows
+            const int S = gridDim.z;
+            const int band = (TILE_W + S - 1) / S;
+            const int dest = row / band, slot = row - dest * band;
+            const uint32_t base = tc::map_to_rank(tc::smem_addr(reduce), (uint32_t)dest) +
+                                  (uint32_t)((blockIdx.z * BN) * band + slot) * 4u;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t v[16];
+                if (have) {
+                    tc::tmem_ld_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+                    tc::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0u;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    tc::st_cluster_f32(base + (uint32_t)((c + j) * band) * 4u, __uint_as_float(v[j]));
+            }
+        } else if (have) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 if (m0 + c >= M) break;
@@ -169,8 +225,198 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             }
         }
     }
+    if (CLUSTER) {
+        __syncwarp();
+        tc::cluster_sync();                 // every slice has delivered its partial sums
+        const int S = gridDim.z;
+        const int band = (TILE_W + S - 1) / S;
+        const int first = blockIdx.z * band;
+        const int rows = max(0, min(band, TILE_W - first));
+        const int e = (int)threadIdx.x - 64;              // the four epilogue warps add the band
+        if (e >= 0 && !skip) {
+            const int mcols = min(BN, M - m0);
+            for (int idx = e; idx < rows * mcols; idx += 128) {
+                const int c = idx / rows, i = idx - c * rows;
+                float sum = 0.f;
+                for (int s = 0; s < S; ++s) sum += reduce[(s * BN + c) * band + i];   // slices in order
+                const int n = n0 + first + i;
+                if (n < N) out[(size_t)(m0 + c) * ldc + n] = ap_from_float<TO>(sum);
+            }
+        }
+    }
     tc::fence_before_sync();
     __syncthreads();
+    if (!one_wave) ap_pdl_trigger();
+    if (warp == 1) {
+        __syncwarp();
+        tc::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Two weight tiles per CTA against the same activation tile: a 256 x BN output tile from
+// two accumulators (2 * BN tensor-memory columns).  Every activation tile that reaches
+// shared memory now feeds twice the FLOPs, which matters once many rows are in flight and
+// the product is bound by what L2 can deliver to the SMs.  The second weight tile starts
+// `w1_offset` rows after the first: 128 for two adjacent tiles, or the intermediate size
+// when the weight is [W_gate; W_up] stacked; then (SWIGLU) the epilogue writes
+// silu(gate) * up, so the gated activation never makes a round trip through memory.
+// ---------------------------------------------------------------------------
+template <int BN> struct DualCfg {
+    static constexpr int kStages = BN >= 256 ? 3 : 4;
+    static constexpr int kBBytes = BN * TILE_K * 2;
+    static constexpr int kStageBytes = 2 * A_TILE_BYTES + kBBytes;
+    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+template <int BN, typename TO, bool SWIGLU>
+__global__ void __launch_bounds__(192)
+gemm_tc_dual_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+                    TO* __restrict__ out, int M, int N, int K, long long ldc, int w1_offset) {
+    using Cfg = DualCfg<BN>;
+    constexpr int STAGES = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* w_tiles = smem;                                   // [stage][2][128 x 64]
+    uint8_t* a_tiles = smem + STAGES * 2 * A_TILE_BYTES;
+    uint64_t* full = (uint64_t*)(smem + STAGES * Cfg::kStageBytes);
+    uint64_t* empty = full + STAGES;
+    uint64_t* accum = empty + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(accum + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    if (*(volatile int*)&g_tc_status != 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // SWIGLU: N counts output columns (the intermediate size); tile x covers gate rows
+    // [128x, 128x+128) and the up rows w1_offset further on.  Else tile x covers 256 rows.
+    const int n0 = blockIdx.x * (SWIGLU ? TILE_W : 2 * TILE_W);
+    const int m0 = blockIdx.y * BN;
+    const int nkb = (K + TILE_K - 1) / TILE_K;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], 1);
+        }
+        tc::mbar_init(accum, 1);
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::prefetch_tensormap(&tmap_w);
+        tc::prefetch_tensormap(&tmap_a);
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            ap_pdl_wait();
+            int issued = 0;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                if (*abort_flag) break;
+                if (!tc::mbar_wait(&empty[s], ph ^ 1)) {
+                    *abort_flag = 1;
+                    atomicExch(&g_tc_status, TC_ERR_EMPTY_WAIT);
+                    break;
+                }
+                tc::mbar_expect_tx(&full[s], Cfg::kStageBytes);
+                tc::tma_load_2d(w_tiles + (2 * s) * A_TILE_BYTES, &tmap_w, i * TILE_K, n0, &full[s]);
+                tc::tma_load_2d(w_tiles + (2 * s + 1) * A_TILE_BYTES, &tmap_w, i * TILE_K, n0 + w1_offset, &full[s]);
+                tc::tma_load_2d(a_tiles + s * Cfg::kBBytes, &tmap_a, i * TILE_K, m0, &full[s]);
+                issued = i + 1;
+            }
+            if (*abort_flag) {
+                for (int i = max(0, issued - STAGES); i < issued; ++i)
+                    tc::mbar_wait(&full[i % STAGES], (i / STAGES) & 1, 200000000LL);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::instr_desc_bf16_f32(TILE_W, BN);
+            bool ok = true;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                if (*abort_flag) { ok = false; break; }
+                if (!tc::mbar_wait(&full[s], ph)) {
+                    *abort_flag = 1;
+                    atomicExch(&g_tc_status, TC_ERR_FULL_WAIT);
+                    ok = false;
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint64_t w0 = tc::smem_desc_k_major_sw128(w_tiles + (2 * s) * A_TILE_BYTES);
+                const uint64_t w1 = tc::smem_desc_k_major_sw128(w_tiles + (2 * s + 1) * A_TILE_BYTES);
+                const uint64_t ad = tc::smem_desc_k_major_sw128(a_tiles + s * Cfg::kBBytes);
+#pragma unroll
+                for (int k = 0; k < TILE_K / 16; ++k) {
+                    const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                    tc::mma_bf16(tmem_base, w0 + 2 * k, ad + 2 * k, idesc, acc);
+                    tc::mma_bf16(tmem_base + BN, w1 + 2 * k, ad + 2 * k, idesc, acc);
+                }
+                tc::mma_commit(&empty[s]);
+            }
+            if (ok) tc::mma_commit(accum);
+        }
+    } else {
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        ap_pdl_wait();
+        bool have = true;
+        if (!tc::mbar_wait(accum, 0)) {
+            if (!*abort_flag) {
+                *abort_flag = 1;
+                atomicExch(&g_tc_status, TC_ERR_ACCUM_WAIT);
+            }
+            have = false;
+        }
+        tc::fence_after_sync();
+        if (have) {
+            const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (m0 + c >= M) break;
+                uint32_t v0[16], v1[16];
+                tc::tmem_ld_x16(lane_base + (uint32_t)c, v0);
+                tc::tmem_ld_x16(lane_base + (uint32_t)(BN + c), v1);
+                tc::tmem_ld_wait();
+                if (SWIGLU) {
+                    const int n = n0 + row;
+                    if (n < N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int m = m0 + c + j;
+                            if (m >= M) break;
+                            // the gate and the up value pass through the storage type, as when the
+                            // activation is a kernel of its own
+                            const float g = ap_to_float(ap_from_float<TO>(__uint_as_float(v0[j])));
+                            const float u = ap_to_float(ap_from_float<TO>(__uint_as_float(v1[j])));
+                            // the result is rounded to the storage type: the fast exponential and
+                            // division (a few 32-bit ulps) are far below that rounding
+                            out[(size_t)m * ldc + n] = ap_from_float<TO>(__fdividef(g, 1.0f + __expf(-g)) * u);
+                        }
+                    }
+                } else {
+                    const int na = n0 + row, nb = n0 + w1_offset + row;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = m0 + c + j;
+                        if (m >= M) break;
+                        if (na < N) out[(size_t)m * ldc + na] = ap_from_float<TO>(__uint_as_float(v0[j]));
+                        if (nb < N) out[(size_t)m * ldc + nb] = ap_from_float<TO>(__uint_as_float(v1[j]));
+                    }
+                }
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    ap_pdl_trigger();
     if (warp == 1) {
         __syncwarp();
         tc::tmem_dealloc(tmem_base, Cfg::kTmemCols);
@@ -213,46 +459,85 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
 static int pick_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256; }
 
 // How many K slices the kernel wants for this shape (1: none).  Few rows leave too few
-// weight tiles to keep every SM loading, so K is split until about two CTAs per SM exist,
-// as long as the partial sums stay small beside the weight itself.
+// weight tiles to keep every SM loading, so K is split until about two CTAs per SM exist
+// (at most 8: the slices of a tile form one thread-block cluster that adds them up).
 AP_EXPORT int ap_gemm_tc_plan(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0) return 1;
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     const int bn = pick_bn(M);
     const long long tiles = (long long)((N + TILE_W - 1) / TILE_W) * ((M + bn - 1) / bn);
     if (M > 64 || tiles >= 148) return 1;
-    int ns = (int)((296 + tiles - 1) / tiles);
+    // as many slices as keep the whole grid resident at once (two CTAs per SM, a little
+    // slack so that the clusters find room side by side)
+    int ns = (int)(288 / tiles);
     ns = min(ns, kb_total / 4);
-    ns = min(ns, max(1, K / (16 * M)));
-    ns = min(ns, 16);
+    ns = min(ns, max(1, K / (16 * M)));    // more rows: fewer, longer slices
+    ns = min(ns, 8);                       // one thread-block cluster adds the slices
     if (ns < 1) ns = 1;
+    while (ns & (ns - 1)) ns &= ns - 1;    // clusters of 2, 4 or 8 CTAs find room side by side; odd sizes do not
     const int per = (kb_total + ns - 1) / ns;
     return (kb_total + per - 1) / per;
 }
 
-template <int BN, typename TO>
+template <int BN, typename TO, bool CLUSTER>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K,
                      long long ldc, int nsplit, long long split_stride, cudaStream_t stream) {
-    using Cfg = TileCfg<BN>;
-    auto kern = gemm_tc_kernel<BN, TO>;
+    using Cfg = TileCfg<BN, CLUSTER>;
+    auto kern = gemm_tc_kernel<BN, TO, CLUSTER>;
+    constexpr int smem = CLUSTER ? Cfg::kSmemBytesCluster : Cfg::kSmemBytes;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-        AP_REQUIRE(e == cudaSuccess, "gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::kSmemBytes,
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        AP_REQUIRE(e == cudaSuccess, "gemm_tc: cannot reserve %d bytes of shared memory: %s", smem,
                    cudaGetErrorString(e));
         configured = true;
     }
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     const int per = (kb_total + nsplit - 1) / nsplit;
-    dim3 grid((N + TILE_W - 1) / TILE_W, (M + BN - 1) / BN, nsplit);
-    kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(mw, ma, (TO*)out, M, N, K, ldc, per, split_stride);
-    AP_CHECK_LAUNCH("gemm_tc");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((N + TILE_W - 1) / TILE_W, (M + BN - 1) / BN, nsplit);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int nattr = 0;
+    if (CLUSTER) {
+        attr[nattr].id = cudaLaunchAttributeClusterDimension;
+        attr[nattr].val.clusterDim.x = 1;
+        attr[nattr].val.clusterDim.y = 1;
+        attr[nattr].val.clusterDim.z = nsplit;
+        ++nattr;
+    }
+    if (ap_pdl_enabled()) {
+        attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+        ++nattr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = nattr;
+    // Weight tiles each CTA asks L2 for before it waits for the kernels ahead of it: only
+    // for single-wave grids, and only as much as L2 can hold without pushing out what is
+    // in use (a budget of 32 MiB over the whole grid).
+    const long long ctas = (long long)cfg.gridDim.x * cfg.gridDim.y * cfg.gridDim.z;
+    int l2_tiles = 0;
+    if (ap_pdl_enabled() && ctas <= 2 * 148 && g_l2_prefetch_budget > 0)
+        l2_tiles = (int)(g_l2_prefetch_budget / (ctas * A_TILE_BYTES));
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, ma, (TO*)out, M, N, K, ldc, per, split_stride, l2_tiles);
+    if (e != cudaSuccess) {
+        ap_set_error("gemm_tc: launch failed: %s", cudaGetErrorString(e));
+        return AP_ERR_LAUNCH;
+    }
     return AP_OK;
 }
 
+#define AP_MAX_CLUSTER 8
+
+// reduce != 0: the K slices add up inside a thread-block cluster and `out` is the finished
+// [M, N] matrix (any output type, nsplit <= 8, M <= 64); else slice z writes 32-bit partial
+// sums at out + z * split_stride.
 AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K,
                          long long lda, long long ldw, long long ldc, int nsplit, long long split_stride,
-                         cudaStream_t stream) {
+                         int reduce, cudaStream_t stream) {
     AP_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     if (M == 0) return AP_OK;
     AP_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
@@ -261,27 +546,99 @@ AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype,
     AP_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_tc: a leading dimension is below its row length");
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     AP_REQUIRE(nsplit >= 1 && nsplit <= kb_total && nsplit <= 65535, "gemm_tc: cannot split K=%d into %d", K, nsplit);
-    AP_REQUIRE(nsplit == 1 || out_dtype == AP_F32, "gemm_tc: partial sums must be 32-bit");
     AP_REQUIRE((long long)(nsplit - 1) * ((kb_total + nsplit - 1) / nsplit) < kb_total,
                "gemm_tc: %d slices leave an empty one for K=%d", nsplit, K);
+    AP_REQUIRE(out_dtype == AP_F32 || out_dtype == AP_BF16, "gemm_tc: unknown output dtype %d", out_dtype);
     const int bn = pick_bn(M);
     AP_REQUIRE((M + bn - 1) / bn <= 65535, "gemm_tc: %d rows exceed the grid", M);
+    const bool cluster = reduce != 0 && nsplit > 1;
+    AP_REQUIRE(!cluster || (nsplit <= AP_MAX_CLUSTER && bn <= 64),
+               "gemm_tc: slices are added in a cluster only for up to %d slices and 64 rows (got %d, %d)",
+               AP_MAX_CLUSTER, nsplit, M);
+    AP_REQUIRE(cluster || nsplit == 1 || out_dtype == AP_F32, "gemm_tc: partial sums must be 32-bit");
     CUtensorMap mw, ma;
     AP_REQUIRE(make_map(&mw, w, N, K, ldw, TILE_W), "gemm_tc: cannot encode the weight's tensor map");
     AP_REQUIRE(make_map(&ma, a, M, K, lda, bn), "gemm_tc: cannot encode the activations' tensor map");
-#define GO(BN)                                                                                          \
-    return out_dtype == AP_F32                                                                          \
-               ? launch_tc<BN, float>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, stream)          \
-               : launch_tc<BN, bf16>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, stream)
-    AP_REQUIRE(out_dtype == AP_F32 || out_dtype == AP_BF16, "gemm_tc: unknown output dtype %d", out_dtype);
+#define GO(BN, CL)                                                                                       \
+    return out_dtype == AP_F32                                                                           \
+               ? launch_tc<BN, float, CL>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, stream)       \
+               : launch_tc<BN, bf16, CL>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, stream)
+    if (cluster) {
+        switch (bn) {
+            case 16: GO(16, true);
+            case 32: GO(32, true);
+            default: GO(64, true);
+        }
+    }
     switch (bn) {
-        case 16: GO(16);
-        case 32: GO(32);
-        case 64: GO(64);
-        case 128: GO(128);
-        default: GO(256);
+        case 16: GO(16, false);
+        case 32: GO(32, false);
+        case 64: GO(64, false);
+        case 128: GO(128, false);
+        default: GO(256, false);
     }
 #undef GO
+}
+
+template <int BN, typename TO, bool SWIGLU>
+static int launch_dual(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K,
+                       long long ldc, int w1_offset, cudaStream_t stream) {
+    using Cfg = DualCfg<BN>;
+    auto kern = gemm_tc_dual_kernel<BN, TO, SWIGLU>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        AP_REQUIRE(e == cudaSuccess, "gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::kSmemBytes,
+                   cudaGetErrorString(e));
+        configured = true;
+    }
+    const int tile_n = SWIGLU ? TILE_W : 2 * TILE_W;
+    dim3 grid((N + tile_n - 1) / tile_n, (M + BN - 1) / BN, 1);
+    AP_CHECK_PDL_LAUNCH("gemm_tc_dual", ap_launch_pdl(kern, grid, dim3(192), (size_t)Cfg::kSmemBytes, stream, mw, ma,
+                                                      (TO*)out, M, N, K, ldc, w1_offset));
+    return AP_OK;
+}
+
+// Two weight tiles per CTA (see gemm_tc_dual_kernel), for products with more than 64 rows.
+//   swiglu == 0: out[M, N] = a * w^T for w [N, K].
+//   swiglu != 0: w is [2N, K] = [W_gate; W_up]; out[M, N] = silu(a W_gate^T) * (a W_up^T).
+AP_EXPORT int ap_gemm_tc_dual(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K,
+                              long long lda, long long ldw, long long ldc, int swiglu, cudaStream_t stream) {
+    AP_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+    if (M == 0) return AP_OK;
+    AP_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
+               "gemm_tc: K=%d and the leading dimensions must be multiples of 8 (16-byte rows for TMA)", K);
+    AP_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
+    AP_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_tc: a leading dimension is below its row length");
+    AP_REQUIRE(out_dtype == AP_F32 || out_dtype == AP_BF16, "gemm_tc: unknown output dtype %d", out_dtype);
+    const int bn = M <= 128 ? 128 : 256;
+    AP_REQUIRE((M + bn - 1) / bn <= 65535, "gemm_tc: %d rows exceed the grid", M);
+    CUtensorMap mw, ma;
+    AP_REQUIRE(make_map(&mw, w, swiglu ? 2LL * N : N, K, ldw, TILE_W), "gemm_tc: cannot encode the weight's tensor map");
+    AP_REQUIRE(make_map(&ma, a, M, K, lda, bn), "gemm_tc: cannot encode the activations' tensor map");
+    const int off = swiglu ? N : TILE_W;
+#define GO(BN, SW)                                                                             \
+    return out_dtype == AP_F32 ? launch_dual<BN, float, SW>(mw, ma, out, M, N, K, ldc, off, stream) \
+                               : launch_dual<BN, bf16, SW>(mw, ma, out, M, N, K, ldc, off, stream)
+    if (swiglu) {
+        if (bn == 128) GO(128, true);
+        GO(256, true);
+    }
+    if (bn == 128) GO(128, false);
+    GO(256, false);
+#undef GO
+}
+
+// Whether two weight tiles per CTA beat one for this shape: a dual tile takes about 1.65
+// times as long as a single one, and either kind runs in waves of one CTA per SM.
+AP_EXPORT int ap_gemm_tc_prefers_dual(int M, int N, int K) {
+    (void)K;
+    if (M <= 64) return 0;
+    const int bn = M <= 128 ? 128 : 256;
+    const long long rows = (M + bn - 1) / bn;
+    const long long single = ((N + TILE_W - 1) / TILE_W) * rows, dual = ((N + 2 * TILE_W - 1) / (2 * TILE_W)) * rows;
+    const long long ws = (single + 147) / 148, wd = (dual + 147) / 148;
+    return wd * 165 < ws * 100 ? 1 : 0;
 }
 
 // 0 when every tensor-core product so far ran to its end; else the code of the wait that
@@ -290,6 +647,12 @@ AP_EXPORT int ap_gemm_tc_status(void) {
     int v = -1;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
     return v;
+}
+
+// Bytes of weight a single-wave product may ask L2 for ahead of its dependency wait (0: none).
+AP_EXPORT int ap_gemm_tc_set_l2_prefetch(long long bytes) {
+    g_l2_prefetch_budget = bytes < 0 ? 0 : bytes;
+    return AP_OK;
 }
 
 // Clear the status word so that products run again after a reported expiry.

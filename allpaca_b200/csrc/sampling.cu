@@ -33,6 +33,8 @@ argmax_kernel(const float* __restrict__ logits, long long row_stride, int V, int
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const float* row = logits + (size_t)blockIdx.x * row_stride;
+    ap_pdl_trigger();
+    ap_pdl_wait();
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < V; i += SAMP_THREADS) {
@@ -58,8 +60,8 @@ AP_EXPORT int ap_argmax(const float* logits, long long row_stride, int R, int V,
                         cudaStream_t stream) {
     AP_REQUIRE(R >= 0 && V > 0 && row_stride >= V, "argmax: bad sizes R=%d V=%d", R, V);
     if (R == 0) return AP_OK;
-    argmax_kernel<<<R, SAMP_THREADS, 0, stream>>>(logits, row_stride, V, out);
-    AP_CHECK_LAUNCH("argmax");
+    AP_CHECK_PDL_LAUNCH("argmax", ap_launch_pdl(argmax_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, logits,
+                                                row_stride, V, out));
     return AP_OK;
 }
 

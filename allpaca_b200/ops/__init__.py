@@ -180,11 +180,14 @@ def tensor_core_gemm_available() -> bool:
     return hasattr(core(), "ap_gemm_tc")
 
 
-def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1) -> None:
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1,
+            reduce: bool = False) -> None:
     """bfloat16 ``a[M,K] @ w[N,K]^T`` on the tcgen05 tensor cores.
 
-    ``out`` is ``[M,N]`` (bfloat16 or float32) for ``nsplit == 1`` and float32
-    ``[nsplit, M, N]`` partial sums otherwise.
+    ``nsplit`` K slices run as separate CTAs.  With ``reduce`` they add up inside a
+    thread-block cluster (at most 8 slices, at most 64 rows) and ``out`` is the finished
+    ``[M,N]`` in bfloat16 or float32; without it ``out`` is float32 ``[nsplit, M, N]`` partial
+    sums (``[M,N]`` for ``nsplit == 1``).
     """
     _check(a, "a", torch.bfloat16, 2)
     _check(w, "w", torch.bfloat16, 2)
@@ -193,7 +196,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError("gemm_tc: inner sizes disagree")
-    if nsplit == 1:
+    if nsplit == 1 or reduce:
         if tuple(out.shape) != (M, N):
             raise KernelError("gemm_tc: out must be [M,N]")
         stride = 0
@@ -202,7 +205,24 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1
             raise KernelError("gemm_tc: partial sums must be float32 [nsplit,M,N]")
         stride = M * N
     call(core(), "ap_gemm_tc", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
-         M, N, K, K, K, N, nsplit, stride, stream_handle())
+         M, N, K, K, K, N, nsplit, stride, 1 if reduce else 0, stream_handle())
+
+
+def gemm_tc_dual(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
+    """The tensor-core product with two weight tiles per CTA, for more than 64 rows.
+
+    ``swiglu`` False: ``out[M,N] = a[M,K] @ w[N,K]^T``.  True: ``w`` is ``[2N, K]``, gate rows
+    then up rows, and ``out[M,N] = silu(a @ w_gate^T) * (a @ w_up^T)``.
+    """
+    _check(a, "a", torch.bfloat16, 2)
+    _check(w, "w", torch.bfloat16, 2)
+    _check(out, "out", dims=2)
+    M, K = a.shape
+    N = w.shape[0] // 2 if swiglu else w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N) or (swiglu and w.shape[0] % 2):
+        raise KernelError(f"gemm_tc_dual: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    call(core(), "ap_gemm_tc_dual", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+         M, N, K, K, K, N, 1 if swiglu else 0, stream_handle())
 
 
 def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
@@ -210,13 +230,16 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: int = 0, seq_start: Optional[torch.Tensor] = None,
               query_lens: Optional[Sequence[int]] = None, max_context: int = 0,
-              scratch=None) -> None:
+              scratch=None, zero_scratch=None) -> None:
     """Causal attention of every row of ``q [T, nh*hd]`` over its sequence's cached keys.
 
     float32 runs the general CUDA-core kernel (the true 32-bit path).  bfloat16 runs on the
     tensor cores when ``seq_start`` (device, ``[nseq+1]``) and ``query_lens`` (host) are
     given: the split kernel when every sequence brings one row, else the tile kernel.
-    ``scratch(name, shape, dtype)`` supplies the partial-result buffers of the split kernel.
+    ``scratch(name, shape, dtype)`` supplies the partial-result buffers of the split kernel;
+    ``zero_scratch`` (same signature) supplies buffers that are zero when first handed out
+    and stay with the caller: with it the last key slice to arrive combines all slices,
+    without it a second kernel does.
     """
     _check(q, "q", dims=2)
     _check(out, "out", q.dtype, 2)
@@ -239,21 +262,26 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
             raise KernelError("attention: seq_start/query_lens do not describe the rows")
         if all(n == 1 for n in query_lens):
             nsplit = decode_splits(T, num_heads, num_kv_heads, max_context, window)
-            po = pm = 0
+            po = pm = pc = 0
             if nsplit > 1:
                 if scratch is None:
                     raise KernelError("attention: key slices need a scratch provider")
                 po = scratch("attn.part_o", (nsplit, T, num_heads, head_dim), torch.float32).data_ptr()
                 pm = scratch("attn.part_ml", (nsplit, T, num_heads, 2), torch.float32).data_ptr()
+                if zero_scratch is not None:
+                    # arrival counters of the slices: zero now, and left zero by every launch
+                    reps = num_heads // num_kv_heads
+                    chunks = -(-reps // min(reps, 16))
+                    pc = zero_scratch("attn.counters", (T * num_kv_heads * chunks,), torch.int32).data_ptr()
             mode, tiles = 1, 0
         else:
             tpt = int(lib.ap_attention_tc_tokens_per_tile(num_heads, num_kv_heads))
             tiles = sum(-(-n // tpt) for n in query_lens)
-            mode, nsplit, po, pm = 0, 1, 0, 0
+            mode, nsplit, po, pm, pc = 0, 1, 0, 0, 0
         call(lib, "ap_attention_tc", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
              block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(), positions.data_ptr(),
              nseq, T, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0), float(scale),
-             int(window or 0), mode, tiles, nsplit, po, pm, stream_handle())
+             int(window or 0), mode, tiles, nsplit, po, pm, pc, stream_handle())
         return
     call(lib, "ap_attention_rows", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
          dtype_code(q.dtype), block_table.data_ptr(), block_table.shape[1], token_seq.data_ptr(),
@@ -302,6 +330,12 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
     if not hasattr(lib, "ap_gemm_tc_plan"):
         return 1
     return max(1, int(lib.ap_gemm_tc_plan(int(M), int(N), int(K))))
+
+
+def gemm_tc_prefers_dual(M: int, N: int, K: int) -> bool:
+    """Whether the kernel with two weight tiles per CTA is the faster one for this shape."""
+    lib = core()
+    return hasattr(lib, "ap_gemm_tc_prefers_dual") and bool(lib.ap_gemm_tc_prefers_dual(int(M), int(N), int(K)))
 
 
 def gemm_tc_status() -> int:

@@ -33,9 +33,12 @@ _CORE_SIGNATURES = {
     "ap_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
 }
 _OPTIONAL_CORE_SIGNATURES = {
-    # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, stream)
-    "ap_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _L, _P],
+    # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, stream)
+    "ap_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _L, _I, _P],
+    "ap_gemm_tc_dual": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P],
     "ap_gemm_tc_plan": [_I, _I, _I],
+    "ap_gemm_tc_prefers_dual": [_I, _I, _I],
+    "ap_gemm_tc_set_l2_prefetch": [_L],
     "ap_gemm_tc_status": [],
     "ap_gemm_tc_reset_status": [],
 }
@@ -103,7 +106,7 @@ def attention(head_dim: int) -> ctypes.CDLL:
 
 
 _OPTIONAL_ATTN_SIGNATURES: Dict[str, list] = {
-    "ap_attention_tc": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _L, _F, _I, _I, _I, _I, _P, _P, _P],
+    "ap_attention_tc": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _L, _F, _I, _I, _I, _I, _P, _P, _P, _P],
     "ap_attention_tc_tokens_per_tile": [_I, _I],
 }
 

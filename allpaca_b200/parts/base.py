@@ -100,6 +100,20 @@ class Workspace:
             self.generation += 1
         return buf[:n].view(*shape)
 
+    def get_zeroed(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        """Like :meth:`get`, but the memory is zero when it is first handed out (and after
+        growing); users that leave it zero find it zero again."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = f"{name}:{dtype}"
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+            self.generation += 1
+        return buf[:n].view(*shape)
+
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
 

@@ -3,8 +3,9 @@
 float32 runs on the CUDA cores with 32-bit accumulation (the true 32-bit path);
 bfloat16 runs on the tcgen05 tensor cores when the shape allows TMA (rows of a
 multiple of 8 elements), else on the CUDA-core kernel.  For few rows the
-tensor-core kernel splits K over several thread blocks and returns 32-bit partial
-sums ``[S, T, N]``, which every consumer adds in order.
+tensor-core kernel splits K over the CTAs of a thread-block cluster, which add their
+partial tiles through distributed shared memory.  Consumers also accept 32-bit partial
+sums ``[S, T, N]`` and add them in order (S is 1 for everything produced here).
 
 Reference parity: weights are ``[out, in]`` row-major and ``y = W x`` is ``matmul_nt``
 (crates/allpaca-cpu/src/kernels.rs:98-130); no biases on this path.
@@ -40,26 +41,38 @@ class Linear:
         """``a [T, in]`` times the weight.
 
         ``kind`` says what the consumer takes:
-        ``"delta"``   32-bit partial sums ``[S, T, out]`` (S may be 1), for the residual;
-        ``"either"``  ``[T, out]`` in the activation type, or ``[S, T, out]`` partial sums
-                      when the kernel chose to split K;
+        ``"delta"``   32-bit ``[1, T, out]`` for the residual (consumers take ``[S, T, out]``);
+        ``"either"``  ``[T, out]`` in the activation type;
         ``"float32"`` 32-bit ``[T, out]`` (logits).
         """
         T = a.shape[0]
         N = self.out_features
         ws = self.env.workspace
         tc = self.uses_tensor_cores()
-        nsplit = ops.gemm_tc_splits(T, N, self.in_features) if (tc and kind != "float32") else 1
-        if kind == "delta" or (kind == "either" and nsplit > 1):
-            out = ws.get(buffer_name, (nsplit, T, N), torch.float32)
-            if tc:
-                ops.gemm_tc(a, self.weight, out if nsplit > 1 else out[0], nsplit)
-            else:
-                ops.gemm_simt(a, self.weight, out[0])
-            return out
-        out = ws.get(buffer_name, (T, N), torch.float32 if kind == "float32" else self.env.dtype)
-        if tc:
-            ops.gemm_tc(a, self.weight, out, 1)
+        # K slices of the tensor-core kernel add up inside a thread-block cluster, so every
+        # kind of consumer gets finished sums; S stays 1
+        nsplit = ops.gemm_tc_splits(T, N, self.in_features) if tc else 1
+        if kind == "delta":
+            out = ws.get(buffer_name, (1, T, N), torch.float32)
+            target = out[0]
         else:
-            ops.gemm_simt(a, self.weight, out)
+            out = ws.get(buffer_name, (T, N), torch.float32 if kind == "float32" else self.env.dtype)
+            target = out
+        if tc and nsplit == 1 and ops.gemm_tc_prefers_dual(T, N, self.in_features):
+            ops.gemm_tc_dual(a, self.weight, target)
+        elif tc:
+            ops.gemm_tc(a, self.weight, target, nsplit, reduce=nsplit > 1)
+        else:
+            ops.gemm_simt(a, self.weight, target)
+        return out
+
+    def forward_gated(self, a: torch.Tensor, buffer_name: str) -> Optional[torch.Tensor]:
+        """For a weight that stacks gate rows over up rows: ``silu(a W_gate^T) * (a W_up^T)`` in
+        one kernel, ``[T, out/2]`` in the activation type; None when the shape is not one the
+        fused kernel is used for (the caller then multiplies and activates separately)."""
+        T = a.shape[0]
+        if not self.uses_tensor_cores() or T <= 64 or self.out_features % 2:
+            return None
+        out = self.env.workspace.get(buffer_name, (T, self.out_features // 2), self.env.dtype)
+        ops.gemm_tc_dual(a, self.weight, out, swiglu=True)
         return out

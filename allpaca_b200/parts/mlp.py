@@ -39,7 +39,9 @@ class SwiGLU(FeedForward):
 
     def forward(self, h: torch.Tensor, step) -> torch.Tensor:
         T = h.shape[0]
-        gu = self.gate_up.forward(h, "ffn.gate_up", "either")
-        act = self.env.workspace.get("ffn.act", (T, self.inter), self.env.dtype)
-        ops.swiglu(gu, act)
+        act = self.gate_up.forward_gated(h, "ffn.act")        # one kernel when there are many rows
+        if act is None:
+            gu = self.gate_up.forward(h, "ffn.gate_up", "either")
+            act = self.env.workspace.get("ffn.act", (T, self.inter), self.env.dtype)
+            ops.swiglu(gu, act)
         return self.down.forward(act, "ffn.down", "delta")

@@ -125,7 +125,9 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
+    ap.add_argument("--prefill-only", action="store_true", help="time only the prefill (for profilers)")
     ap.add_argument("--seed", type=int, default=2)
+    ap.add_argument("--l2-prefetch-mb", type=int, default=0, help="weight bytes a GEMM may prefetch into L2 early")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profilers)")
     args = ap.parse_args()
 
@@ -148,6 +150,7 @@ def main() -> int:
     from allpaca_b200.weights.random_model import random_model_on_device
 
     pk = peaks()
+    library.core().ap_gemm_tc_set_l2_prefetch(args.l2_prefetch_mb << 20)
     raw = preset_config(args.preset)
     full_layers = raw["num_hidden_layers"]
     layers = args.layers or full_layers
@@ -263,6 +266,11 @@ def main() -> int:
             + layers * 4.0 * cfg.q_size * tokens_n * (tokens_n + 1) / 2
         return best, flops
 
+    if args.prefill_only:
+        pms, flops = prefill_run(args.prefill_tokens)
+        print(json.dumps({"prefill_ms": round(pms, 3), "tokens": args.prefill_tokens, "layers": layers,
+                          "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}))
+        return 0
     value, ms, e2e, launches, h2d, d2h, clocks = decode_run(args.batch, args.steps, args.warmup, True)
     ctx_mid = args.context - (args.steps + 2) // 2
     step_bytes = 2.0 * linear_elems + args.batch * ctx_mid * kv_per_token

@@ -1,0 +1,48 @@
+"""The tensor-core matrix product with its K slices added inside a thread-block cluster."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(got, ref):
+    return float((got.double().cpu() - ref).abs().max() / ref.abs().max())
+
+
+@pytest.mark.parametrize("M,N,K,S", [(1, 128, 512, 2), (8, 301, 1000, 3), (16, 256, 4096, 8), (8, 4096, 4096, 7),
+                                     (64, 384, 1024, 4), (5, 640, 14336, 8), (33, 130, 640, 5), (17, 6144, 4096, 6)])
+@pytest.mark.parametrize("odtype", [torch.float32, torch.bfloat16])
+def test_cluster_reduction(M, N, K, S, odtype):
+    from allpaca_b200 import ops
+    g = torch.Generator().manual_seed(S + M)
+    a = torch.randn(M, K, generator=g).bfloat16()
+    w = torch.randn(N, K, generator=g).bfloat16()
+    out = torch.full((M + 1, N), 7.0, dtype=odtype, device="cuda")
+    ops.gemm_tc(a.cuda(), w.cuda(), out[:M], S, reduce=True)
+    ops.check_kernel_status()
+    ref = a.double() @ w.double().T
+    assert rel_err(out[:M], ref) < (1e-5 if odtype == torch.float32 else 5e-3)
+    assert torch.all(out[M:] == 7.0)
+    # the same product twice gives the same bits: slices are added in a fixed order
+    again = torch.empty(M, N, dtype=odtype, device="cuda")
+    ops.gemm_tc(a.cuda(), w.cuda(), again, S, reduce=True)
+    assert torch.equal(again, out[:M])
+
+
+def test_plan_stays_within_a_cluster():
+    from allpaca_b200 import ops
+    for M in (1, 8, 16, 33, 64):
+        for N, K in ((4096, 4096), (6144, 4096), (28672, 4096), (4096, 14336), (128256, 4096), (96, 64)):
+            s = ops.gemm_tc_splits(M, N, K)
+            kb = -(-K // 64)
+            assert 1 <= s <= 8 and (s - 1) * (-(-kb // s)) < kb
+    assert ops.gemm_tc_splits(65, 4096, 4096) == 1 and ops.gemm_tc_splits(2048, 4096, 4096) == 1
+
+
+def test_cluster_reduction_refuses_too_many_slices():
+    from allpaca_b200 import ops
+    a = torch.randn(4, 4608).bfloat16().cuda()
+    w = torch.randn(128, 4608).bfloat16().cuda()
+    out = torch.empty(4, 128, device="cuda")
+    with pytest.raises(ops.KernelError, match="cluster"):
+        ops.gemm_tc(a, w, out, 9, reduce=True)
