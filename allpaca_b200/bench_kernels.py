@@ -81,6 +81,9 @@ def _paged(batch, context, nkv, hd, P):
 
 def bench_attention(args) -> dict:
     from allpaca_b200 import ops
+    if args.splits:
+        forced = args.splits
+        ops.decode_splits = lambda *a, **k: forced          # try a slice count other than the plan's
     B, C, nh, nkv, hd, P = args.batch, args.context, args.heads, args.kv_heads, args.head_dim, args.page_size
     per = B * C * 2 * nkv * hd * 2
     copies = max(2, int(math.ceil(300e6 / per)))
@@ -162,6 +165,7 @@ def main(argv=None) -> int:
             s.add_argument("--context", type=int, default=4096)
             s.add_argument("--tokens", type=int, default=2048)
             s.add_argument("--separate-merge", action="store_true", help="combine key slices in a second kernel")
+            s.add_argument("--splits", type=int, default=0, help="key slices (0: the kernel's own plan)")
     args = p.parse_args(argv)
     fn = {"gemm": bench_gemm, "attention": bench_attention, "prefill-attention": bench_prefill_attention}[args.what]
     print(json.dumps(fn(args)))

@@ -129,7 +129,8 @@ template <int NT>
 __device__ __forceinline__ void process_keys(const uint8_t* ks, const uint8_t* vs, int key0, int k0,
                                              const uint32_t (&qf)[KSTEPS][4], float (&o)[DTILES][4],
                                              float (&m)[2], float (&l)[2], const int (&qpos)[2],
-                                             const bool (&rvalid)[2], int window, float scale_log2) {
+                                             const bool (&rvalid)[2], int window, float scale_log2,
+                                             bool all_visible = false) {
     const int lane = threadIdx.x & 31;
     const int mi = lane >> 3, r8 = lane & 7;
     float s[NT][4];
@@ -148,18 +149,30 @@ __device__ __forceinline__ void process_keys(const uint8_t* ks, const uint8_t* v
             mma_16816(s[2 * np + 1], qf[kk], b[2], b[3]);
         }
     }
-    // scale, mask, running maximum
+    // scale, mask, running maximum (a tile every row of the warp sees whole needs no mask)
     float mx[2] = {-INFINITY, -INFINITY};
+    if (all_visible) {
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
+        for (int j = 0; j < NT; ++j) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int h = e >> 1;
-            const int kpos = k0 + key0 + j * 8 + (lane & 3) * 2 + (e & 1);
-            const bool ok = rvalid[h] && kpos <= qpos[h] && (window <= 0 || qpos[h] - kpos < window);
-            const float v = ok ? s[j][e] * scale_log2 : -INFINITY;
-            s[j][e] = v;
-            mx[h] = fmaxf(mx[h], v);
+            for (int e = 0; e < 4; ++e) {
+                const float v = s[j][e] * scale_log2;
+                s[j][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = e >> 1;
+                const int kpos = k0 + key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+                const bool ok = rvalid[h] && kpos <= qpos[h] && (window <= 0 || qpos[h] - kpos < window);
+                const float v = ok ? s[j][e] * scale_log2 : -INFINITY;
+                s[j][e] = v;
+                mx[h] = fmaxf(mx[h], v);
+            }
         }
     }
     float alpha[2], muse[2];
@@ -227,7 +240,8 @@ attention_tile_kernel(const AttnTcParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ int s_seq, s_tile;
     if (threadIdx.x == 0) {
-        int t = blockIdx.x, found = -1;
+        // late tiles of a sequence have the most keys to walk: hand them out first
+        int t = gridDim.x - 1 - blockIdx.x, found = -1;
         for (int s = 0; s < p.nseq; ++s) {
             const int n = p.seq_start[s + 1] - p.seq_start[s];
             const int nt = (n + p.tokens_per_tile - 1) / p.tokens_per_tile;
@@ -284,6 +298,12 @@ attention_tile_kernel(const AttnTcParams p) {
     wm = max(wm, __shfl_xor_sync(0xffffffffu, wm, 4));
     wm = max(wm, __shfl_xor_sync(0xffffffffu, wm, 8));
     wm = max(wm, __shfl_xor_sync(0xffffffffu, wm, 16));
+    // ... and the first (-1 unless every row of the warp is valid): tiles that end at or
+    // before it are visible to all rows of the warp and need no mask
+    int wmin = (rvalid[0] && rvalid[1]) ? min(qpos[0], qpos[1]) : -1;
+    wmin = min(wmin, __shfl_xor_sync(0xffffffffu, wmin, 4));
+    wmin = min(wmin, __shfl_xor_sync(0xffffffffu, wmin, 8));
+    wmin = min(wmin, __shfl_xor_sync(0xffffffffu, wmin, 16));
 
     const int t_lo = kmin / BKV, t_hi = kmax / BKV;
     fetch_tile(smem, 0, t_lo * BKV, kmin, kmax, p.cache, table, p.P, p.page_stride, head_off, v_off);
@@ -297,8 +317,11 @@ attention_tile_kernel(const AttnTcParams p) {
         __syncthreads();
         const uint8_t* ks = smem + cur * SmemLayout::kStage;
         // a warp whose rows all sit before this tile has nothing to add (causal)
-        if (wm >= t * BKV)
-            process_keys<8>(ks, ks + TILE_BYTES, 0, t * BKV, qf, o, m, l, qpos, rvalid, p.window, p.scale_log2);
+        if (wm >= t * BKV) {
+            const bool all_visible = t * BKV + BKV - 1 <= wmin && (p.window <= 0 || wm - t * BKV < p.window);
+            process_keys<8>(ks, ks + TILE_BYTES, 0, t * BKV, qf, o, m, l, qpos, rvalid, p.window, p.scale_log2,
+                            all_visible);
+        }
         __syncthreads();
     }
     cp_async_wait<0>();

@@ -71,8 +71,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const bool skip = *(volatile int*)&g_tc_status != 0;
     if (!CLUSTER && skip) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * TILE_W;
-    const int m0 = blockIdx.y * BN;
+    // blockIdx.x walks the row tiles: CTAs that share a weight tile run side by side, so the
+    // weight comes from HBM once and from L2 for the others
+    const int n0 = blockIdx.y * TILE_W;
+    const int m0 = blockIdx.x * BN;
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     const int kb0 = blockIdx.z * kb_per_split;
     const int kb1 = min(kb_total, kb0 + kb_per_split);
@@ -290,8 +292,8 @@ gemm_tc_dual_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // SWIGLU: N counts output columns (the intermediate size); tile x covers gate rows
     // [128x, 128x+128) and the up rows w1_offset further on.  Else tile x covers 256 rows.
-    const int n0 = blockIdx.x * (SWIGLU ? TILE_W : 2 * TILE_W);
-    const int m0 = blockIdx.y * BN;
+    const int n0 = blockIdx.y * (SWIGLU ? TILE_W : 2 * TILE_W);
+    const int m0 = blockIdx.x * BN;            // row tiles side by side: they share the weight tiles
     const int nkb = (K + TILE_K - 1) / TILE_K;
 
     if (threadIdx.x == 0) {
@@ -495,7 +497,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, in
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     const int per = (kb_total + nsplit - 1) / nsplit;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((N + TILE_W - 1) / TILE_W, (M + BN - 1) / BN, nsplit);
+    cfg.gridDim = dim3((M + BN - 1) / BN, (N + TILE_W - 1) / TILE_W, nsplit);
     cfg.blockDim = dim3(192);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -550,7 +552,7 @@ AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype,
                "gemm_tc: %d slices leave an empty one for K=%d", nsplit, K);
     AP_REQUIRE(out_dtype == AP_F32 || out_dtype == AP_BF16, "gemm_tc: unknown output dtype %d", out_dtype);
     const int bn = pick_bn(M);
-    AP_REQUIRE((M + bn - 1) / bn <= 65535, "gemm_tc: %d rows exceed the grid", M);
+    AP_REQUIRE((N + TILE_W - 1) / TILE_W <= 65535, "gemm_tc: %d output features exceed the grid", N);
     const bool cluster = reduce != 0 && nsplit > 1;
     AP_REQUIRE(!cluster || (nsplit <= AP_MAX_CLUSTER && bn <= 64),
                "gemm_tc: slices are added in a cluster only for up to %d slices and 64 rows (got %d, %d)",
@@ -593,7 +595,7 @@ static int launch_dual(const CUtensorMap& mw, const CUtensorMap& ma, void* out, 
         configured = true;
     }
     const int tile_n = SWIGLU ? TILE_W : 2 * TILE_W;
-    dim3 grid((N + tile_n - 1) / tile_n, (M + BN - 1) / BN, 1);
+    dim3 grid((M + BN - 1) / BN, (N + tile_n - 1) / tile_n, 1);
     AP_CHECK_PDL_LAUNCH("gemm_tc_dual", ap_launch_pdl(kern, grid, dim3(192), (size_t)Cfg::kSmemBytes, stream, mw, ma,
                                                       (TO*)out, M, N, K, ldc, w1_offset));
     return AP_OK;
@@ -612,7 +614,7 @@ AP_EXPORT int ap_gemm_tc_dual(const void* a, const void* w, void* out, int out_d
     AP_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_tc: a leading dimension is below its row length");
     AP_REQUIRE(out_dtype == AP_F32 || out_dtype == AP_BF16, "gemm_tc: unknown output dtype %d", out_dtype);
     const int bn = M <= 128 ? 128 : 256;
-    AP_REQUIRE((M + bn - 1) / bn <= 65535, "gemm_tc: %d rows exceed the grid", M);
+    AP_REQUIRE((N + TILE_W - 1) / TILE_W <= 65535, "gemm_tc: %d output features exceed the grid", N);
     CUtensorMap mw, ma;
     AP_REQUIRE(make_map(&mw, w, swiglu ? 2LL * N : N, K, ldw, TILE_W), "gemm_tc: cannot encode the weight's tensor map");
     AP_REQUIRE(make_map(&ma, a, M, K, lda, bn), "gemm_tc: cannot encode the activations' tensor map");

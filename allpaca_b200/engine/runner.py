@@ -58,7 +58,7 @@ class ModelRunner:
         self._staging_cap = 0
         self._host = None
         self._dev = None
-        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graphs: Dict[tuple, "_DecodeGraph"] = {}
 
     # ---- caches ---------------------------------------------------------
     def _setup_caches(self) -> None:
@@ -138,11 +138,19 @@ class ModelRunner:
         contents change between replays.  A graph is captured again when a workspace
         buffer it points to has been replaced."""
         B = len(entries)
-        gs = self._graphs.get(B)
+        # the number of key slices of the attention kernel is part of the graph: graphs are kept
+        # per power-of-two bound on the longest context, so it suits the contexts it serves
+        longest = max(self.cache.num_tokens(en.request) if self.cache.has(en.request) else 0
+                      for en in entries) + 1
+        bound = 256
+        while bound < longest:
+            bound *= 2
+        bound = min(bound, max(self.max_model_len, 256))
+        gs = self._graphs.get((B, bound))
         if gs is None:
-            gs = self._graphs[B] = _DecodeGraph(self, B)
+            gs = self._graphs[(B, bound)] = _DecodeGraph(self, B)
         batch = self.prepare(entries, staging=gs, widths=gs.widths)
-        batch.max_context_len = self.max_model_len       # fixes the number of key slices
+        batch.max_context_len = bound
         if gs.graph is not None and gs.generation == self.workspace.generation:
             gs.graph.replay()
             library.add_launches(gs.num_kernels)
