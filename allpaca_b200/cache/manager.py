@@ -1,28 +1,31 @@
-"""Bookkeeping of cache pages, block tables and state slots (host side, no tensors).
+"""Cache pages, block tables and state slots: the Python face of the C++ cache manager.
 
-Keys and values live in fixed-size pages.  Layers with the same need form a *group*
-with a page pool of its own: a group either keeps every key of a request (``window``
-None) or only a trailing window of them, in which case pages the window has passed
-go back to the pool while the request is still running.  Each request has, per
-group, a block table: logical page index -> page id (``FREED`` where the page was
-given back).  Beside the pages there are slots for per-request state of fixed size,
-one per running request, whatever the architecture keeps in them.
+The bookkeeping itself is C++ (``csrc/host/cache_manager.cpp``, built on first use with the
+C++ compiler alone, so it runs where there is no GPU); this module maps request ids to
+handles, turns status codes into exceptions and hands block tables back as lists.
 
-Role in the reference: ``KvTierManager`` page allocation and release
-(crates/allpaca-core/src/kv_tier.rs:341-474, :498-532), the per-request page lists of
-``ActiveRequest`` (crates/allpaca-core/src/engine.rs:97) released on drop
-(engine.rs:409-432), growth by ``ensure_pages`` (crates/allpaca-core/src/model.rs:13452-13480)
-and the per-request recurrent state (crates/allpaca-core/src/anchors.rs:16-56).  The
-reference allocates a page per layer and evicts to slower tiers when VRAM is full;
-here one page id addresses the same page in every layer of its group, there is one
-tier, and running out of pages is reported to the scheduler.
+Keys and values live in fixed-size pages.  Layers with the same need form a *group* with a
+page pool of its own: a group either keeps every key of a request (``window`` None) or only a
+trailing window of them, in which case pages the window has passed go back to the pool while
+the request is still running.  Each request has, per group, a block table: logical page index
+-> page id (``FREED`` where the page was given back).  Beside the pages there are slots for
+per-request state of fixed size, one per running request, whatever the architecture keeps in
+them.
+
+Role in the reference: ``KvTierManager`` (crates/allpaca-core/src/kv_tier.rs:341-474,
+:498-532), the per-request page lists released on drop (crates/allpaca-core/src/engine.rs:97,
+:409-432), ``ensure_pages`` (crates/allpaca-core/src/model.rs:13452-13480) and the per-request
+recurrent state (crates/allpaca-core/src/anchors.rs:16-56).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from ctypes import POINTER, c_int, c_int32, c_int64, c_void_p, c_char_p
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 
 FREED = -1
+_OK, _MISUSE, _OUT_OF_PAGES = 0, 1, 2
 
 
 class CacheError(RuntimeError):
@@ -33,6 +36,59 @@ class OutOfPages(RuntimeError):
     """A group's pool cannot supply the pages asked for; nothing was changed."""
 
 
+_lib = None
+
+
+def host_library() -> ctypes.CDLL:
+    """The C++ host library, built on first use."""
+    global _lib
+    if _lib is None:
+        from ..csrc import build
+        lib = ctypes.CDLL(build.build_host())
+        lib.apc_last_error.restype = c_char_p
+        lib.apc_pool_create.restype = c_void_p
+        lib.apc_pool_create.argtypes = [c_int]
+        for name in ("apc_pool_destroy",):
+            getattr(lib, name).argtypes = [c_void_p]
+            getattr(lib, name).restype = None
+        for name, args in {
+            "apc_pool_alloc": [c_void_p], "apc_pool_free": [c_void_p, c_int], "apc_pool_num_free": [c_void_p],
+            "apc_pool_held": [c_void_p, c_int],
+            "apc_cache_begin": [c_void_p, c_int64, POINTER(c_int)], "apc_cache_free": [c_void_p, c_int64],
+            "apc_cache_has": [c_void_p, c_int64], "apc_cache_num_running": [c_void_p],
+            "apc_cache_can_begin": [c_void_p], "apc_cache_num_free_pages": [c_void_p, c_int],
+            "apc_cache_state_slot": [c_void_p, c_int64],
+            "apc_cache_pages_missing": [c_void_p, c_int64, c_int64, POINTER(c_int)],
+            "apc_cache_can_append": [c_void_p, c_int64, c_int64, POINTER(c_int)],
+            "apc_cache_append": [c_void_p, c_int64, c_int64, POINTER(c_int64)],
+            "apc_cache_release_passed": [c_void_p, c_int64, POINTER(c_int)], "apc_cache_check": [c_void_p],
+            "apc_cache_table": [c_void_p, c_int64, c_int, POINTER(c_int), c_int],
+        }.items():
+            getattr(lib, name).argtypes = args
+            getattr(lib, name).restype = c_int
+        lib.apc_cache_num_tokens.argtypes = [c_void_p, c_int64]
+        lib.apc_cache_num_tokens.restype = c_int64
+        lib.apc_cache_create.argtypes = [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]
+        lib.apc_cache_create.restype = c_void_p
+        lib.apc_cache_destroy.argtypes = [c_void_p]
+        lib.apc_cache_destroy.restype = None
+        lib.apc_prepare_step.argtypes = [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                         c_void_p]
+        lib.apc_prepare_step.restype = c_int
+        _lib = lib
+    return _lib
+
+
+def _raise(status: int, what: str = "") -> None:
+    msg = host_library().apc_last_error().decode() or what
+    if what and what not in msg:
+        msg = f"{what}: {msg}"
+    if status == _OUT_OF_PAGES:
+        raise OutOfPages(msg)
+    raise CacheError(msg)
+
+
 class PagePool:
     """Page ids ``0 .. n-1`` with a last-in-first-out free list, so a page that was just
     given back is the next one handed out."""
@@ -41,32 +97,31 @@ class PagePool:
         if num_pages <= 0:
             raise CacheError(f"a page pool needs at least one page, got {num_pages}")
         self.num_pages = int(num_pages)
-        self._free: List[int] = list(range(self.num_pages - 1, -1, -1))
-        self._held = [False] * self.num_pages
+        self._lib = host_library()
+        self._h = self._lib.apc_pool_create(self.num_pages)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.apc_pool_destroy(self._h)
+            self._h = None
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.apc_pool_num_free(self._h)
 
     def alloc(self) -> int:
-        if not self._free:
+        p = self._lib.apc_pool_alloc(self._h)
+        if p < 0:
             raise OutOfPages("the page pool is empty")
-        p = self._free.pop()
-        if self._held[p]:
-            raise CacheError(f"page {p} was on the free list while held")
-        self._held[p] = True
         return p
 
     def free(self, page: int) -> None:
-        if not (0 <= page < self.num_pages):
-            raise CacheError(f"page {page} is outside the pool of {self.num_pages}")
-        if not self._held[page]:
-            raise CacheError(f"page {page} is freed twice")
-        self._held[page] = False
-        self._free.append(page)
+        rc = self._lib.apc_pool_free(self._h, int(page))
+        if rc != _OK:
+            _raise(rc)
 
     def held(self) -> List[int]:
-        return [p for p, h in enumerate(self._held) if h]
+        return [p for p in range(self.num_pages) if self._lib.apc_pool_held(self._h, p)]
 
 
 @dataclass(frozen=True)
@@ -78,147 +133,167 @@ class GroupLayout:
     window: Optional[int] = None
 
 
-@dataclass
-class _Sequence:
-    tables: List[List[int]]
-    num_tokens: int = 0
-    state_slot: int = -1
-
-
 class CacheManager:
     """Pages, block tables and state slots of all running requests."""
 
     def __init__(self, groups: Sequence[GroupLayout], max_seqs: int):
         if max_seqs <= 0:
             raise CacheError("max_seqs must be positive")
+        if len(groups) > 8:
+            raise CacheError("at most 8 cache groups are supported")
         for g in groups:
             if g.page_size <= 0:
                 raise CacheError("page_size must be positive")
+            if g.num_pages <= 0:
+                raise CacheError(f"a page pool needs at least one page, got {g.num_pages}")
             if g.window is not None and g.window <= 0:
                 raise CacheError("a window must be positive")
         self.groups = list(groups)
-        self.pools = [PagePool(g.num_pages) for g in self.groups]
         self.max_seqs = int(max_seqs)
-        self._free_slots: List[int] = list(range(self.max_seqs - 1, -1, -1))
-        self._seqs: Dict[Hashable, _Sequence] = {}
+        self._lib = host_library()
+        n = len(self.groups)
+        arr = c_int * max(n, 1)
+        self._h = self._lib.apc_cache_create(
+            n, arr(*[g.page_size for g in self.groups]), arr(*[g.num_pages for g in self.groups]),
+            arr(*[(g.window or -1) for g in self.groups]), self.max_seqs)
+        if not self._h:
+            raise CacheError("the cache manager could not be created")
+        self._handles: Dict[Hashable, int] = {}
+        self._next = 0
+        self._ints = (c_int * max(n, 1))()
 
-    # ---- requests -------------------------------------------------------
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.apc_cache_destroy(self._h)
+            self._h = None
+
+    # ---- handles ----------------------------------------------------------
+    def handle(self, req: Hashable) -> int:
+        """The integer the C++ side knows a request by (-1: it holds no cache)."""
+        return self._handles.get(req, -1)
+
+    @property
+    def native(self) -> int:
+        """The C++ object, for other native code (the step builder)."""
+        return self._h
+
+    def _need(self, req: Hashable) -> int:
+        try:
+            return self._handles[req]
+        except KeyError:
+            raise CacheError(f"request {req!r} holds no cache") from None
+
+    # ---- requests ---------------------------------------------------------
     def has(self, req: Hashable) -> bool:
-        return req in self._seqs
+        return req in self._handles
 
     def num_running(self) -> int:
-        return len(self._seqs)
+        return len(self._handles)
 
     def can_begin(self) -> bool:
-        return bool(self._free_slots)
+        return bool(self._lib.apc_cache_can_begin(self._h))
 
     def begin(self, req: Hashable) -> int:
         """Register a request and give it a state slot.  Returns the slot."""
-        if req in self._seqs:
+        if req in self._handles:
             raise CacheError(f"request {req!r} already holds a cache")
-        if not self._free_slots:
-            raise OutOfPages("every state slot is taken")
-        slot = self._free_slots.pop()
-        self._seqs[req] = _Sequence(tables=[[] for _ in self.groups], state_slot=slot)
-        return slot
+        h = self._next
+        slot = c_int(-1)
+        rc = self._lib.apc_cache_begin(self._h, h, ctypes.byref(slot))
+        if rc != _OK:
+            _raise(rc)
+        self._next += 1
+        self._handles[req] = h
+        return slot.value
+
+    def adopt(self, req: Hashable) -> int:
+        """Reserve the handle a new request will get from native code that begins it
+        (the step builder); returns it."""
+        h = self._next
+        self._next += 1
+        self._handles[req] = h
+        return h
+
+    def forget(self, req: Hashable) -> None:
+        """Drop a handle reserved with :meth:`adopt` whose request never began."""
+        self._handles.pop(req, None)
 
     def free(self, req: Hashable) -> None:
         """Give back everything the request holds."""
-        seq = self._seqs.pop(req, None)
-        if seq is None:
+        h = self._handles.pop(req, None)
+        if h is None:
             raise CacheError(f"request {req!r} holds no cache (freed twice?)")
-        for g, table in enumerate(seq.tables):
-            for page in reversed(table):
-                if page != FREED:
-                    self.pools[g].free(page)
-        self._free_slots.append(seq.state_slot)
+        rc = self._lib.apc_cache_free(self._h, h)
+        if rc != _OK:
+            _raise(rc, f"request {req!r}")
 
-    # ---- pages ----------------------------------------------------------
+    # ---- pages ------------------------------------------------------------
     def num_tokens(self, req: Hashable) -> int:
-        return self._seq(req).num_tokens
+        return int(self._lib.apc_cache_num_tokens(self._h, self._need(req)))
 
     def state_slot(self, req: Hashable) -> int:
-        return self._seq(req).state_slot
+        return int(self._lib.apc_cache_state_slot(self._h, self._need(req)))
 
     def pages_missing(self, req: Optional[Hashable], num_new: int, have_tokens: int = 0) -> List[int]:
         """Pages each group still has to allocate so that ``num_new`` more tokens fit.
-        ``req`` None asks for a request that has not begun (``have_tokens`` = 0)."""
-        out = []
-        for g, layout in enumerate(self.groups):
-            if req is None:
-                have_pages, total = 0, have_tokens + num_new
-            else:
-                seq = self._seq(req)
-                have_pages, total = len(seq.tables[g]), seq.num_tokens + num_new
-            need = -(-total // layout.page_size)
-            out.append(max(0, need - have_pages))
-        return out
+        ``req`` None asks for a request that has not begun."""
+        h = -1 if req is None else self._need(req)
+        rc = self._lib.apc_cache_pages_missing(self._h, h, int(num_new) + int(have_tokens), self._ints)
+        if rc != _OK:
+            _raise(rc)
+        return [self._ints[g] for g in range(len(self.groups))]
 
     def can_append(self, req: Optional[Hashable], num_new: int, reserve: Optional[Sequence[int]] = None) -> bool:
-        """Whether :meth:`append` would succeed.  ``reserve[g]`` pages of each pool are
-        treated as already spoken for (by other requests of the same step)."""
-        for g, miss in enumerate(self.pages_missing(req, num_new)):
-            taken = reserve[g] if reserve is not None else 0
-            if miss > self.pools[g].num_free - taken:
-                return False
-        return True
+        """Whether :meth:`append` would succeed.  ``reserve[g]`` pages of each pool are treated
+        as already spoken for (by other requests of the same step)."""
+        h = -1 if req is None else self._need(req)
+        res = None
+        if reserve is not None:
+            res = (c_int * max(len(self.groups), 1))(*[int(r) for r in reserve])
+        return bool(self._lib.apc_cache_can_append(self._h, h, int(num_new), res))
 
     def append(self, req: Hashable, num_new: int) -> int:
-        """Make room for ``num_new`` more tokens and count them as held.  Returns the
-        position of the first new token.  On :class:`OutOfPages` nothing has changed."""
-        if num_new <= 0:
-            raise CacheError("append needs at least one token")
-        seq = self._seq(req)
-        missing = self.pages_missing(req, num_new)
-        for g, miss in enumerate(missing):
-            if miss > self.pools[g].num_free:
-                raise OutOfPages(
-                    f"group {g} needs {miss} more pages for request {req!r}, "
-                    f"{self.pools[g].num_free} are free")
-        for g, miss in enumerate(missing):
-            for _ in range(miss):
-                seq.tables[g].append(self.pools[g].alloc())
-        first = seq.num_tokens
-        seq.num_tokens += num_new
-        return first
+        """Make room for ``num_new`` more tokens and count them as held.  Returns the position
+        of the first new token.  On :class:`OutOfPages` nothing has changed."""
+        first = c_int64(0)
+        rc = self._lib.apc_cache_append(self._h, self._need(req), int(num_new), ctypes.byref(first))
+        if rc != _OK:
+            _raise(rc, f"request {req!r}")
+        return int(first.value)
 
     def release_passed(self, req: Hashable) -> int:
-        """Give back pages of windowed groups that no later token of the request can
-        see.  Call after the step that computed the held tokens.  Returns pages freed."""
-        seq = self._seq(req)
-        freed = 0
-        for g, layout in enumerate(self.groups):
-            if layout.window is None:
-                continue
-            # the next row sits at position num_tokens and sees keys > num_tokens - window
-            first_visible = seq.num_tokens - layout.window + 1
-            if first_visible <= 0:
-                continue
-            dead_pages = min(first_visible // layout.page_size, len(seq.tables[g]))
-            table = seq.tables[g]
-            for j in range(dead_pages):
-                if table[j] != FREED:
-                    self.pools[g].free(table[j])
-                    table[j] = FREED
-                    freed += 1
-        return freed
+        """Give back pages of windowed groups that no later token of the request can see.
+        Call after the step that computed the held tokens.  Returns pages freed."""
+        freed = c_int(0)
+        rc = self._lib.apc_cache_release_passed(self._h, self._need(req), ctypes.byref(freed))
+        if rc != _OK:
+            _raise(rc)
+        return freed.value
+
+    def has_windows(self) -> bool:
+        return any(g.window is not None for g in self.groups)
 
     def block_table(self, req: Hashable, group: int) -> List[int]:
-        return self._seq(req).tables[group]
+        h = self._need(req)
+        n = self._lib.apc_cache_table(self._h, h, int(group), None, 0)
+        if n < 0:
+            raise CacheError(f"request {req!r} has no group {group}")
+        buf = (c_int * max(n, 1))()
+        self._lib.apc_cache_table(self._h, h, int(group), buf, n)
+        return list(buf[:n])
 
     def slot(self, req: Hashable, group: int, position: int) -> int:
         """``page * page_size + offset`` of a held position; its page must be live."""
-        layout = self.groups[group]
-        table = self._seq(req).tables[group]
-        j = position // layout.page_size
+        P = self.groups[group].page_size
+        table = self.block_table(req, group)
+        j = position // P
         if j >= len(table) or table[j] == FREED:
             raise CacheError(f"position {position} of request {req!r} has no live page in group {group}")
-        return table[j] * layout.page_size + position % layout.page_size
+        return table[j] * P + position % P
 
     def slots(self, req: Hashable, group: int, first: int, count: int) -> List[int]:
-        layout = self.groups[group]
-        table = self._seq(req).tables[group]
-        P = layout.page_size
+        P = self.groups[group].page_size
+        table = self.block_table(req, group)
         out = []
         for pos in range(first, first + count):
             page = table[pos // P]
@@ -227,32 +302,14 @@ class CacheManager:
             out.append(page * P + pos % P)
         return out
 
-    # ---- inspection -----------------------------------------------------
+    # ---- inspection -------------------------------------------------------
     def num_free_pages(self, group: int = 0) -> int:
-        return self.pools[group].num_free
+        return int(self._lib.apc_cache_num_free_pages(self._h, int(group)))
 
     def check(self) -> None:
         """Every page is either free or held by exactly one request."""
-        for g, pool in enumerate(self.pools):
-            owners: Dict[int, Hashable] = {}
-            for req, seq in self._seqs.items():
-                for page in seq.tables[g]:
-                    if page == FREED:
-                        continue
-                    if page in owners:
-                        raise CacheError(f"page {page} of group {g} is held by {owners[page]!r} and {req!r}")
-                    owners[page] = req
-            held = set(pool.held())
-            if held != set(owners):
-                raise CacheError(f"group {g}: pool holds {sorted(held)}, requests hold {sorted(owners)}")
-            if len(held) + pool.num_free != pool.num_pages:
-                raise CacheError(f"group {g}: {len(held)} held + {pool.num_free} free != {pool.num_pages}")
-        slots = [s.state_slot for s in self._seqs.values()]
-        if len(set(slots)) != len(slots) or len(slots) + len(self._free_slots) != self.max_seqs:
-            raise CacheError("state slots are lost or held twice")
-
-    def _seq(self, req: Hashable) -> _Sequence:
-        try:
-            return self._seqs[req]
-        except KeyError:
-            raise CacheError(f"request {req!r} holds no cache") from None
+        rc = self._lib.apc_cache_check(self._h)
+        if rc != _OK:
+            _raise(rc)
+        if self._lib.apc_cache_num_running(self._h) != len(self._handles):
+            raise CacheError("the request table and the native cache manager disagree")

@@ -1,7 +1,9 @@
 """Builds the CUDA kernel libraries of this package with nvcc, for sm_100a only.
 
-Two kinds of shared library are produced, each from the sources in this folder:
+Three kinds of shared library are produced, each from the sources in this folder:
 
+* ``host``: the C++ host code (cache manager, step builder), built with the C++ compiler
+  alone, so it also builds and is tested where there is no GPU.
 * ``core``: every kernel that does not depend on a model size known only at run
   time (row-wise kernels, matrix products, sampling).
 * ``attn<HD>``: the attention kernels specialised for one head size, built on
@@ -103,7 +105,7 @@ class _Progress:
                   file=sys.stderr, flush=True)
 
     def __enter__(self):
-        print(f"[allpaca_b200] compiling {self.what} for sm_100a", file=sys.stderr, flush=True)
+        print(f"[allpaca_b200] compiling {self.what} ", file=sys.stderr, flush=True)
         self._t.start()
         return self
 
@@ -161,6 +163,46 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
     return lib
 
 
+HOST_SOURCES = ["host/cache_manager.cpp", "host/step_builder.cpp", "host/c_api.cpp"]
+HOST_HEADERS = ["host/cache_manager.hpp", "host/step_builder.hpp"]
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and (os.path.isfile(cand) or shutil.which(cand)):
+            return cand
+    raise BuildError("no C++ compiler was found (looked at $CXX, g++, c++, clang++)")
+
+
+def build_host(verbose: bool = False) -> str:
+    """The host library (cache manager, step builder): plain C++, no CUDA needed."""
+    flags = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+    h = hashlib.sha256()
+    for n in HOST_SOURCES + HOST_HEADERS:
+        with open(os.path.join(CSRC, n), "rb") as f:
+            h.update(n.encode())
+            h.update(f.read())
+    h.update(" ".join(flags).encode())
+    tag = h.hexdigest()[:16]
+    out_dir = build_dir()
+    lib = os.path.join(out_dir, f"liballpaca_host.{tag}.so")
+    if os.path.isfile(lib):
+        return lib
+    with _Progress("allpaca_host (" + ", ".join(HOST_SOURCES) + ")"):
+        tmp = lib + f".tmp{os.getpid()}"
+        log = _run([find_cxx()] + flags + ["-o", tmp] + [os.path.join(CSRC, s) for s in HOST_SOURCES])
+        os.replace(tmp, lib)
+    if verbose:
+        print(log, file=sys.stderr)
+    for f in os.listdir(out_dir):
+        if f.startswith("liballpaca_host.") and f.endswith(".so") and f != os.path.basename(lib):
+            try:
+                os.remove(os.path.join(out_dir, f))
+            except OSError:
+                pass
+    return lib
+
+
 def build_core(verbose: bool = False) -> str:
     return build_library("allpaca_core", CORE_SOURCES, verbose=verbose)
 
@@ -179,7 +221,7 @@ def build_attention(head_dim: int, verbose: bool = False) -> str:
 
 
 def build_all(head_dims: Sequence[int] = (16, 32, 64, 128), verbose: bool = False) -> Dict[str, str]:
-    out = {"core": build_core(verbose)}
+    out = {"host": build_host(verbose), "core": build_core(verbose)}
     for hd in head_dims:
         out[f"attn{hd}"] = build_attention(hd, verbose)
     return out

@@ -8,9 +8,12 @@ __all__ = ["BatchEntry", "StepBatch", "AdmissionError", "FinishReason", "Request
 
 
 def __getattr__(name):
-    if name in ("ModelRunner", "StepError"):
-        from . import runner
-        return getattr(runner, name)
+    if name == "StepError":
+        from .step_builder import StepError
+        return StepError
+    if name == "ModelRunner":
+        from .runner import ModelRunner
+        return ModelRunner
     if name in ("LLM", "RequestOutput"):
         from . import llm
         return getattr(llm, name)

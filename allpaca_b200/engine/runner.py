@@ -24,10 +24,7 @@ from ..parts import BuildEnv, Workspace
 from ..weights import load_checkpoint
 from ..ops import library
 from .batch import BatchEntry, StepBatch
-
-
-class StepError(ValueError):
-    """A batch the step function cannot run (caller's mistake); nothing was changed."""
+from .step_builder import StepError, build_step
 
 
 class ModelRunner:
@@ -119,8 +116,9 @@ class ModelRunner:
         else:
             batch = self.prepare(entries)
             logits = self.model.forward(batch)
-        for en in entries:
-            self.cache.release_passed(en.request)
+        if self.cache.has_windows():
+            for en in entries:
+                self.cache.release_passed(en.request)
         return logits
 
     # ---- decode steps as CUDA graphs ------------------------------------
@@ -170,111 +168,43 @@ class ModelRunner:
 
     def prepare(self, entries: Sequence[BatchEntry], staging=None, widths=None) -> StepBatch:
         """Check the batch, allocate its pages and upload its metadata (into ``staging``'s
-        fixed buffers with the given block-table widths, when given)."""
-        if not entries:
-            raise StepError("a step needs at least one entry")
-        seen = set()
-        T = 0
-        for en in entries:
-            if en.request in seen:
-                raise StepError(f"request {en.request!r} appears twice in one step")
-            seen.add(en.request)
-            n = len(en.tokens)
-            if n == 0:
-                raise StepError(f"request {en.request!r} brings no tokens")
-            arr = np.asarray(en.tokens, dtype=np.int64)
-            if arr.min() < 0 or arr.max() >= self.vocab_size:
-                # crates/allpaca-core/src/model.rs:8215-8219
-                bad = int(arr[(arr < 0) | (arr >= self.vocab_size)][0])
-                raise StepError(f"token {bad} out of vocab {self.vocab_size}")
-            for w in en.want:
-                if not (0 <= int(w) < n):
-                    raise StepError(f"request {en.request!r} wants row {w} of {n}")
-            held = self.cache.num_tokens(en.request) if self.cache.has(en.request) else 0
-            if held + n > self.max_model_len:
-                raise StepError(f"request {en.request!r} would hold {held + n} tokens, "
-                                f"the model takes {self.max_model_len}")
-            T += n
-        if T > self.engine.max_num_batched_tokens:
-            raise StepError(f"{T} rows exceed max_num_batched_tokens {self.engine.max_num_batched_tokens}")
-        if not self.can_run(entries):
-            new = sum(1 for en in entries if not self.cache.has(en.request))
-            if new > self.engine.max_num_seqs - self.cache.num_running():
-                raise OutOfPages(f"{new} new requests beside {self.cache.num_running()} running ones exceed "
-                                 f"max_num_seqs {self.engine.max_num_seqs}")
-            raise OutOfPages("the cache pools cannot hold this step's tokens")
+        fixed buffers with the given block-table widths, when given).
 
+        The checking, the page allocation and the filling of the metadata block are the C++
+        step builder's (``csrc/host/step_builder.cpp``); on an error nothing has changed."""
         nseq = len(entries)
-        firsts: List[int] = []
-        for en in entries:
-            if not self.cache.has(en.request):
-                self.cache.begin(en.request)
-            firsts.append(self.cache.append(en.request, len(en.tokens)))
-
-        groups = range(len(self.cache.groups))
-        if widths is None:
-            widths = [max(len(self.cache.block_table(en.request, g)) for en in entries) for g in groups]
+        G = len(self.cache.groups)
+        T = sum(len(en.tokens) for en in entries)
         R = sum(len(en.want) for en in entries)
-        total = 3 * T + (nseq + 1) + 2 * nseq + R + sum(nseq * w for w in widths)
+        widest = -(-self.max_model_len // min(g.page_size for g in self.cache.groups)) if G else 0
+        total_cap = 3 * T + 3 * nseq + 1 + R + nseq * widest * G
         if staging is None:
-            host, dev = self._staging(total)
+            host, dev = self._staging(total_cap)
             host_tensor, copied = self._host_tensor, self._copied
         else:
             staging.copied.synchronize()
             host, dev, host_tensor, copied = staging.host, staging.dev, staging.host_tensor, staging.copied
-        o = 0
-
-        def region(n):
-            nonlocal o
-            a, b = o, o + n
-            o = b
-            return a, b
-
-        r_tok, r_pos, r_seq = region(T), region(T), region(T)
-        r_start, r_ctx, r_slot, r_rows = region(nseq + 1), region(nseq), region(nseq), region(R)
-        r_tables = [region(nseq * w) for w in widths]
-
-        row = 0
-        out_row = 0
-        max_q = max_ctx = 0
-        starts = [0]
-        for s, en in enumerate(entries):
-            n = len(en.tokens)
-            host[r_tok[0] + row:r_tok[0] + row + n] = np.asarray(en.tokens, dtype=np.int32)
-            host[r_pos[0] + row:r_pos[0] + row + n] = np.arange(firsts[s], firsts[s] + n, dtype=np.int32)
-            host[r_seq[0] + row:r_seq[0] + row + n] = s
-            for w in en.want:
-                host[r_rows[0] + out_row] = row + int(w)
-                out_row += 1
-            host[r_ctx[0] + s] = firsts[s] + n
-            host[r_slot[0] + s] = self.cache.state_slot(en.request)
-            for g in groups:
-                table = self.cache.block_table(en.request, g)
-                base = r_tables[g][0] + s * widths[g]
-                host[base:base + len(table)] = np.asarray(table, dtype=np.int32)
-                host[base + len(table):base + widths[g]] = FREED
-            row += n
-            starts.append(row)
-            max_q = max(max_q, n)
-            max_ctx = max(max_ctx, firsts[s] + n)
-        host[r_start[0]:r_start[1]] = np.asarray(starts, dtype=np.int32)
-
+        built = build_step(self.cache, entries, self.vocab_size, self.max_model_len,
+                           self.engine.max_num_batched_tokens, host, widths)
+        layout, firsts, slots, lens, tok_off = built.layout, built.first_position, built.state_slot, \
+            built.query_lens, built.seq_start
+        total = int(layout.total)
         dev[:total].copy_(host_tensor[:total], non_blocking=True)
         copied.record()
 
-        def view(r):
-            return dev[r[0]:r[1]]
-
+        def view(off, n):
+            return dev[off:off + n]
         return StepBatch(
             num_tokens=T, num_seqs=nseq, num_logit_rows=R,
-            token_ids=view(r_tok), positions=view(r_pos), token_seq=view(r_seq),
-            seq_start=view(r_start), context_lens=view(r_ctx), state_slots=view(r_slot),
-            logit_rows=view(r_rows),
-            block_tables=[view(r_tables[g]).view(nseq, widths[g]) for g in groups],
-            host_seq_start=starts, host_first_position=firsts,
-            host_query_lens=[len(en.tokens) for en in entries],
-            host_state_slots=[self.cache.state_slot(en.request) for en in entries],
-            max_query_len=max_q, max_context_len=max_ctx)
+            token_ids=view(layout.off_tokens, T), positions=view(layout.off_positions, T),
+            token_seq=view(layout.off_seq, T), seq_start=view(layout.off_start, nseq + 1),
+            context_lens=view(layout.off_context, nseq), state_slots=view(layout.off_slot, nseq),
+            logit_rows=view(layout.off_rows, R),
+            block_tables=[view(layout.off_table[g], nseq * layout.width[g]).view(nseq, layout.width[g])
+                          for g in range(G)],
+            host_seq_start=tok_off, host_first_position=firsts,
+            host_query_lens=lens, host_state_slots=slots,
+            max_query_len=int(layout.max_query_len), max_context_len=int(layout.max_context_len))
 
     def _staging(self, n: int):
         if n > self._staging_cap:
