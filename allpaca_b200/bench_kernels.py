@@ -132,10 +132,10 @@ def bench_prefill_attention(args) -> dict:
 
     def fn(i):
         ops.attention(q, out, cache, table, seq, pos, nh, nkv, hd, 1.0 / math.sqrt(hd), 0, seq_start=start,
-                      query_lens=[T], max_context=T)
+                      query_lens=[T], max_context=T, use_tcgen05=not args.mma_sync)
     us = _time(fn, args.iters, args.warmup, not args.no_graph)
     flops = 4.0 * nh * hd * T * (T + 1) / 2
-    return {"kernel": "attention_tile", "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
+    return {"kernel": "attention_tile" if args.mma_sync else "attention_tcgen05", "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
             "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
@@ -166,6 +166,7 @@ def main(argv=None) -> int:
             s.add_argument("--tokens", type=int, default=2048)
             s.add_argument("--separate-merge", action="store_true", help="combine key slices in a second kernel")
             s.add_argument("--splits", type=int, default=0, help="key slices (0: the kernel's own plan)")
+            s.add_argument("--mma-sync", action="store_true", help="prompt attention with the mma.sync tile kernel")
     args = p.parse_args(argv)
     fn = {"gemm": bench_gemm, "attention": bench_attention, "prefill-attention": bench_prefill_attention}[args.what]
     print(json.dumps(fn(args)))

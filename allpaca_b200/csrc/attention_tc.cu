@@ -308,6 +308,7 @@ attention_tile_kernel(const AttnTcParams p) {
     const int t_lo = kmin / BKV, t_hi = kmax / BKV;
     fetch_tile(smem, 0, t_lo * BKV, kmin, kmax, p.cache, table, p.P, p.page_stride, head_off, v_off);
     cp_async_commit();
+    __syncthreads();      // the row pointers of this fetch have been read: the next fetch may replace them
     for (int t = t_lo; t <= t_hi; ++t) {
         const int cur = (t - t_lo) & 1;
         if (t < t_hi)
@@ -390,6 +391,7 @@ attention_split_kernel(const AttnTcParams p) {
     if (t_lo <= t_hi) {
         fetch_tile(smem, 0, t_lo * BKV, kmin, kmax, p.cache, table, p.P, p.page_stride, head_off, v_off);
         cp_async_commit();
+        __syncthreads();  // the row pointers of this fetch have been read: the next fetch may replace them
         for (int t = t_lo; t <= t_hi; ++t) {
             const int cur = (t - t_lo) & 1;
             if (t < t_hi)

@@ -1,0 +1,491 @@
+// Causal grouped-query attention for prompt portions on the 5th-generation tensor cores,
+// over paged keys and values, for head sizes 64 and 128 (-DAP_HEAD_DIM).
+//
+// A CTA owns 128 rows = (128 / group) tokens x the `group` query heads of one KV head of
+// one sequence, and walks the sequence's keys in tiles of 128:
+//
+//   TMA      Q once (a 3-D box tokens x heads x 64 columns per half of the head), then per
+//            tile the pages of K and V named by the block table (one 2-D box per page and
+//            half), into two stages of shared memory, 128-byte swizzle.
+//   MMA 1    S[128 x 128] = Q K^T        tcgen05.mma, accumulator in tensor memory
+//   softmax  two groups of four warps, one row per thread and 64 of the tile's 128 keys per
+//            group: read S from tensor memory, scale, mask, running maximum and sum in
+//            32-bit, write P in bfloat16 to shared memory in the operand layout, read the
+//            group's O_tile back after MMA 2 and fold it into the row's accumulator.  The two
+//            groups keep separate running maxima, like two key slices, and are combined at
+//            the end; eight warps give every scheduler two streams of this latency-bound work.
+//   MMA 2    O_tile_g[128 x HD] = P_g V_g for each group's 64 keys.  V is stored [key][dim],
+//            i.e. the B operand is "MN-major": no transposition of V anywhere.
+//
+// One thread issues the MMAs, one warp the TMA loads; MMA 1 of the next tile runs while the
+// softmax warps fold the O_tiles of this one.  Every barrier wait is bounded (status word as in
+// the matrix product).  Rows of other sequences that fall into a tile, keys past a row's
+// position or outside its window, and pages that were given back are masked or skipped.
+//
+// Shapes this kernel takes: head size 64 or 128, page size a multiple of 8 that divides
+// 128, a group size that divides 128.  Everything else runs on attention_tile_kernel.
+//
+// Reference counterpart: attention_qtile_kernel (cuda/src/kernels.cu:1801), causal rule
+// :1583-1585; the reference first packs pages into a contiguous buffer
+// (crates/allpaca-core/src/kv_tier.rs:1317-1417).
+#include "common.cuh"
+#include "tcgen05.cuh"
+#include <math.h>
+
+#ifndef AP_HEAD_DIM
+#error "compile with -DAP_HEAD_DIM=<head size>"
+#endif
+
+#if (AP_HEAD_DIM == 64 || AP_HEAD_DIM == 128)
+
+#define HD AP_HEAD_DIM
+#define NHALF (HD / 64)
+#define BQ 128
+#define BKV 128
+#define SUB_BYTES (128 * 128)              // a [128 rows x 64 bf16] sub-tile
+#define Q_BYTES (NHALF * SUB_BYTES)
+#define KV_BYTES (NHALF * SUB_BYTES)       // K (or V) of one tile
+#define P_BYTES (2 * SUB_BYTES)
+#define T5_THREADS 320                     // producer warp, MMA warp, 2 x 4 softmax warps
+#define T5_TMEM_COLS (HD == 128 ? 512 : 256)   // S: 128 columns, two O_tiles of HD columns
+#define LOG2E_F 1.4426950408889634f
+
+#define T5_ERR_WAIT 4
+
+static __device__ int g_t5_status;
+
+struct AttnT5Params {
+    bf16* out;
+    const int* block_table;
+    const int* seq_start;
+    const int* positions;
+    int max_blocks, nseq, nh, nkv, P, window, group, tokens_per_tile;
+    float scale_log2;
+};
+
+struct T5Smem {
+    static constexpr int kQ = 0;
+    static constexpr int kK = kQ + Q_BYTES;                 // two stages
+    static constexpr int kV = kK + 2 * KV_BYTES;            // two stages
+    static constexpr int kP = kV + 2 * KV_BYTES;
+    static constexpr int kBars = kP + P_BYTES;
+    static constexpr int kTotal = kBars + 256 + 1024;       // + alignment slack
+};
+
+__global__ void __launch_bounds__(T5_THREADS)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
+                         const AttnT5Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + T5Smem::kBars);
+    uint64_t* q_full = bars + 0;
+    uint64_t* kv_full = bars + 1;      // [2]
+    uint64_t* kv_empty = bars + 3;     // [2]
+    uint64_t* s_full = bars + 5;
+    uint64_t* p_ready = bars + 6;      // [2] one per softmax group
+    uint64_t* o_full = bars + 8;       // [2]
+    uint64_t* o_empty = bars + 10;     // [2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    volatile int* s_seq = (volatile int*)(tmem_slot + 2);
+    volatile int* s_tile = (volatile int*)(tmem_slot + 3);
+
+    if (*(volatile int*)&g_t5_status != 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        // late tiles of a sequence have the most keys to walk: hand them out first
+        int t = gridDim.x - 1 - blockIdx.x, found = -1;
+        for (int s = 0; s < p.nseq; ++s) {
+            const int n = p.seq_start[s + 1] - p.seq_start[s];
+            const int nt = (n + p.tokens_per_tile - 1) / p.tokens_per_tile;
+            if (t < nt) { found = s; break; }
+            t -= nt;
+        }
+        *s_seq = found;
+        *s_tile = t;
+        tc::mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            tc::mbar_init(&kv_full[s], 1);
+            tc::mbar_init(&kv_empty[s], 1);
+        }
+        tc::mbar_init(s_full, 1);
+        for (int g = 0; g < 2; ++g) {
+            tc::mbar_init(&p_ready[g], 128);
+            tc::mbar_init(&o_full[g], 1);
+            tc::mbar_init(&o_empty[g], 128);
+        }
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::prefetch_tensormap(&tmap_q);
+        tc::prefetch_tensormap(&tmap_kv);
+    }
+    // V stages start as zeros: what a skipped page leaves in them must be finite, because a
+    // probability of zero times a NaN would poison the row
+    for (int i = threadIdx.x; i < 2 * KV_BYTES / 16; i += T5_THREADS)
+        reinterpret_cast<uint4*>(smem + T5Smem::kV)[i] = make_uint4(0, 0, 0, 0);
+    tc::fence_proxy_async();
+    if (warp == 1) tc::tmem_alloc(tmem_slot, T5_TMEM_COLS);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const int seq = *s_seq;
+    const uint32_t tmem_base = *tmem_slot;
+    const bool active = seq >= 0;
+
+    // geometry of this CTA's tile (identical in every thread)
+    const int G = p.group;
+    int row0 = 0, ntok = 0, kmax = -1, kmin = 0, kvh = 0, head0 = 0;
+    if (active) {
+        row0 = p.seq_start[seq] + *s_tile * p.tokens_per_tile;
+        ntok = min(p.tokens_per_tile, p.seq_start[seq + 1] - row0);
+        kvh = blockIdx.y;
+        head0 = kvh * G;
+        // positions are read after the kernels before this one have finished
+    }
+    ap_pdl_wait();
+    if (active) {
+        kmax = p.positions[row0 + ntok - 1];
+        const int first = p.positions[row0];
+        kmin = (p.window > 0 && first - p.window + 1 > 0) ? first - p.window + 1 : 0;
+    }
+    const int t_lo = kmin / BKV, t_hi = active ? kmax / BKV : -1;
+    const int ntiles = t_hi - t_lo + 1;
+    const int* table = p.block_table + (size_t)(active ? seq : 0) * p.max_blocks;
+
+    if (warp == 0) {
+        if (active) {
+            // The whole warp produces: lane j looks up page j of the tile in the block table and
+            // issues that page's loads, so the table reads of a tile cost one round trip to L2.
+            if (lane == 0) {
+                tc::mbar_expect_tx(q_full, Q_BYTES);
+                for (int h = 0; h < NHALF; ++h)
+                    tc::tma_load_3d(smem + T5Smem::kQ + h * SUB_BYTES, &tmap_q, h * 64, head0, row0, q_full);
+            }
+            const int pages_per_tile = BKV / p.P;
+            const int page_bytes = p.P * 128;                       // one page, one half: P rows of 128 bytes
+            auto page_of = [&](int it) {
+                const int lp = (t_lo + it) * (BKV / p.P) + lane;
+                if (it >= ntiles || lane >= pages_per_tile || lp >= p.max_blocks || lp * p.P > kmax ||
+                    lp * p.P + p.P - 1 < kmin)
+                    return -1;
+                return table[lp];
+            };
+            int page = page_of(0);
+            for (int it = 0; it < ntiles; ++it) {
+                const int s = it & 1;
+                const uint32_t ph = (it >> 1) & 1;
+                const int next_page = page_of(it + 1);              // in flight while this tile's loads go out
+                const int valid = __popc(__ballot_sync(0xffffffffu, page >= 0));
+                int fine = 1;
+                if (lane == 0) {
+                    if (*abort_flag) fine = 0;
+                    if (fine && !tc::mbar_wait(&kv_empty[s], ph ^ 1)) {
+                        *abort_flag = 1;
+                        atomicExch(&g_t5_status, T5_ERR_WAIT);
+                        fine = 0;
+                    }
+                    if (fine) tc::mbar_expect_tx(&kv_full[s], (uint32_t)(valid * page_bytes * NHALF * 2));
+                }
+                fine = __shfl_sync(0xffffffffu, fine, 0);
+                if (!fine) break;
+                if (page >= 0) {
+                    const int krow = ((page * 2 + 0) * p.nkv + kvh) * p.P;
+                    const int vrow = ((page * 2 + 1) * p.nkv + kvh) * p.P;
+                    for (int h = 0; h < NHALF; ++h) {
+                        tc::tma_load_2d(smem + T5Smem::kK + s * KV_BYTES + h * SUB_BYTES + lane * page_bytes, &tmap_kv,
+                                        h * 64, krow, &kv_full[s]);
+                        tc::tma_load_2d(smem + T5Smem::kV + s * KV_BYTES + h * SUB_BYTES + lane * page_bytes, &tmap_kv,
+                                        h * 64, vrow, &kv_full[s]);
+                    }
+                }
+                page = next_page;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && active) {
+            constexpr uint32_t idesc_s = tc::instr_desc_bf16_f32(BQ, BKV);
+            constexpr uint32_t idesc_o = tc::instr_desc_bf16_f32_b_mn(BQ, HD);
+            const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + BKV;
+            bool ok = tc::mbar_wait(q_full, 0);
+            for (int it = 0; it < ntiles && ok && !*abort_flag; ++it) {
+                const int s = it & 1;
+                ok = tc::mbar_wait(&kv_full[s], (it >> 1) & 1);
+                if (!ok) break;
+                tc::fence_after_sync();
+                // S = Q K^T  (S of the tile before has been read: its p_ready was waited for)
+#pragma unroll
+                for (int h = 0; h < NHALF; ++h) {
+                    const uint64_t qd = tc::smem_desc_k_major_sw128(smem + T5Smem::kQ + h * SUB_BYTES);
+                    const uint64_t kd = tc::smem_desc_k_major_sw128(smem + T5Smem::kK + s * KV_BYTES + h * SUB_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tc::mma_bf16(tmem_s, qd + 2 * k, kd + 2 * k, idesc_s, (h > 0 || k > 0) ? 1u : 0u);
+                }
+                tc::mma_commit(s_full);
+                // O_tile_g = P_g V_g, one product per softmax group as soon as its P is written
+                const uint64_t vd = tc::smem_desc_mn_major_sw128(smem + T5Smem::kV + s * KV_BYTES, SUB_BYTES);
+                for (int g = 0; g < 2 && ok; ++g) {
+                    ok = tc::mbar_wait(&p_ready[g], it & 1);
+                    if (ok && it > 0) ok = tc::mbar_wait(&o_empty[g], (it - 1) & 1);
+                    if (!ok) break;
+                    tc::fence_after_sync();
+                    const uint64_t pd = tc::smem_desc_k_major_sw128(smem + T5Smem::kP + g * SUB_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks)
+                        tc::mma_bf16(tmem_o + g * HD, pd + 2 * ks, vd + (uint64_t)((g * 4 + ks) * (16 * 128 / 16)),
+                                     idesc_o, ks > 0 ? 1u : 0u);
+                    tc::mma_commit(&o_full[g]);
+                }
+                if (!ok) break;
+                tc::mma_commit(&kv_empty[s]);
+            }
+            if (!ok && !*abort_flag) {
+                *abort_flag = 1;
+                atomicExch(&g_t5_status, T5_ERR_WAIT);
+            }
+        }
+    }
+    // ---- softmax groups: warps 2..5 take keys 0..63 of every tile, warps 6..9 keys 64..127 ----
+    const int grp = warp >= 6 ? 1 : 0;
+    const int qtr = warp & 3;
+    const int r = qtr * 32 + lane;                 // row of the tile = (token r / G, head r % G)
+    const int tok = r / G, hq = r - tok * G;
+    const bool rvalid = active && warp >= 2 && tok < ntok;
+    float o[HD];
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    if (warp >= 2 && active) {
+        const int qpos = p.positions[row0 + (rvalid ? tok : 0)];
+        const uint32_t lane_base = tmem_base + ((uint32_t)(qtr * 32) << 16);
+        const uint32_t s_cols = lane_base + (uint32_t)(grp * 64);
+        const uint32_t o_cols = lane_base + (uint32_t)(BKV + grp * HD);
+        uint8_t* prow = smem + T5Smem::kP + grp * SUB_BYTES + r * 128;
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        for (int it = 0; it < ntiles; ++it) {
+            const int k0 = (t_lo + it) * BKV + grp * 64;       // first key of this group's half tile
+            // tcgen05.ld is a warp-wide instruction: whatever decides whether it runs is a vote
+            if (!__all_sync(0xffffffffu, tc::mbar_wait(s_full, it & 1))) { ok = false; break; }
+            tc::fence_after_sync();
+            const bool row_all = rvalid && k0 + 63 <= qpos && (p.window <= 0 || qpos - k0 < p.window);
+            const bool row_none = !rvalid || k0 > qpos || (p.window > 0 && qpos - (k0 + 63) >= p.window);
+            const bool all_visible = __all_sync(0xffffffffu, row_all);
+            const bool none_visible = __all_sync(0xffffffffu, row_none);
+            // pass 1: the row's maximum over this half tile (four chains, so the adds overlap)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (!none_visible) {
+#pragma unroll 1
+                for (int c = 0; c < 64; c += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld_x32(s_cols + (uint32_t)c, v);
+                    tc::tmem_ld_wait();
+                    if (all_visible) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[j]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int kpos = k0 + c + j;
+                            const bool vis = rvalid && kpos <= qpos && (p.window <= 0 || qpos - kpos < p.window);
+                            mx4[j & 3] = fmaxf(mx4[j & 3], vis ? __uint_as_float(v[j]) : -INFINITY);
+                        }
+                    }
+                }
+            }
+            // the scale is positive: the maximum of the scaled scores is the scaled maximum
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+            const float mnew = fmaxf(m, mx);
+            const float muse = mnew == -INFINITY ? 0.f : mnew;
+            const float alpha = exp2f(m - muse);
+            m = mnew;
+            // pass 2: probabilities, in bfloat16, into the operand layout of the second product
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+            for (int c = 0; c < 64; c += 32) {
+                uint32_t v[32];
+                uint32_t packed[16];
+                if (none_visible) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) packed[j] = 0u;
+                } else {
+                    tc::tmem_ld_x32(s_cols + (uint32_t)c, v);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        float pr[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int kpos = k0 + c + j + e;
+                            const bool vis = all_visible ||
+                                             (rvalid && kpos <= qpos && (p.window <= 0 || qpos - kpos < p.window));
+                            const float x = exp2f(fmaf(__uint_as_float(v[j + e]), p.scale_log2, -muse));
+                            pr[e] = vis ? x : 0.f;
+                            l4[(j + e) & 3] += pr[e];
+                        }
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(pr[0], pr[1]);
+                        packed[j >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+                    }
+                }
+                // keys c..c+31 of the half tile = four 16-byte chunks of the row
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int chunk = (c >> 3) + ch;
+                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
+                        make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+                }
+            }
+            l = l * alpha + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
+            tc::fence_proxy_async();            // the tensor core reads P through the async proxy
+            tc::fence_before_sync();
+            tc::mbar_arrive(&p_ready[grp]);
+            // fold O_tile into the row's accumulator
+            if (!__all_sync(0xffffffffu, tc::mbar_wait(&o_full[grp], it & 1))) { ok = false; break; }
+            tc::fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t v[32];
+                tc::tmem_ld_x32(o_cols + (uint32_t)c, v);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[c + j] = fmaf(o[c + j], alpha, __uint_as_float(v[j]));
+            }
+            tc::fence_before_sync();
+            tc::mbar_arrive(&o_empty[grp]);
+        }
+        if (!ok && !*abort_flag) {
+            *abort_flag = 1;
+            atomicExch(&g_t5_status, T5_ERR_WAIT);
+        }
+    }
+    // ---- combine the two groups (like two key slices) and write the rows ----
+    __syncthreads();                       // every load has landed and every product is done
+    float* xch = reinterpret_cast<float*>(smem + T5Smem::kK);      // [128 rows][HD + 2], over the K/V stages
+    if (warp >= 6 && active) {
+        float* dst = xch + (size_t)r * (HD + 2);
+#pragma unroll
+        for (int d = 0; d < HD; ++d) dst[d] = o[d];
+        dst[HD] = m;
+        dst[HD + 1] = l;
+    }
+    __syncthreads();
+    if (warp >= 2 && warp < 6 && active && ok && !*abort_flag && rvalid) {
+        const float* src = xch + (size_t)r * (HD + 2);
+        const float m1 = src[HD], l1 = src[HD + 1];
+        const float M = fmaxf(m, m1);
+        const float f0 = M == -INFINITY ? 0.f : exp2f(m - M), f1 = M == -INFINITY ? 0.f : exp2f(m1 - M);
+        const float L = l * f0 + l1 * f1;
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        bf16* dst = p.out + ((size_t)(row0 + tok) * p.nh + head0 + hq) * HD;
+#pragma unroll
+        for (int d = 0; d < HD; d += 8) {
+            uint4 w;
+            __nv_bfloat162* w2 = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                w2[e] = __floats2bfloat162_rn((o[d + 2 * e] * f0 + src[d + 2 * e] * f1) * inv,
+                                              (o[d + 2 * e + 1] * f0 + src[d + 2 * e + 1] * f1) * inv);
+            *reinterpret_cast<uint4*>(dst + d) = w;
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    ap_pdl_trigger();
+    if (warp == 1) {
+        __syncwarp();
+        tc::tmem_dealloc(tmem_base, T5_TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn5)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn5 encode_fn5() {
+    static EncodeTiledFn5 fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn5)ptr;
+    }
+    return fn;
+}
+
+// 1 when ap_attention_tcgen05 takes this shape, else 0 (the caller then uses the tile kernel)
+AP_EXPORT int ap_attention_tcgen05_supports(int nh, int nkv, int hd, int P) {
+    if (hd != HD || nkv <= 0 || nh % nkv) return 0;
+    const int g = nh / nkv;
+    if (g > 128 || 128 % g) return 0;
+    if (P <= 0 || P % 8 || BKV % P) return 0;
+    return encode_fn5() != nullptr;
+}
+
+AP_EXPORT int ap_attention_tcgen05_tokens_per_tile(int nh, int nkv) { return 128 / (nh / nkv); }
+
+AP_EXPORT int ap_attention_tcgen05(const void* q, void* out, const void* cache, long long num_pages,
+                                   const int* block_table, int max_blocks, const int* seq_start,
+                                   const int* positions, int nseq, int T, int nh, int nkv, int hd, int P,
+                                   long long page_stride, float scale, int window, int total_tiles,
+                                   cudaStream_t stream) {
+    AP_REQUIRE(ap_attention_tcgen05_supports(nh, nkv, hd, P), "attention (tcgen05): shape not supported: heads=%d "
+               "kv_heads=%d head_dim=%d page=%d", nh, nkv, hd, P);
+    AP_REQUIRE(page_stride == 2LL * nkv * P * HD, "attention (tcgen05): pages must be contiguous");
+    AP_REQUIRE(T > 0 && nseq > 0 && total_tiles > 0 && max_blocks > 0 && num_pages > 0, "attention (tcgen05): bad sizes");
+    AP_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)cache & 15) == 0, "attention (tcgen05): operands must be 16-byte aligned");
+    const int G = nh / nkv;
+    EncodeTiledFn5 enc = encode_fn5();
+    CUtensorMap mq, mkv;
+    {
+        cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)nh, (cuuint64_t)T};
+        cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)nh * HD * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(128 / G)};
+        cuuint32_t es[3] = {1, 1, 1};
+        AP_REQUIRE(enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, es,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
+                   "attention (tcgen05): cannot encode the query tensor map");
+    }
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)(num_pages * 2 * nkv * P)};
+        cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)P};
+        cuuint32_t es[2] = {1, 1};
+        AP_REQUIRE(enc(&mkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, es,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
+                   "attention (tcgen05): cannot encode the cache tensor map");
+    }
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             T5Smem::kTotal);
+        AP_REQUIRE(e == cudaSuccess, "attention (tcgen05): cannot reserve %d bytes of shared memory: %s",
+                   T5Smem::kTotal, cudaGetErrorString(e));
+        configured = true;
+    }
+    AttnT5Params p;
+    p.out = (bf16*)out; p.block_table = block_table; p.seq_start = seq_start; p.positions = positions;
+    p.max_blocks = max_blocks; p.nseq = nseq; p.nh = nh; p.nkv = nkv; p.P = P; p.window = window; p.group = G;
+    p.tokens_per_tile = 128 / G;
+    p.scale_log2 = scale * LOG2E_F;
+    AP_REQUIRE(nkv <= 65535, "attention (tcgen05): too many KV heads for the grid");
+    dim3 grid(total_tiles, nkv);
+    AP_CHECK_PDL_LAUNCH("attention_tcgen05", ap_launch_pdl(attention_tcgen05_kernel, grid, dim3(T5_THREADS),
+                                                           (size_t)T5Smem::kTotal, stream, mq, mkv, p));
+    return AP_OK;
+}
+
+AP_EXPORT int ap_attention_tcgen05_status(void) {
+    int v = -1;
+    if (cudaMemcpyFromSymbol(&v, g_t5_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
+#else   // head sizes the tcgen05 kernel is not built for
+
+AP_EXPORT int ap_attention_tcgen05_supports(int, int, int, int) { return 0; }
+
+#endif

@@ -64,6 +64,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         ::"r"(smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_addr(bar))
+        : "memory");
+}
 // Ask for a tile to be brought into L2 (no shared-memory destination, nothing to wait for).
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y)
@@ -104,6 +111,23 @@ __device__ __forceinline__ uint64_t smem_desc_k_major_sw128(const void* tile) {
     d |= (uint64_t)2 << 61;                         // 128-byte swizzle
     return d;
 }
+// Shared-memory B operand stored [k][n] with n contiguous ("MN-major"): sub-tiles of 64
+// n-elements (128-byte rows, one row per k, 128-byte swizzle as TMA writes it), `n_stride`
+// bytes from one 64-wide sub-tile to the next; 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_mn_major_sw128(const void* tile, uint32_t n_stride) {
+    const uint32_t addr = smem_addr(tile);
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((n_stride >> 4) & 0x3fffu) << 16;   // leading byte offset: between 64-wide sub-tiles
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset: 8 rows of k
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// bf16 x bf16 -> f32, A K-major, B stored [k][n] (MN-major), M x N tile.
+__host__ __device__ constexpr uint32_t instr_desc_bf16_f32_b_mn(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
 // bf16 x bf16 -> f32, both operands K-major, M x N tile.
 __host__ __device__ constexpr uint32_t instr_desc_bf16_f32(int M, int N) {
     return (1u << 4)                   // D format f32
@@ -137,6 +161,17 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t* v) {
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr)
         : "memory");
 }

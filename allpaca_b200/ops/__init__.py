@@ -230,12 +230,13 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: int = 0, seq_start: Optional[torch.Tensor] = None,
               query_lens: Optional[Sequence[int]] = None, max_context: int = 0,
-              scratch=None, zero_scratch=None) -> None:
+              scratch=None, zero_scratch=None, use_tcgen05: bool = True) -> None:
     """Causal attention of every row of ``q [T, nh*hd]`` over its sequence's cached keys.
 
     float32 runs the general CUDA-core kernel (the true 32-bit path).  bfloat16 runs on the
     tensor cores when ``seq_start`` (device, ``[nseq+1]``) and ``query_lens`` (host) are
-    given: the split kernel when every sequence brings one row, else the tile kernel.
+    given: the split kernel when every sequence brings one row; else, for 64 rows or more and
+    the shapes it takes, the tcgen05 kernel (``use_tcgen05``), and otherwise the tile kernel.
     ``scratch(name, shape, dtype)`` supplies the partial-result buffers of the split kernel;
     ``zero_scratch`` (same signature) supplies buffers that are zero when first handed out
     and stay with the caller: with it the last key slice to arrive combines all slices,
@@ -275,6 +276,17 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
                     pc = zero_scratch("attn.counters", (T * num_kv_heads * chunks,), torch.int32).data_ptr()
             mode, tiles = 1, 0
         else:
+            if (use_tcgen05 and T >= 64 and hasattr(lib, "ap_attention_tcgen05")
+                    and lib.ap_attention_tcgen05_supports(num_heads, num_kv_heads, head_dim, P)
+                    and cache_layer.stride(0) == 2 * num_kv_heads * P * head_dim):
+                # prompt portions on the tcgen05 tensor cores
+                tpt = int(lib.ap_attention_tcgen05_tokens_per_tile(num_heads, num_kv_heads))
+                tiles = sum(-(-n // tpt) for n in query_lens)
+                call(lib, "ap_attention_tcgen05", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
+                     cache_layer.shape[0], block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(),
+                     positions.data_ptr(), nseq, T, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0),
+                     float(scale), int(window or 0), tiles, stream_handle())
+                return
             tpt = int(lib.ap_attention_tc_tokens_per_tile(num_heads, num_kv_heads))
             tiles = sum(-(-n // tpt) for n in query_lens)
             mode, nsplit, po, pm, pc = 0, 1, 0, 0, 0
@@ -357,6 +369,10 @@ def gemm_tc_status() -> int:
 
 def check_kernel_status() -> None:
     """Raise if a kernel reported that it gave up (a bounded wait inside it expired)."""
+    for hd, lib in list(library._attn.items()):
+        if hasattr(lib, "ap_attention_tcgen05_status") and int(lib.ap_attention_tcgen05_status()) != 0:
+            raise KernelError(f"the tcgen05 attention kernel (head size {hd}) gave up waiting on its pipeline; "
+                              f"its results are void")
     code = gemm_tc_status()
     if code != 0:
         raise KernelError(f"the tensor-core matrix product gave up waiting (code {code}: "

@@ -108,6 +108,10 @@ def attention(head_dim: int) -> ctypes.CDLL:
 _OPTIONAL_ATTN_SIGNATURES: Dict[str, list] = {
     "ap_attention_tc": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _L, _F, _I, _I, _I, _I, _P, _P, _P, _P],
     "ap_attention_tc_tokens_per_tile": [_I, _I],
+    "ap_attention_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _L, _F, _I, _I, _P],
+    "ap_attention_tcgen05_supports": [_I, _I, _I, _I],
+    "ap_attention_tcgen05_tokens_per_tile": [_I, _I],
+    "ap_attention_tcgen05_status": [],
 }
 
 

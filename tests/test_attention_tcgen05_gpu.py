@@ -1,0 +1,91 @@
+"""The tcgen05 attention kernel for prompt portions against the plain attention and against
+the mma.sync tile kernel: several sequences, odd lengths, windows, pages given back, a far
+key that must be found."""
+import math
+
+import pytest
+import torch
+
+from test_kernels_gpu import paged_case, reference_attention, rel_err, run_attention
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(8, 2, 128, 16), (32, 8, 128, 16), (4, 4, 128, 8), (16, 2, 64, 32), (8, 8, 64, 16), (16, 1, 128, 64)]
+SEQS = [(700, 700), (129, 129), (333, 40), (64, 2), (257, 130), (1, 1), (200, 1)]
+
+
+def supported(ops, nh, nkv, hd, P):
+    from allpaca_b200.ops import library
+    lib = library.attention(hd)
+    return hasattr(lib, "ap_attention_tcgen05") and bool(lib.ap_attention_tcgen05_supports(nh, nkv, hd, P))
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from allpaca_b200 import ops as o
+    return o
+
+
+@pytest.mark.parametrize("nh,nkv,hd,P", SHAPES)
+@pytest.mark.parametrize("window", [0, 37, 300])
+def test_against_plain_and_tile_kernel(ops, nh, nkv, hd, P, window):
+    assert supported(ops, nh, nkv, hd, P)
+    case = paged_case(SEQS, nh, nkv, hd, P, torch.bfloat16, seed=hd + P + window)
+    scale = 0.9 / math.sqrt(hd)
+    got = run_attention(ops, case, nh, nkv, hd, scale, window, tensor_cores=True)
+    ops.check_kernel_status()
+    ref = reference_attention(case, SEQS, nh, hd, window or None, scale=scale)
+    assert rel_err(got, ref) < 1.5e-2
+    # the mma.sync tile kernel on the same inputs
+    q = case["q"].cuda()
+    out = torch.empty_like(q)
+    ops.attention(q, out, case["cache"].cuda(), case["table"].cuda(), case["token_seq"].cuda(),
+                  case["positions"].cuda(), nh, nkv, hd, scale, window, seq_start=case["seq_start"].cuda(),
+                  query_lens=case["query_lens"], max_context=int(case["positions"].max()) + 1, use_tcgen05=False)
+    assert rel_err(out.cpu(), ref) < 1.5e-2
+    assert rel_err(got, out.cpu().double()) < 1.5e-2
+
+
+def test_unsupported_shapes_fall_back(ops):
+    assert not supported(ops, 6, 2, 48, 16)          # head size 48
+    assert not supported(ops, 6, 2, 128, 16)         # group 3 does not divide 128
+    assert not supported(ops, 8, 2, 128, 4)          # page of 4
+    assert not supported(ops, 8, 2, 128, 48)         # page that does not divide 128
+    seqs = [(90, 90)]
+    case = paged_case(seqs, 6, 2, 128, 16, torch.bfloat16, seed=1)
+    got = run_attention(ops, case, 6, 2, 128, 0.1, 0, tensor_cores=True)
+    assert rel_err(got, reference_attention(case, seqs, 6, 128, None, scale=0.1)) < 1.5e-2
+
+
+@pytest.mark.parametrize("far", [0, 15, 16, 127, 128, 129, 255, 256, 600, 1023])
+def test_finds_one_far_key(ops, far):
+    nh, nkv, hd, P = 4, 2, 64, 16
+    ctx = 1024
+    seqs = [(ctx, 70)]
+    case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=far)
+    k, v = case["ks"][0], case["vs"][0]
+    qrow = case["rows_q"][0][-1]
+    for h in range(nkv):
+        k[far, h] = (qrow[h * 2].float() * 40.0 / qrow[h * 2].float().norm()).bfloat16()
+        v[far, h] = torch.full((hd,), 3.0 + h).bfloat16()
+    page = int(case["table"][0, far // P])
+    case["cache"][page, 0, :, far % P] = k[far]
+    case["cache"][page, 1, :, far % P] = v[far]
+    for h in range(nkv):
+        case["rows_q"][0][-1, h * 2] = (qrow[h * 2].float() * 3.0).bfloat16()
+    case["q"] = torch.cat(case["rows_q"]).reshape(-1, nh * hd)
+    got = run_attention(ops, case, nh, nkv, hd, 1.0, 0, tensor_cores=True).view(-1, nh, hd)[-1]
+    ref = reference_attention(case, seqs, nh, hd, None, scale=1.0).view(-1, nh, hd)[-1]
+    for h in range(nkv):
+        assert abs(float(ref[h * 2].mean()) - (3.0 + h)) < 0.05
+        assert float((got[h * 2].double() - ref[h * 2]).abs().max()) < 0.05
+
+
+def test_pages_given_back_are_not_read(ops):
+    nh, nkv, hd, P, window = 8, 2, 128, 16, 150
+    seqs = [(900, 80), (500, 200)]
+    freed = [900 - 80 - window + 1, 500 - 200 - window + 1]
+    case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=9, freed_before=freed)
+    got = run_attention(ops, case, nh, nkv, hd, 0.08, window, tensor_cores=True)
+    ops.check_kernel_status()
+    assert rel_err(got, reference_attention(case, seqs, nh, hd, window, scale=0.08)) < 1.5e-2
