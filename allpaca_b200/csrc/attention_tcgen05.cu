@@ -10,15 +10,22 @@
 //   MMA 1    S[128 x 128] = Q K^T        tcgen05.mma, accumulator in tensor memory
 //   softmax  two groups of four warps, one row per thread and 64 of the tile's 128 keys per
 //            group: read S from tensor memory, scale, mask, running maximum and sum in
-//            32-bit, write P in bfloat16 to shared memory in the operand layout, read the
-//            group's O_tile back after MMA 2 and fold it into the row's accumulator.  The two
+//            32-bit, write P in bfloat16 to shared memory in the operand layout.  The two
 //            groups keep separate running maxima, like two key slices, and are combined at
 //            the end; eight warps give every scheduler two streams of this latency-bound work.
-//   MMA 2    O_tile_g[128 x HD] = P_g V_g for each group's 64 keys.  V is stored [key][dim],
-//            i.e. the B operand is "MN-major": no transposition of V anywhere.
+//   MMA 2    O_g[128 x HD] += P_g V_g for each group's 64 keys, accumulated in tensor memory
+//            over all tiles.  V is stored [key][dim], i.e. the B operand is "MN-major": no
+//            transposition of V anywhere.
 //
-// One thread issues the MMAs, one warp the TMA loads; MMA 1 of the next tile runs while the
-// softmax warps fold the O_tiles of this one.  Every barrier wait is bounded (status word as in
+// A row's probabilities are taken against a reference maximum that is moved only when the
+// true maximum has grown by more than 2^8 over it; only then is the row of O_g in tensor
+// memory scaled down (read, multiplied, written back by the row's thread).  The row sum uses
+// the same reference, so the quotient is the same up to rounding, and the scaling, which would
+// otherwise cost a pass over O per tile, happens a few times per row.
+//
+// One thread issues the MMAs, one warp the TMA loads.  S and P are double-buffered and K and V
+// have barriers of their own, so the tensor cores compute S of tile i+1 and P V of tile i-1
+// while the softmax warps work on tile i.  Every barrier wait is bounded (status word as in
 // the matrix product).  Rows of other sequences that fall into a tile, keys past a row's
 // position or outside its window, and pages that were given back are masked or skipped.
 //
@@ -47,12 +54,20 @@
 #define KV_BYTES (NHALF * SUB_BYTES)       // K (or V) of one tile
 #define P_BYTES (2 * SUB_BYTES)
 #define T5_THREADS 320                     // producer warp, MMA warp, 2 x 4 softmax warps
-#define T5_TMEM_COLS (HD == 128 ? 512 : 256)   // S: 128 columns, two O_tiles of HD columns
+#define T5_TMEM_COLS 512                   // S twice: 2 x 128 columns, then two O_tiles of HD columns
+#define T5_O_COL 256
 #define LOG2E_F 1.4426950408889634f
 
 #define T5_ERR_WAIT 4
 
 static __device__ int g_t5_status;
+
+// 2^x by the special-function unit; exactly 0 for x = -inf
+__device__ __forceinline__ float t5_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 struct AttnT5Params {
     bf16* out;
@@ -68,7 +83,7 @@ struct T5Smem {
     static constexpr int kK = kQ + Q_BYTES;                 // two stages
     static constexpr int kV = kK + 2 * KV_BYTES;            // two stages
     static constexpr int kP = kV + 2 * KV_BYTES;
-    static constexpr int kBars = kP + P_BYTES;
+    static constexpr int kBars = kP + 2 * P_BYTES;          // P twice
     static constexpr int kTotal = kBars + 256 + 1024;       // + alignment slack
 };
 
@@ -79,13 +94,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + T5Smem::kBars);
     uint64_t* q_full = bars + 0;
-    uint64_t* kv_full = bars + 1;      // [2]
-    uint64_t* kv_empty = bars + 3;     // [2]
-    uint64_t* s_full = bars + 5;
-    uint64_t* p_ready = bars + 6;      // [2] one per softmax group
-    uint64_t* o_full = bars + 8;       // [2]
-    uint64_t* o_empty = bars + 10;     // [2]
-    uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+    uint64_t* k_full = bars + 1;       // [stage]
+    uint64_t* k_empty = bars + 3;      // [stage]
+    uint64_t* v_full = bars + 5;       // [stage]
+    uint64_t* v_empty = bars + 7;      // [stage]
+    uint64_t* s_full = bars + 9;       // [S buffer]
+    uint64_t* p_ready = bars + 11;     // [softmax group][P buffer]
+    uint64_t* o_full = bars + 15;      // [softmax group]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 20);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     volatile int* s_seq = (volatile int*)(tmem_slot + 2);
     volatile int* s_tile = (volatile int*)(tmem_slot + 3);
@@ -106,14 +122,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         *s_tile = t;
         tc::mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            tc::mbar_init(&kv_full[s], 1);
-            tc::mbar_init(&kv_empty[s], 1);
-        }
-        tc::mbar_init(s_full, 1);
-        for (int g = 0; g < 2; ++g) {
-            tc::mbar_init(&p_ready[g], 128);
-            tc::mbar_init(&o_full[g], 1);
-            tc::mbar_init(&o_empty[g], 128);
+            tc::mbar_init(&k_full[s], 1);
+            tc::mbar_init(&k_empty[s], 1);
+            tc::mbar_init(&v_full[s], 1);
+            tc::mbar_init(&v_empty[s], 1);
+            tc::mbar_init(&s_full[s], 1);
+            tc::mbar_init(&p_ready[s], 128);
+            tc::mbar_init(&p_ready[2 + s], 128);
+            tc::mbar_init(&o_full[s], 1);
         }
         *abort_flag = 0;
         tc::fence_barrier_init();
@@ -171,74 +187,87 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     return -1;
                 return table[lp];
             };
-            int page = page_of(0);
-            for (int it = 0; it < ntiles; ++it) {
+            // K runs one tile ahead of V: K of tile i+1 feeds S of tile i+1, which the tensor cores
+            // compute while the softmax warps are still on tile i; V of tile i is wanted last.
+            auto load = [&](int it, int page, int which, uint64_t* full, uint64_t* empty, int base) -> int {
                 const int s = it & 1;
                 const uint32_t ph = (it >> 1) & 1;
-                const int next_page = page_of(it + 1);              // in flight while this tile's loads go out
                 const int valid = __popc(__ballot_sync(0xffffffffu, page >= 0));
                 int fine = 1;
                 if (lane == 0) {
                     if (*abort_flag) fine = 0;
-                    if (fine && !tc::mbar_wait(&kv_empty[s], ph ^ 1)) {
+                    if (fine && !tc::mbar_wait(&empty[s], ph ^ 1)) {
                         *abort_flag = 1;
                         atomicExch(&g_t5_status, T5_ERR_WAIT);
                         fine = 0;
                     }
-                    if (fine) tc::mbar_expect_tx(&kv_full[s], (uint32_t)(valid * page_bytes * NHALF * 2));
+                    if (fine) tc::mbar_expect_tx(&full[s], (uint32_t)(valid * page_bytes * NHALF));
                 }
                 fine = __shfl_sync(0xffffffffu, fine, 0);
-                if (!fine) break;
-                if (page >= 0) {
-                    const int krow = ((page * 2 + 0) * p.nkv + kvh) * p.P;
-                    const int vrow = ((page * 2 + 1) * p.nkv + kvh) * p.P;
-                    for (int h = 0; h < NHALF; ++h) {
-                        tc::tma_load_2d(smem + T5Smem::kK + s * KV_BYTES + h * SUB_BYTES + lane * page_bytes, &tmap_kv,
-                                        h * 64, krow, &kv_full[s]);
-                        tc::tma_load_2d(smem + T5Smem::kV + s * KV_BYTES + h * SUB_BYTES + lane * page_bytes, &tmap_kv,
-                                        h * 64, vrow, &kv_full[s]);
-                    }
+                if (fine && page >= 0) {
+                    const int row = ((page * 2 + which) * p.nkv + kvh) * p.P;
+                    for (int h = 0; h < NHALF; ++h)
+                        tc::tma_load_2d(smem + base + s * KV_BYTES + h * SUB_BYTES + lane * page_bytes, &tmap_kv,
+                                        h * 64, row, &full[s]);
                 }
-                page = next_page;
+                return fine;
+            };
+            int page_v = page_of(0);
+            int fine = load(0, page_v, 0, k_full, k_empty, T5Smem::kK);
+            for (int it = 0; it < ntiles && fine; ++it) {
+                const int page_k = page_of(it + 1);
+                if (it + 1 < ntiles) fine = load(it + 1, page_k, 0, k_full, k_empty, T5Smem::kK);
+                if (fine) fine = load(it, page_v, 1, v_full, v_empty, T5Smem::kV);
+                page_v = page_k;
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && active) {
             constexpr uint32_t idesc_s = tc::instr_desc_bf16_f32(BQ, BKV);
             constexpr uint32_t idesc_o = tc::instr_desc_bf16_f32_b_mn(BQ, HD);
-            const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + BKV;
-            bool ok = tc::mbar_wait(q_full, 0);
-            for (int it = 0; it < ntiles && ok && !*abort_flag; ++it) {
+            const uint32_t tmem_o = tmem_base + T5_O_COL;
+            // S[buffer it & 1] = Q K^T of tile `it`; K's stage is free as soon as this product is done
+            auto scores = [&](int it) -> bool {
                 const int s = it & 1;
-                ok = tc::mbar_wait(&kv_full[s], (it >> 1) & 1);
-                if (!ok) break;
+                if (!tc::mbar_wait(&k_full[s], (it >> 1) & 1)) return false;
                 tc::fence_after_sync();
-                // S = Q K^T  (S of the tile before has been read: its p_ready was waited for)
 #pragma unroll
                 for (int h = 0; h < NHALF; ++h) {
                     const uint64_t qd = tc::smem_desc_k_major_sw128(smem + T5Smem::kQ + h * SUB_BYTES);
                     const uint64_t kd = tc::smem_desc_k_major_sw128(smem + T5Smem::kK + s * KV_BYTES + h * SUB_BYTES);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        tc::mma_bf16(tmem_s, qd + 2 * k, kd + 2 * k, idesc_s, (h > 0 || k > 0) ? 1u : 0u);
+                        tc::mma_bf16(tmem_base + (uint32_t)(s * BKV), qd + 2 * k, kd + 2 * k, idesc_s,
+                                     (h > 0 || k > 0) ? 1u : 0u);
                 }
-                tc::mma_commit(s_full);
-                // O_tile_g = P_g V_g, one product per softmax group as soon as its P is written
+                tc::mma_commit(&k_empty[s]);
+                tc::mma_commit(&s_full[s]);
+                return true;
+            };
+            bool ok = tc::mbar_wait(q_full, 0);
+            if (ok) ok = scores(0);
+            for (int it = 0; it < ntiles && ok && !*abort_flag; ++it) {
+                const int s = it & 1;
+                // S of tile it+1 goes into the buffer that tile it-1 used; the softmax groups have
+                // handed over P of tile it-1 (waited for below, one iteration ago), so they have read it
+                if (it + 1 < ntiles) ok = scores(it + 1);
+                if (ok) ok = tc::mbar_wait(&v_full[s], (it >> 1) & 1);
+                // O_g += P_g V_g, one product per softmax group as soon as its P is written (by then
+                // the group has also scaled O_g down where a row's reference maximum moved)
                 const uint64_t vd = tc::smem_desc_mn_major_sw128(smem + T5Smem::kV + s * KV_BYTES, SUB_BYTES);
                 for (int g = 0; g < 2 && ok; ++g) {
-                    ok = tc::mbar_wait(&p_ready[g], it & 1);
-                    if (ok && it > 0) ok = tc::mbar_wait(&o_empty[g], (it - 1) & 1);
+                    ok = tc::mbar_wait(&p_ready[g * 2 + s], (it >> 1) & 1);
                     if (!ok) break;
                     tc::fence_after_sync();
-                    const uint64_t pd = tc::smem_desc_k_major_sw128(smem + T5Smem::kP + g * SUB_BYTES);
+                    const uint64_t pd = tc::smem_desc_k_major_sw128(smem + T5Smem::kP + s * P_BYTES + g * SUB_BYTES);
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks)
                         tc::mma_bf16(tmem_o + g * HD, pd + 2 * ks, vd + (uint64_t)((g * 4 + ks) * (16 * 128 / 16)),
-                                     idesc_o, ks > 0 ? 1u : 0u);
+                                     idesc_o, (it > 0 || ks > 0) ? 1u : 0u);
                     tc::mma_commit(&o_full[g]);
                 }
                 if (!ok) break;
-                tc::mma_commit(&kv_empty[s]);
+                tc::mma_commit(&v_empty[s]);
             }
             if (!ok && !*abort_flag) {
                 *abort_flag = 1;
@@ -252,107 +281,96 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     const int r = qtr * 32 + lane;                 // row of the tile = (token r / G, head r % G)
     const int tok = r / G, hq = r - tok * G;
     const bool rvalid = active && warp >= 2 && tok < ntok;
-    float o[HD];
-    float m = -INFINITY, l = 0.f;
-    bool ok = true;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(qtr * 32) << 16);
+    const uint32_t o_cols = lane_base + (uint32_t)(T5_O_COL + grp * HD);
+    float mref = -INFINITY, l = 0.f;               // the row's reference maximum (log2 units) and sum
+    bool ok = true;                                // the same in all lanes of a warp
     if (warp >= 2 && active) {
         const int qpos = p.positions[row0 + (rvalid ? tok : 0)];
-        const uint32_t lane_base = tmem_base + ((uint32_t)(qtr * 32) << 16);
-        const uint32_t s_cols = lane_base + (uint32_t)(grp * 64);
-        const uint32_t o_cols = lane_base + (uint32_t)(BKV + grp * HD);
-        uint8_t* prow = smem + T5Smem::kP + grp * SUB_BYTES + r * 128;
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
         for (int it = 0; it < ntiles; ++it) {
             const int k0 = (t_lo + it) * BKV + grp * 64;       // first key of this group's half tile
-            // tcgen05.ld is a warp-wide instruction: whatever decides whether it runs is a vote
-            if (!__all_sync(0xffffffffu, tc::mbar_wait(s_full, it & 1))) { ok = false; break; }
+            const int buf = it & 1;
+            const uint32_t s_cols = lane_base + (uint32_t)(buf * BKV + grp * 64);
+            uint8_t* prow = smem + T5Smem::kP + buf * P_BYTES + grp * SUB_BYTES + r * 128;
+            // tcgen05.ld and .st are warp-wide instructions: whatever decides whether one runs is a vote
+            if (!__all_sync(0xffffffffu, tc::mbar_wait(&s_full[buf], (it >> 1) & 1))) { ok = false; break; }
             tc::fence_after_sync();
             const bool row_all = rvalid && k0 + 63 <= qpos && (p.window <= 0 || qpos - k0 < p.window);
             const bool row_none = !rvalid || k0 > qpos || (p.window > 0 && qpos - (k0 + 63) >= p.window);
             const bool all_visible = __all_sync(0xffffffffu, row_all);
             const bool none_visible = __all_sync(0xffffffffu, row_none);
-            // pass 1: the row's maximum over this half tile (four chains, so the adds overlap)
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (!none_visible) {
-#pragma unroll 1
-                for (int c = 0; c < 64; c += 32) {
-                    uint32_t v[32];
-                    tc::tmem_ld_x32(s_cols + (uint32_t)c, v);
-                    tc::tmem_ld_wait();
-                    if (all_visible) {
+            uint32_t packed[32];
+            float lsum = 0.f;
+            if (none_visible) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[j]));
-                    } else {
+                for (int j = 0; j < 32; ++j) packed[j] = 0u;
+            } else {
+                uint32_t v[64];
+                tc::tmem_ld_x32(s_cols, v);
+                tc::tmem_ld_x32(s_cols + 32u, v + 32);
+                tc::tmem_ld_wait();
+                if (!all_visible) {
+                    // a masked score becomes -inf, whose probability below is exactly zero
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int kpos = k0 + c + j;
-                            const bool vis = rvalid && kpos <= qpos && (p.window <= 0 || qpos - kpos < p.window);
-                            mx4[j & 3] = fmaxf(mx4[j & 3], vis ? __uint_as_float(v[j]) : -INFINITY);
-                        }
+                    for (int j = 0; j < 64; ++j) {
+                        const int kpos = k0 + j;
+                        const bool vis = rvalid && kpos <= qpos && (p.window <= 0 || qpos - kpos < p.window);
+                        v[j] = vis ? v[j] : 0xff800000u;
                     }
                 }
-            }
-            // the scale is positive: the maximum of the scaled scores is the scaled maximum
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-            const float mnew = fmaxf(m, mx);
-            const float muse = mnew == -INFINITY ? 0.f : mnew;
-            const float alpha = exp2f(m - muse);
-            m = mnew;
-            // pass 2: probabilities, in bfloat16, into the operand layout of the second product
-            float l4[4] = {0.f, 0.f, 0.f, 0.f};
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int j = 0; j < 64; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[j]));
+                // the scale is positive: the maximum of the scaled scores is the scaled maximum
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+                const bool grow = mx > mref + 8.0f;            // also the row's first visible key
+                float alpha = 1.f;
+                if (grow) {
+                    alpha = t5_exp2(mref - mx);                // 0 when the row had no key yet
+                    mref = mx;
+                    l *= alpha;
+                }
+                if (it > 0 && __any_sync(0xffffffffu, grow)) {
+                    // scale this warp's rows of O_g down, once the product of the tile before is in
+                    if (!__all_sync(0xffffffffu, tc::mbar_wait(&o_full[grp], (it - 1) & 1))) { ok = false; break; }
+                    tc::fence_after_sync();
 #pragma unroll 1
-            for (int c = 0; c < 64; c += 32) {
-                uint32_t v[32];
-                uint32_t packed[16];
-                if (none_visible) {
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t w[32];
+                        tc::tmem_ld_x32(o_cols + (uint32_t)c, w);
+                        tc::tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) packed[j] = 0u;
-                } else {
-                    tc::tmem_ld_x32(s_cols + (uint32_t)c, v);
-                    tc::tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        float pr[2];
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int kpos = k0 + c + j + e;
-                            const bool vis = all_visible ||
-                                             (rvalid && kpos <= qpos && (p.window <= 0 || qpos - kpos < p.window));
-                            const float x = exp2f(fmaf(__uint_as_float(v[j + e]), p.scale_log2, -muse));
-                            pr[e] = vis ? x : 0.f;
-                            l4[(j + e) & 3] += pr[e];
-                        }
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(pr[0], pr[1]);
-                        packed[j >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+                        for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(__uint_as_float(w[j]) * alpha);
+                        tc::tmem_st_x32(o_cols + (uint32_t)c, w);
                     }
+                    tc::tmem_st_wait();
                 }
-                // keys c..c+31 of the half tile = four 16-byte chunks of the row
+                const float muse = mref == -INFINITY ? 0.f : mref;
+                float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    const int chunk = (c >> 3) + ch;
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) =
-                        make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+                for (int j = 0; j < 64; j += 2) {
+                    const float x0 = t5_exp2(fmaf(__uint_as_float(v[j]), p.scale_log2, -muse));
+                    const float x1 = t5_exp2(fmaf(__uint_as_float(v[j + 1]), p.scale_log2, -muse));
+                    l4[j & 3] += x0;
+                    l4[(j + 1) & 3] += x1;
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(x0, x1);
+                    packed[j >> 1] = *reinterpret_cast<uint32_t*>(&b2);
                 }
+                lsum = (l4[0] + l4[1]) + (l4[2] + l4[3]);
             }
-            l = l * alpha + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
+            l += lsum;
+            // the half tile's 64 keys = eight 16-byte chunks of the row, in the operand's swizzle
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) =
+                    make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
             tc::fence_proxy_async();            // the tensor core reads P through the async proxy
             tc::fence_before_sync();
-            tc::mbar_arrive(&p_ready[grp]);
-            // fold O_tile into the row's accumulator
-            if (!__all_sync(0xffffffffu, tc::mbar_wait(&o_full[grp], it & 1))) { ok = false; break; }
-            tc::fence_after_sync();
-#pragma unroll
-            for (int c = 0; c < HD; c += 32) {
-                uint32_t v[32];
-                tc::tmem_ld_x32(o_cols + (uint32_t)c, v);
-                tc::tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o[c + j] = fmaf(o[c + j], alpha, __uint_as_float(v[j]));
-            }
-            tc::fence_before_sync();
-            tc::mbar_arrive(&o_empty[grp]);
+            tc::mbar_arrive(&p_ready[grp * 2 + buf]);
         }
+        // the last product into O_g
+        if (ok && !__all_sync(0xffffffffu, tc::mbar_wait(&o_full[grp], (ntiles - 1) & 1))) ok = false;
+        tc::fence_after_sync();
         if (!ok && !*abort_flag) {
             *abort_flag = 1;
             atomicExch(&g_t5_status, T5_ERR_WAIT);
@@ -360,32 +378,55 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     }
     // ---- combine the two groups (like two key slices) and write the rows ----
     __syncthreads();                       // every load has landed and every product is done
-    float* xch = reinterpret_cast<float*>(smem + T5Smem::kK);      // [128 rows][HD + 2], over the K/V stages
-    if (warp >= 6 && active) {
-        float* dst = xch + (size_t)r * (HD + 2);
+    const bool fine = active && !*abort_flag;
+    constexpr int XS = HD + 3;             // row stride in floats: odd, so rows fall into different banks
+    float* xch = reinterpret_cast<float*>(smem + T5Smem::kK);      // [128 rows][XS], over the K/V stages
+    if (warp >= 6 && fine) {
+        float* dst = xch + (size_t)r * XS;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+            uint32_t w[32];
+            tc::tmem_ld_x32(o_cols + (uint32_t)c, w);
+            tc::tmem_ld_wait();
 #pragma unroll
-        for (int d = 0; d < HD; ++d) dst[d] = o[d];
-        dst[HD] = m;
+            for (int j = 0; j < 32; ++j) dst[c + j] = __uint_as_float(w[j]);
+        }
+        dst[HD] = mref;
         dst[HD + 1] = l;
     }
     __syncthreads();
-    if (warp >= 2 && warp < 6 && active && ok && !*abort_flag && rvalid) {
-        const float* src = xch + (size_t)r * (HD + 2);
+    if (warp >= 2 && warp < 6 && fine) {
+        const float* src = xch + (size_t)r * XS;
         const float m1 = src[HD], l1 = src[HD + 1];
-        const float M = fmaxf(m, m1);
-        const float f0 = M == -INFINITY ? 0.f : exp2f(m - M), f1 = M == -INFINITY ? 0.f : exp2f(m1 - M);
+        const float M = fmaxf(mref, m1);
+        const float f0 = mref == -INFINITY ? 0.f : t5_exp2(mref - M), f1 = m1 == -INFINITY ? 0.f : t5_exp2(m1 - M);
         const float L = l * f0 + l1 * f1;
         const float inv = L > 0.f ? 1.0f / L : 0.f;
-        bf16* dst = p.out + ((size_t)(row0 + tok) * p.nh + head0 + hq) * HD;
+        const float g0 = f0 * inv, g1 = f1 * inv;
+        bf16* dst = p.out + ((size_t)(row0 + (rvalid ? tok : 0)) * p.nh + head0 + hq) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+            uint32_t w[32];
+            tc::tmem_ld_x32(o_cols + (uint32_t)c, w);
+            tc::tmem_ld_wait();
+            if (rvalid) {
 #pragma unroll
-        for (int d = 0; d < HD; d += 8) {
-            uint4 w;
-            __nv_bfloat162* w2 = reinterpret_cast<__nv_bfloat162*>(&w);
+                for (int d = 0; d < 32; d += 8) {
+                    uint4 o8;
+                    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o8);
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                w2[e] = __floats2bfloat162_rn((o[d + 2 * e] * f0 + src[d + 2 * e] * f1) * inv,
-                                              (o[d + 2 * e + 1] * f0 + src[d + 2 * e + 1] * f1) * inv);
-            *reinterpret_cast<uint4*>(dst + d) = w;
+                    for (int e = 0; e < 4; ++e) {
+                        // a group that saw no key of this row holds zeros (0 x finite V) or, where
+                        // its factor is zero, is not counted at all
+                        const float a0 = f0 > 0.f ? __uint_as_float(w[d + 2 * e]) * g0 : 0.f;
+                        const float a1 = f0 > 0.f ? __uint_as_float(w[d + 2 * e + 1]) * g0 : 0.f;
+                        const float b0 = f1 > 0.f ? src[c + d + 2 * e] * g1 : 0.f;
+                        const float b1 = f1 > 0.f ? src[c + d + 2 * e + 1] * g1 : 0.f;
+                        o2[e] = __floats2bfloat162_rn(a0 + b0, a1 + b1);
+                    }
+                    *reinterpret_cast<uint4*>(dst + c + d) = o8;
+                }
+            }
         }
     }
     tc::fence_before_sync();
