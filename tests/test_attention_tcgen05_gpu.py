@@ -89,3 +89,31 @@ def test_pages_given_back_are_not_read(ops):
     got = run_attention(ops, case, nh, nkv, hd, 0.08, window, tensor_cores=True)
     ops.check_kernel_status()
     assert rel_err(got, reference_attention(case, seqs, nh, hd, window, scale=0.08)) < 1.5e-2
+
+
+@pytest.mark.parametrize("rising", [True, False])
+def test_scores_that_rise_or_fall_along_the_sequence(ops, rising):
+    """Rising scores move every row's reference maximum in every key tile, so the accumulator
+    in tensor memory is scaled down again and again; falling scores never move it after the
+    first tile, and the late probabilities are tiny."""
+    nh, nkv, hd, P = 8, 2, 128, 16
+    ctx = 1024
+    seqs = [(ctx, ctx)]
+    case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=5)
+    g = torch.Generator().manual_seed(11)
+    u = torch.randn(hd, generator=g)
+    u = u / u.norm()
+    ramp = torch.arange(ctx, dtype=torch.float32) / ctx
+    if not rising:
+        ramp = 1.0 - ramp
+    k = case["ks"][0].float() * 0.1 + 14.0 * ramp[:, None, None] * u
+    case["ks"][0] = k.bfloat16()
+    case["rows_q"][0] = (case["rows_q"][0].float() * 0.1 + 14.0 * u).bfloat16()
+    for j in range(ctx):
+        page = int(case["table"][0, j // P])
+        case["cache"][page, 0, :, j % P] = case["ks"][0][j]
+    case["q"] = torch.cat(case["rows_q"]).reshape(-1, nh * hd)
+    got = run_attention(ops, case, nh, nkv, hd, 1.0, 0, tensor_cores=True)
+    ops.check_kernel_status()
+    ref = reference_attention(case, seqs, nh, hd, None, scale=1.0)
+    assert rel_err(got, ref) < 1.5e-2
