@@ -53,7 +53,12 @@ def bench_gemm(args) -> dict:
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     S = args.splits or ops.gemm_tc_splits(M, N, K)
     odt = torch.float32 if args.out == "float32" else torch.bfloat16
-    if args.dual or args.swiglu:
+    if args.persistent:
+        n_out = N // 2 if args.swiglu else N
+        out = torch.empty(M, n_out, device="cuda", dtype=odt)
+        fn = lambda i: ops.gemm_tc_persistent(a, ws[i % copies], out, pairs=args.swiglu)   # noqa: E731
+        S = 1
+    elif args.dual or args.swiglu:
         n_out = N // 2 if args.swiglu else N
         out = torch.empty(M, n_out, device="cuda", dtype=odt)
         fn = lambda i: ops.gemm_tc_dual(a, ws[i % copies], out, swiglu=args.swiglu)   # noqa: E731
@@ -68,7 +73,7 @@ def bench_gemm(args) -> dict:
     ops.check_kernel_status()
     nbytes = N * K * 2 + M * K * 2 + out.numel() * out.element_size()
     flops = 2.0 * M * N * K
-    return {"kernel": "gemm_tc_dual" if (args.dual or args.swiglu) else "gemm_tc", "M": M, "N": N, "K": K, "splits": S, "partials": bool(args.partials),
+    return {"kernel": "gemm_tc_persistent" if args.persistent else "gemm_tc_dual" if (args.dual or args.swiglu) else "gemm_tc", "M": M, "N": N, "K": K, "splits": S, "partials": bool(args.partials),
             "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
@@ -156,6 +161,8 @@ def main(argv=None) -> int:
             s.add_argument("--out", choices=["float32", "bfloat16"], default="bfloat16")
             s.add_argument("--dual", action="store_true", help="two weight tiles per CTA")
             s.add_argument("--swiglu", action="store_true", help="w is [gate; up]: fused gated activation")
+            s.add_argument("--persistent", action="store_true",
+                           help="the persistent kernel (with --swiglu: gate and up rows alternate)")
         else:
             s.add_argument("--heads", type=int, default=32)
             s.add_argument("--kv-heads", type=int, default=8)

@@ -371,40 +371,53 @@ AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in
 }
 
 // ---------------------------------------------------------------------------
-// gated activation: out[t, j] = silu(g) * u,  g = in[t, j], u = in[t, I + j]
+// gated activation: out[t, j] = silu(g) * u,  g = in[t, j], u = in[t, I + j]; or, with gate and up
+// columns alternating (`pairs`), g = in[t, 2j], u = in[t, 2j + 1]
 // ---------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ in, int S, size_t in_stride, TO* __restrict__ out,
-                              int T, int I) {
+                              int T, int I, int pairs) {
     const size_t n = (size_t)T * I;
     ap_pdl_trigger();
     ap_pdl_wait();
     for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
         const size_t t = e / I, j = e - t * I;
         const size_t base = t * 2 * (size_t)I;
-        const float g = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + j)));
-        const float u = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + I + j)));
+        const float g = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, pairs ? base + 2 * j : base + j)));
+        const float u = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, pairs ? base + 2 * j + 1 : base + I + j)));
         const float a = g / (1.0f + expf(-g));
         out[e] = ap_from_float<TO>(a * u);
     }
 }
 
 // bfloat16 in and out, 8 elements (16 bytes) per thread
+template <bool PAIRS>
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int T, int I) {
     const size_t n8 = (size_t)T * (I / 8);
     ap_pdl_trigger();
     ap_pdl_wait();
     for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n8; e += (size_t)gridDim.x * blockDim.x) {
         const size_t t = e / (I / 8), j = (e - t * (I / 8)) * 8;
-        const uint4 g4 = *reinterpret_cast<const uint4*>(in + t * 2 * (size_t)I + j);
-        const uint4 u4 = *reinterpret_cast<const uint4*>(in + t * 2 * (size_t)I + I + j);
+        // the 16 values that make these 8 outputs: two separate runs of 8, or one run of 16 pairs
+        const uint4 g4 = *reinterpret_cast<const uint4*>(in + t * 2 * (size_t)I + (PAIRS ? 2 * j : j));
+        const uint4 u4 = *reinterpret_cast<const uint4*>(in + t * 2 * (size_t)I + (PAIRS ? 2 * j + 8 : I + j));
         const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
         const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
         uint4 o4;
         __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+            float2 g, u;
+            if (PAIRS) {
+                // every bfloat162 is one (gate, up) pair; outputs 2k and 2k+1 come from pairs 2k, 2k+1
+                const float2 p0 = __bfloat1622float2(k < 2 ? g2[2 * k] : u2[2 * k - 4]);
+                const float2 p1 = __bfloat1622float2(k < 2 ? g2[2 * k + 1] : u2[2 * k - 3]);
+                g = make_float2(p0.x, p1.x);
+                u = make_float2(p0.y, p1.y);
+            } else {
+                g = __bfloat1622float2(g2[k]);
+                u = __bfloat1622float2(u2[k]);
+            }
             o2[k] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
         }
         *reinterpret_cast<uint4*>(out + t * (size_t)I + j) = o4;
@@ -412,7 +425,7 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restri
 }
 
 AP_EXPORT int ap_swiglu(const void* in, int in_dtype, int S, long long in_stride, void* out, int out_dtype,
-                        int T, int I, cudaStream_t stream) {
+                        int T, int I, int pairs, cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && I > 0 && S >= 1, "swiglu: bad sizes T=%d I=%d S=%d", T, I, S);
     if (T == 0) return AP_OK;
     const int threads = 256;
@@ -422,13 +435,17 @@ AP_EXPORT int ap_swiglu(const void* in, int in_dtype, int S, long long in_stride
         ((uintptr_t)out & 15) == 0) {
         long long b8 = ((long long)T * (I / 8) + threads - 1) / threads;
         if (b8 > 148 * 32) b8 = 148 * 32;
-        AP_CHECK_PDL_LAUNCH("swiglu", ap_launch_pdl(swiglu_bf16x8_kernel, dim3((unsigned)b8), dim3(threads), 0, stream,
-                                                    (const bf16*)in, (bf16*)out, T, I));
+        if (pairs)
+            AP_CHECK_PDL_LAUNCH("swiglu", ap_launch_pdl(swiglu_bf16x8_kernel<true>, dim3((unsigned)b8), dim3(threads), 0,
+                                                        stream, (const bf16*)in, (bf16*)out, T, I));
+        else
+            AP_CHECK_PDL_LAUNCH("swiglu", ap_launch_pdl(swiglu_bf16x8_kernel<false>, dim3((unsigned)b8), dim3(threads), 0,
+                                                        stream, (const bf16*)in, (bf16*)out, T, I));
         return AP_OK;
     }
 #define LAUNCH(TI, TO) \
     AP_CHECK_PDL_LAUNCH("swiglu", ap_launch_pdl(swiglu_kernel<TI, TO>, dim3((unsigned)blocks), dim3(threads), 0, stream, \
-                                                (const TI*)in, S, (size_t)in_stride, (TO*)out, T, I))
+                                                (const TI*)in, S, (size_t)in_stride, (TO*)out, T, I, pairs))
     if (in_dtype == AP_F32 && out_dtype == AP_F32) LAUNCH(float, float);
     else if (in_dtype == AP_F32 && out_dtype == AP_BF16) LAUNCH(float, bf16);
     else if (in_dtype == AP_BF16 && out_dtype == AP_BF16) {

@@ -643,6 +643,286 @@ AP_EXPORT int ap_gemm_tc_prefers_dual(int M, int N, int K) {
     return wd * 165 < ws * 100 ? 1 : 0;
 }
 
+// ---------------------------------------------------------------------------
+// Many rows (prompt portions): a persistent kernel, one CTA per SM, that walks output tiles of
+// 128 weight rows x BN tokens.  The accumulator is double-buffered in tensor memory (2 x BN
+// columns), so the four epilogue warps read tile j out and write it while the tensor cores
+// are already on tile j+1; the operand ring keeps running across tiles.  Consecutive tiles
+// differ in the token tile first, so the CTAs that run at the same time share weight tiles
+// and the whole activation matrix stays in L2.
+//
+// PAIRS: the weight's rows alternate gate, up, gate, up ... (row 2i and 2i+1 belong to output
+// column i).  Neighbouring lanes exchange their values by shuffle and the epilogue writes
+// silu(gate) * up to out[M, N/2]: the gated activation never makes a round trip to memory.
+// ---------------------------------------------------------------------------
+template <int BN> struct PersistCfg {
+    static constexpr int kStages = BN >= 256 ? 4 : 6;
+    static constexpr int kBBytes = BN * TILE_K * 2;
+    static constexpr int kStageBytes = A_TILE_BYTES + kBBytes;
+    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+template <int BN, typename TO, bool PAIRS>
+__global__ void __launch_bounds__(192)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+                          TO* __restrict__ out, int M, int N, int K, long long ldc, int tiles_m, int tiles_total) {
+    using Cfg = PersistCfg<BN>;
+    constexpr int STAGES = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* w_tiles = smem;
+    uint8_t* a_tiles = smem + STAGES * A_TILE_BYTES;
+    uint64_t* full = (uint64_t*)(smem + STAGES * Cfg::kStageBytes);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;       // [accumulator buffer]
+    uint64_t* acc_empty = acc_full + 2;        // [accumulator buffer]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    if (*(volatile int*)&g_tc_status != 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nkb = (K + TILE_K - 1) / TILE_K;
+    const int my_tiles = ((int)blockIdx.x < tiles_total) ? (tiles_total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(&acc_full[b], 1);
+            tc::mbar_init(&acc_empty[b], 128);
+        }
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::prefetch_tensormap(&tmap_w);
+        tc::prefetch_tensormap(&tmap_a);
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0 && my_tiles > 0) {
+            const long long total = (long long)my_tiles * nkb;
+            // the weight does not depend on earlier kernels: fill the ring with the first tile's
+            // weight blocks, then wait for the kernels that produce the activations
+            const int pre = (int)min((long long)STAGES, (long long)nkb);
+            {
+                const int t = blockIdx.x;
+                const int n0 = (t / tiles_m) * TILE_W;
+                for (int i = 0; i < pre; ++i) {
+                    tc::mbar_expect_tx(&full[i], Cfg::kStageBytes);
+                    tc::tma_load_2d(w_tiles + i * A_TILE_BYTES, &tmap_w, i * TILE_K, n0, &full[i]);
+                }
+                ap_pdl_wait();
+                const int m0 = (t % tiles_m) * BN;
+                for (int i = 0; i < pre; ++i)
+                    tc::tma_load_2d(a_tiles + i * Cfg::kBBytes, &tmap_a, i * TILE_K, m0, &full[i]);
+            }
+            long long issued = pre;
+            long long idx = 0;
+            for (int j = 0; j < my_tiles && !*abort_flag; ++j) {
+                const int t = blockIdx.x + j * gridDim.x;
+                const int n0 = (t / tiles_m) * TILE_W, m0 = (t % tiles_m) * BN;
+                for (int kb = 0; kb < nkb; ++kb, ++idx) {
+                    if (idx < pre) continue;
+                    const int s = (int)(idx % STAGES);
+                    const uint32_t ph = (uint32_t)((idx / STAGES) & 1);
+                    if (*abort_flag) break;
+                    if (!tc::mbar_wait(&empty[s], ph ^ 1)) {
+                        *abort_flag = 1;
+                        atomicExch(&g_tc_status, TC_ERR_EMPTY_WAIT);
+                        break;
+                    }
+                    tc::mbar_expect_tx(&full[s], Cfg::kStageBytes);
+                    tc::tma_load_2d(w_tiles + s * A_TILE_BYTES, &tmap_w, kb * TILE_K, n0, &full[s]);
+                    tc::tma_load_2d(a_tiles + s * Cfg::kBBytes, &tmap_a, kb * TILE_K, m0, &full[s]);
+                    issued = idx + 1;
+                }
+            }
+            (void)total;
+            if (*abort_flag) {
+                // let the loads that are still in flight land before the CTA's memory goes away
+                for (long long i = max(0LL, issued - STAGES); i < issued; ++i)
+                    tc::mbar_wait(&full[i % STAGES], (uint32_t)((i / STAGES) & 1), 200000000LL);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::instr_desc_bf16_f32(TILE_W, BN);
+            bool ok = true;
+            long long idx = 0;
+            for (int j = 0; j < my_tiles && ok; ++j) {
+                const int b = j & 1;
+                // the epilogue warps have read this buffer's tile of two rounds ago
+                if (!tc::mbar_wait(&acc_empty[b], (uint32_t)(((j >> 1) & 1) ^ 1))) {
+                    *abort_flag = 1;
+                    atomicExch(&g_tc_status, TC_ERR_ACCUM_WAIT);
+                    ok = false;
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t acc = tmem_base + (uint32_t)(b * BN);
+                for (int kb = 0; kb < nkb; ++kb, ++idx) {
+                    const int s = (int)(idx % STAGES);
+                    const uint32_t ph = (uint32_t)((idx / STAGES) & 1);
+                    if (*abort_flag) { ok = false; break; }
+                    if (!tc::mbar_wait(&full[s], ph)) {
+                        *abort_flag = 1;
+                        atomicExch(&g_tc_status, TC_ERR_FULL_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    tc::fence_after_sync();
+                    const uint64_t wd = tc::smem_desc_k_major_sw128(w_tiles + s * A_TILE_BYTES);
+                    const uint64_t ad = tc::smem_desc_k_major_sw128(a_tiles + s * Cfg::kBBytes);
+#pragma unroll
+                    for (int k = 0; k < TILE_K / 16; ++k)
+                        tc::mma_bf16(acc, wd + 2 * k, ad + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc::mma_commit(&empty[s]);
+                }
+                if (ok) tc::mma_commit(&acc_full[b]);
+            }
+        }
+    } else {
+        // epilogue: warp q reads lanes 32q..32q+31 = weight rows n0 + 32q + lane
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        ap_pdl_wait();          // `out` may still be read by an earlier kernel
+        bool ok = true;
+        for (int j = 0; j < my_tiles && ok; ++j) {
+            const int t = blockIdx.x + j * gridDim.x;
+            const int n0 = (t / tiles_m) * TILE_W, m0 = (t % tiles_m) * BN;
+            const int b = j & 1;
+            // tcgen05.ld is warp-wide: the whole warp goes on, or none of it
+            if (!__all_sync(0xffffffffu, tc::mbar_wait(&acc_full[b], (uint32_t)((j >> 1) & 1)))) {
+                if (!*abort_flag) {
+                    *abort_flag = 1;
+                    atomicExch(&g_tc_status, TC_ERR_ACCUM_WAIT);
+                }
+                ok = false;
+                break;
+            }
+            tc::fence_after_sync();
+            const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN);
+            const int n = n0 + row;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                if (m0 + c >= M) break;
+                uint32_t v[32];
+                tc::tmem_ld_x32(acc + (uint32_t)c, v);
+                tc::tmem_ld_wait();
+                if (PAIRS) {
+                    // even lane: gate of column n/2, odd lane: up.  The even lane finishes rows
+                    // c..c+15, the odd lane rows c+16..c+31, each with the other's half.
+                    const bool odd = lane & 1;
+                    TO* dst = out + (size_t)(m0 + c + (odd ? 16 : 0)) * ldc + (n >> 1);
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj) {
+                        const uint32_t other = __shfl_xor_sync(0xffffffffu, odd ? v[jj] : v[16 + jj], 1);
+                        // the gate and the up value pass through the storage type, as when the
+                        // activation is a kernel of its own
+                        const float g = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? other : v[jj])));
+                        const float u = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? v[16 + jj] : other)));
+                        const int m = m0 + c + (odd ? 16 : 0) + jj;
+                        if (m < M && n < N)
+                            dst[(size_t)jj * ldc] = ap_from_float<TO>(__fdividef(g, 1.0f + __expf(-g)) * u);
+                    }
+                } else if (n < N) {
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) {
+                        const int m = m0 + c + jj;
+                        if (m < M) out[(size_t)m * ldc + n] = ap_from_float<TO>(__uint_as_float(v[jj]));
+                    }
+                }
+            }
+            tc::fence_before_sync();
+            tc::mbar_arrive(&acc_empty[b]);
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    ap_pdl_trigger();
+    if (warp == 1) {
+        __syncwarp();
+        tc::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+template <int BN, typename TO, bool PAIRS>
+static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K,
+                             long long ldc, cudaStream_t stream) {
+    using Cfg = PersistCfg<BN>;
+    auto kern = gemm_tc_persistent_kernel<BN, TO, PAIRS>;
+    static bool configured = false;
+    static int sms = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        AP_REQUIRE(e == cudaSuccess, "gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::kSmemBytes,
+                   cudaGetErrorString(e));
+        int dev = 0;
+        AP_REQUIRE(cudaGetDevice(&dev) == cudaSuccess &&
+                       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0,
+                   "gemm_tc: cannot read the number of SMs");
+        configured = true;
+    }
+    const int tiles_m = (M + BN - 1) / BN;
+    const long long tiles = (long long)tiles_m * ((N + TILE_W - 1) / TILE_W);
+    AP_REQUIRE(tiles < (1LL << 30), "gemm_tc: too many output tiles");
+    dim3 grid((unsigned)min((long long)sms, tiles), 1, 1);
+    AP_CHECK_PDL_LAUNCH("gemm_tc_persistent", ap_launch_pdl(kern, grid, dim3(192), (size_t)Cfg::kSmemBytes, stream, mw,
+                                                            ma, (TO*)out, M, N, K, ldc, tiles_m, (int)tiles));
+    return AP_OK;
+}
+
+// The persistent kernel (see gemm_tc_persistent_kernel), for products with more than 64 rows.
+//   pairs == 0: out[M, N] = a * w^T for w [N, K].
+//   pairs != 0: w [N, K] has gate and up rows alternating; out[M, N/2] = silu(gate) * up.
+AP_EXPORT int ap_gemm_tc_persistent(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K,
+                                    long long lda, long long ldw, long long ldc, int pairs, cudaStream_t stream) {
+    AP_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+    if (M == 0) return AP_OK;
+    AP_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
+               "gemm_tc: K=%d and the leading dimensions must be multiples of 8 (16-byte rows for TMA)", K);
+    AP_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
+    AP_REQUIRE(!pairs || N % 2 == 0, "gemm_tc: gate and up rows alternate, so the weight has an even number of rows");
+    AP_REQUIRE(lda >= K && ldw >= K && ldc >= (pairs ? N / 2 : N), "gemm_tc: a leading dimension is below its row length");
+    AP_REQUIRE(out_dtype == AP_F32 || out_dtype == AP_BF16, "gemm_tc: unknown output dtype %d", out_dtype);
+    const int bn = M <= 128 ? 128 : 256;
+    CUtensorMap mw, ma;
+    AP_REQUIRE(make_map(&mw, w, N, K, ldw, TILE_W), "gemm_tc: cannot encode the weight's tensor map");
+    AP_REQUIRE(make_map(&ma, a, M, K, lda, bn), "gemm_tc: cannot encode the activations' tensor map");
+#define GO(BN, PR)                                                                                 \
+    return out_dtype == AP_F32 ? launch_persistent<BN, float, PR>(mw, ma, out, M, N, K, ldc, stream) \
+                               : launch_persistent<BN, bf16, PR>(mw, ma, out, M, N, K, ldc, stream)
+    if (pairs) {
+        if (bn == 128) GO(128, true);
+        GO(256, true);
+    }
+    if (bn == 128) GO(128, false);
+    GO(256, false);
+#undef GO
+}
+
+// Whether the persistent kernel is the one to use for this shape.  It is, except where its
+// tiles fill the last round of SMs badly while the kernel with two weight tiles per CTA
+// covers the whole product in a single, well-filled wave.
+AP_EXPORT int ap_gemm_tc_prefers_persistent(int M, int N, int K) {
+    (void)K;
+    if (M <= 64) return 0;
+    const int bn = M <= 128 ? 128 : 256;
+    const long long rows = (M + bn - 1) / bn;
+    const long long tiles = ((N + TILE_W - 1) / TILE_W) * rows, dual = ((N + 2 * TILE_W - 1) / (2 * TILE_W)) * rows;
+    const long long rounds = (tiles + 147) / 148;
+    const bool badly_filled = tiles * 100 < rounds * 148 * 90;
+    const bool dual_one_wave = dual <= 148 && dual >= 118;
+    return (badly_filled && dual_one_wave && rounds <= 2) ? 0 : 1;
+}
+
 // 0 when every tensor-core product so far ran to its end; else the code of the wait that
 // expired (1 free stage, 2 operands, 3 accumulator).  Synchronises the device.
 AP_EXPORT int ap_gemm_tc_status(void) {

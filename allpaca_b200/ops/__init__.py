@@ -152,14 +152,15 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, table: torch.Ten
          stream_handle())
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """``out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]``."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, pairs: bool = False) -> None:
+    """``out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j]``; with ``pairs`` the gate and up
+    columns alternate: ``silu(gate_up[t, 2j]) * gate_up[t, 2j + 1]``."""
     ptr, code, S, stride, T, N = _partials(gate_up, "gate_up")
     _check(out, "out", dims=2)
     if N != 2 * out.shape[1] or out.shape[0] != T:
         raise KernelError("swiglu: out must be [T, I] for gate_up [T, 2I]")
     call(core(), "ap_swiglu", ptr, code, S, stride, out.data_ptr(), dtype_code(out.dtype), T,
-         out.shape[1], stream_handle())
+         out.shape[1], 1 if pairs else 0, stream_handle())
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -223,6 +224,26 @@ def gemm_tc_dual(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bo
         raise KernelError(f"gemm_tc_dual: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     call(core(), "ap_gemm_tc_dual", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
          M, N, K, K, K, N, 1 if swiglu else 0, stream_handle())
+
+
+def gemm_tc_persistent(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pairs: bool = False) -> None:
+    """The persistent tensor-core product for more than 64 rows: one CTA per SM walks the
+    output tiles, and a tile is written out while the next one is being computed.
+
+    ``pairs`` False: ``out[M,N] = a[M,K] @ w[N,K]^T``.  True: the rows of ``w [N,K]`` alternate
+    gate, up, gate, up ... and ``out[M,N/2] = silu(gate) * up``.
+    """
+    _check(a, "a", torch.bfloat16, 2)
+    _check(w, "w", torch.bfloat16, 2)
+    _check(out, "out", dims=2)
+    M, K = a.shape
+    N = w.shape[0]
+    n_out = N // 2 if pairs else N
+    if w.shape[1] != K or tuple(out.shape) != (M, n_out) or (pairs and N % 2):
+        raise KernelError(f"gemm_tc_persistent: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, "
+                          f"out {tuple(out.shape)}")
+    call(core(), "ap_gemm_tc_persistent", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+         M, N, K, K, K, n_out, 1 if pairs else 0, stream_handle())
 
 
 def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
@@ -358,6 +379,13 @@ def gemm_tc_prefers_dual(M: int, N: int, K: int) -> bool:
     """Whether the kernel with two weight tiles per CTA is the faster one for this shape."""
     lib = core()
     return hasattr(lib, "ap_gemm_tc_prefers_dual") and bool(lib.ap_gemm_tc_prefers_dual(int(M), int(N), int(K)))
+
+
+def gemm_tc_prefers_persistent(M: int, N: int, K: int) -> bool:
+    """Whether the persistent kernel is the faster one for this shape (more than 64 rows)."""
+    lib = core()
+    return hasattr(lib, "ap_gemm_tc_prefers_persistent") and \
+        bool(lib.ap_gemm_tc_prefers_persistent(int(M), int(N), int(K)))
 
 
 def gemm_tc_status() -> int:

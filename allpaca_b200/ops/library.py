@@ -27,7 +27,7 @@ _CORE_SIGNATURES = {
     "ap_residual_add": [_P, _P, _I, _L, _L, _P],
     "ap_rope_kv_store": [_P, _I, _I, _L, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _L, _P],
     "ap_rope_table": [_P, _P, _P, _I, _I, _P],
-    "ap_swiglu": [_P, _I, _I, _L, _P, _I, _I, _I, _P],
+    "ap_swiglu": [_P, _I, _I, _L, _P, _I, _I, _I, _I, _P],
     "ap_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "ap_argmax": [_P, _L, _I, _I, _P, _P],
     "ap_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
@@ -36,8 +36,10 @@ _OPTIONAL_CORE_SIGNATURES = {
     # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, stream)
     "ap_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _L, _I, _P],
     "ap_gemm_tc_dual": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P],
+    "ap_gemm_tc_persistent": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P],
     "ap_gemm_tc_plan": [_I, _I, _I],
     "ap_gemm_tc_prefers_dual": [_I, _I, _I],
+    "ap_gemm_tc_prefers_persistent": [_I, _I, _I],
     "ap_gemm_tc_set_l2_prefetch": [_L],
     "ap_gemm_tc_status": [],
     "ap_gemm_tc_reset_status": [],

@@ -58,7 +58,9 @@ class Linear:
         else:
             out = ws.get(buffer_name, (T, N), torch.float32 if kind == "float32" else self.env.dtype)
             target = out
-        if tc and nsplit == 1 and ops.gemm_tc_prefers_dual(T, N, self.in_features):
+        if tc and T > 64 and ops.gemm_tc_prefers_persistent(T, N, self.in_features):
+            ops.gemm_tc_persistent(a, self.weight, target)
+        elif tc and nsplit == 1 and ops.gemm_tc_prefers_dual(T, N, self.in_features):
             ops.gemm_tc_dual(a, self.weight, target)
         elif tc:
             ops.gemm_tc(a, self.weight, target, nsplit, reduce=nsplit > 1)
@@ -67,12 +69,12 @@ class Linear:
         return out
 
     def forward_gated(self, a: torch.Tensor, buffer_name: str) -> Optional[torch.Tensor]:
-        """For a weight that stacks gate rows over up rows: ``silu(a W_gate^T) * (a W_up^T)`` in
-        one kernel, ``[T, out/2]`` in the activation type; None when the shape is not one the
-        fused kernel is used for (the caller then multiplies and activates separately)."""
+        """For a weight whose rows alternate gate and up: ``silu(a W_gate^T) * (a W_up^T)`` in one
+        kernel, ``[T, out/2]`` in the activation type; None when the shape is not one the fused
+        kernel is used for (the caller then multiplies and activates separately)."""
         T = a.shape[0]
         if not self.uses_tensor_cores() or T <= 64 or self.out_features % 2:
             return None
         out = self.env.workspace.get(buffer_name, (T, self.out_features // 2), self.env.dtype)
-        ops.gemm_tc_dual(a, self.weight, out, swiglu=True)
+        ops.gemm_tc_persistent(a, self.weight, out, pairs=True)
         return out

@@ -2,8 +2,10 @@
 
 ``silu(z) = z / (1 + exp(-z))`` (crates/allpaca-cpu/src/kernels.rs:869-871); gate and up
 are separate tensors in the checkpoint (crates/allpaca-core/src/model.rs:5664-5705) and one
-stacked matrix ``[Wgate; Wup]`` here, so one product yields ``[T, 2I]`` and the activation
-kernel reads both halves of a row.
+matrix here whose rows alternate gate, up, gate, up ...: one product yields ``[T, 2I]`` with
+each (gate, up) pair side by side.  On the tensor cores row 2i and 2i+1 of the weight are
+neighbouring lanes of the accumulator, so for many rows the product's epilogue applies the
+activation itself; for few rows a small kernel reads the pairs.
 """
 from __future__ import annotations
 
@@ -34,7 +36,8 @@ class SwiGLU(FeedForward):
                 "down_proj.weight": WeightSpec((self.hidden, self.inter))}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.gate_up.load(torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0))
+        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        self.gate_up.load(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden))
         self.down.load(tensors["down_proj.weight"])
 
     def forward(self, h: torch.Tensor, step) -> torch.Tensor:
@@ -43,5 +46,5 @@ class SwiGLU(FeedForward):
         if act is None:
             gu = self.gate_up.forward(h, "ffn.gate_up", "either")
             act = self.env.workspace.get("ffn.act", (T, self.inter), self.env.dtype)
-            ops.swiglu(gu, act)
+            ops.swiglu(gu, act, pairs=True)
         return self.down.forward(act, "ffn.down", "delta")

@@ -38,8 +38,8 @@ def test_two_layers_of_the_8b_shape(tmp_path):
                 w[prefix + "self_attn.v_proj.weight"] = qkv[Q + KV:]
                 w[prefix + "self_attn.o_proj.weight"] = block.mixer.o.weight
                 gu = block.feed_forward.gate_up.weight
-                w[prefix + "mlp.gate_proj.weight"] = gu[:cfg.intermediate_size]
-                w[prefix + "mlp.up_proj.weight"] = gu[cfg.intermediate_size:]
+                w[prefix + "mlp.gate_proj.weight"] = gu[0::2]      # gate and up rows alternate
+                w[prefix + "mlp.up_proj.weight"] = gu[1::2]
                 w[prefix + "mlp.down_proj.weight"] = block.feed_forward.down.weight
                 w[prefix + "input_layernorm.weight"] = block.mixer_norm.weight
                 w[prefix + "post_attention_layernorm.weight"] = block.feed_forward_norm.weight

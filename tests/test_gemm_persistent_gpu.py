@@ -1,0 +1,56 @@
+"""The persistent tensor-core product against a plain 32-bit product: sizes that are no
+multiple of a tile, fewer tiles than SMs and many more, and the fused gated activation over
+alternating gate and up rows."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from allpaca_b200 import ops as o
+    return o
+
+
+SHAPES = [(65, 128, 64), (128, 384, 256), (200, 1000, 520), (257, 4096, 1024), (700, 18944, 128), (2048, 1536, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_plain_product(ops, M, N, K, out_dtype):
+    g = torch.Generator().manual_seed(M + N + K)
+    a = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.5).bfloat16()
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=out_dtype)
+    ops.gemm_tc_persistent(a.cuda(), w.cuda(), out)
+    ops.check_kernel_status()
+    ref = a.double() @ w.double().T
+    tol = 1e-5 if out_dtype == torch.float32 else 5e-3
+    assert float((out.cpu().double() - ref).abs().max() / ref.abs().max()) < tol
+
+
+@pytest.mark.parametrize("M,I,K", [(65, 64, 64), (130, 333, 256), (513, 1409, 512), (2048, 2048, 1024)])
+def test_gated_activation_over_alternating_rows(ops, M, I, K):
+    g = torch.Generator().manual_seed(M + I + K)
+    a = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    gate = (torch.randn(I, K, generator=g) * 0.3).bfloat16()
+    up = (torch.randn(I, K, generator=g) * 0.3).bfloat16()
+    w = torch.stack([gate, up], dim=1).reshape(2 * I, K).contiguous()
+    out = torch.full((M, I), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_tc_persistent(a.cuda(), w.cuda(), out, pairs=True)
+    ops.check_kernel_status()
+    gv = (a.double() @ gate.double().T).float().bfloat16().double()
+    uv = (a.double() @ up.double().T).float().bfloat16().double()
+    ref = gv / (1.0 + torch.exp(-gv)) * uv
+    assert torch.isfinite(out).all()
+    assert float((out.cpu().double() - ref).abs().max() / ref.abs().max()) < 1e-2
+
+
+def test_a_view_with_a_leading_dimension_is_refused_or_right(ops):
+    """Shapes the kernel cannot take are refused with a message, never computed wrongly."""
+    a = torch.randn(70, 60, device="cuda").bfloat16()          # K = 60: rows of 120 bytes
+    w = torch.randn(128, 60, device="cuda").bfloat16()
+    out = torch.empty(70, 128, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(Exception, match="multiples of 8"):
+        ops.gemm_tc_persistent(a, w, out)

@@ -144,16 +144,19 @@ def test_rope_adjacent_pairing_and_no_rotation(ops):
 
 # ---------------------------------------------------------------- gated activation
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_swiglu(ops, dtype):
+@pytest.mark.parametrize("I", [177, 200])
+@pytest.mark.parametrize("pairs", [False, True])
+def test_swiglu(ops, dtype, I, pairs):
     g = torch.Generator().manual_seed(2)
-    T, I = 5, 177
+    T = 5
     S = 3 if dtype == torch.float32 else 1
     gu = torch.randn(S, T, 2 * I, generator=g) * 2
     inp = gu if dtype == torch.float32 else gu[0].to(dtype)
     out = torch.empty(T, I, dtype=dtype, device="cuda")
-    ops.swiglu(dev(inp), out)
+    ops.swiglu(dev(inp), out, pairs=pairs)
     full = (gu.sum(0) if dtype == torch.float32 else inp.float()).double()
-    ref = plain_llama.silu(full[:, :I]) * full[:, I:]
+    gate, up = (full[:, 0::2], full[:, 1::2]) if pairs else (full[:, :I], full[:, I:])
+    ref = plain_llama.silu(gate) * up
     assert rel_err(out.cpu(), ref) < (1e-5 if dtype == torch.float32 else 5e-3)
 
 
