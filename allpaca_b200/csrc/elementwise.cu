@@ -126,6 +126,9 @@ static int launch_add_rmsnorm(float* x, const float* delta, int S, size_t delta_
     const int per = vec ? 4 : 1;
     int threads = ((H + per - 1) / per + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+    // many rows: smaller blocks, so that an SM holds several rows and one row's reduction
+    // does not leave it idle
+    if (R >= 4 * 148 && threads > 256) threads = 256;
     AP_CHECK_PDL_LAUNCH("add_rmsnorm", ap_launch_pdl(kern, dim3(R), dim3(threads), smem, stream, x, delta, S,
                                                      delta_stride, (const TW*)w, eps, (TO*)out, rows, H));
     return AP_OK;

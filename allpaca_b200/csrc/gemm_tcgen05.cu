@@ -48,7 +48,12 @@ template <int BN, bool CLUSTER = false> struct TileCfg {
 // their partial tiles through distributed shared memory, each CTA finishing a band of the
 // 128 weight rows; `out` is then the finished [M, N] matrix.  Otherwise slice z writes its
 // partial sums to out + z * split_stride.
-template <int BN, typename TO, bool CLUSTER>
+// PAIRS: the weight's rows alternate gate, up, gate, up ...; the finished sums of row 2i and
+// 2i+1 become out[m, i] = silu(gate) * up (out is [M, N/2]), so that the gated activation of a
+// decode step needs no kernel of its own.
+__device__ __forceinline__ float gated(float gate, float up) { return __fdividef(gate, 1.0f + __expf(-gate)) * up; }
+
+template <int BN, typename TO, bool CLUSTER, bool PAIRS = false>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                TO* __restrict__ out, int M, int N, int K, long long ldc, int kb_per_split,
@@ -212,7 +217,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 uint32_t v[16];
                 tc::tmem_ld_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
                 tc::tmem_ld_wait();
-                if (n < N) {
+                if (PAIRS) {
+                    // even lane: gate of column n/2, odd lane: up.  The even lane finishes rows
+                    // c..c+7, the odd lane rows c+8..c+15, each with the other's half; both values
+                    // pass through the storage type, as when the activation is a kernel of its own.
+                    const bool odd = lane & 1;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t other = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[8 + j], 1);
+                        const float gt = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? other : v[j])));
+                        const float up = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? v[8 + j] : other)));
+                        const int m = m0 + c + (odd ? 8 : 0) + j;
+                        if (m < M && n < N) out[(size_t)m * ldc + (n >> 1)] = ap_from_float<TO>(gated(gt, up));
+                    }
+                } else if (n < N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + c + j;
@@ -220,10 +238,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     }
                 }
             }
-        } else if (nkb == 0 && n < N) {
+        } else if (nkb == 0 && n < N && (!PAIRS || !(lane & 1))) {
             for (int c = 0; c < BN; ++c) {
                 const int m = m0 + c;
-                if (m < M) out[(size_t)m * ldc + n] = ap_from_float<TO>(0.f);
+                if (m < M) out[(size_t)m * ldc + (PAIRS ? n >> 1 : n)] = ap_from_float<TO>(0.f);
             }
         }
     }
@@ -237,12 +255,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const int e = (int)threadIdx.x - 64;              // the four epilogue warps add the band
         if (e >= 0 && !skip) {
             const int mcols = min(BN, M - m0);
-            for (int idx = e; idx < rows * mcols; idx += 128) {
-                const int c = idx / rows, i = idx - c * rows;
-                float sum = 0.f;
-                for (int s = 0; s < S; ++s) sum += reduce[(s * BN + c) * band + i];   // slices in order
-                const int n = n0 + first + i;
-                if (n < N) out[(size_t)(m0 + c) * ldc + n] = ap_from_float<TO>(sum);
+            if (PAIRS) {
+                // a band starts at an even row and has an even number of rows: pairs stay together
+                const int prs = rows / 2;
+                for (int idx = e; idx < prs * mcols; idx += 128) {
+                    const int c = idx / prs, i = idx - c * prs;
+                    float gt = 0.f, up = 0.f;
+                    for (int s = 0; s < S; ++s) {                                          // slices in order
+                        gt += reduce[(s * BN + c) * band + 2 * i];
+                        up += reduce[(s * BN + c) * band + 2 * i + 1];
+                    }
+                    gt = ap_to_float(ap_from_float<TO>(gt));
+                    up = ap_to_float(ap_from_float<TO>(up));
+                    const int n = n0 + first + 2 * i;
+                    if (n < N) out[(size_t)(m0 + c) * ldc + (n >> 1)] = ap_from_float<TO>(gated(gt, up));
+                }
+            } else {
+                for (int idx = e; idx < rows * mcols; idx += 128) {
+                    const int c = idx / rows, i = idx - c * rows;
+                    float sum = 0.f;
+                    for (int s = 0; s < S; ++s) sum += reduce[(s * BN + c) * band + i];   // slices in order
+                    const int n = n0 + first + i;
+                    if (n < N) out[(size_t)(m0 + c) * ldc + n] = ap_from_float<TO>(sum);
+                }
             }
         }
     }
@@ -481,11 +516,11 @@ AP_EXPORT int ap_gemm_tc_plan(int M, int N, int K) {
     return (kb_total + per - 1) / per;
 }
 
-template <int BN, typename TO, bool CLUSTER>
+template <int BN, typename TO, bool CLUSTER, bool PAIRS = false>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K,
                      long long ldc, int nsplit, long long split_stride, cudaStream_t stream) {
     using Cfg = TileCfg<BN, CLUSTER>;
-    auto kern = gemm_tc_kernel<BN, TO, CLUSTER>;
+    auto kern = gemm_tc_kernel<BN, TO, CLUSTER, PAIRS>;
     constexpr int smem = CLUSTER ? Cfg::kSmemBytesCluster : Cfg::kSmemBytes;
     static bool configured = false;
     if (!configured) {
@@ -537,17 +572,22 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, in
 // reduce != 0: the K slices add up inside a thread-block cluster and `out` is the finished
 // [M, N] matrix (any output type, nsplit <= 8, M <= 64); else slice z writes 32-bit partial
 // sums at out + z * split_stride.
+// pairs != 0 (bfloat16 out, M <= 64, finished sums only): w's rows alternate gate and up, and
+// out is [M, N/2] = silu(gate) * up.
 AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K,
                          long long lda, long long ldw, long long ldc, int nsplit, long long split_stride,
-                         int reduce, cudaStream_t stream) {
+                         int reduce, int pairs, cudaStream_t stream) {
     AP_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     if (M == 0) return AP_OK;
     AP_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
                "gemm_tc: K=%d and the leading dimensions must be multiples of 8 (16-byte rows for TMA)", K);
     AP_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
-    AP_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_tc: a leading dimension is below its row length");
+    AP_REQUIRE(lda >= K && ldw >= K && ldc >= (pairs ? N / 2 : N), "gemm_tc: a leading dimension is below its row length");
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     AP_REQUIRE(nsplit >= 1 && nsplit <= kb_total && nsplit <= 65535, "gemm_tc: cannot split K=%d into %d", K, nsplit);
+    AP_REQUIRE(!pairs || (N % 2 == 0 && M <= 64 && out_dtype == AP_BF16 && (nsplit == 1 || reduce)),
+               "gemm_tc: the gated epilogue takes an even number of weight rows, at most 64 rows of a, "
+               "bfloat16 output and finished sums");
     AP_REQUIRE((long long)(nsplit - 1) * ((kb_total + nsplit - 1) / nsplit) < kb_total,
                "gemm_tc: %d slices leave an empty one for K=%d", nsplit, K);
     AP_REQUIRE(out_dtype == AP_F32 || out_dtype == AP_BF16, "gemm_tc: unknown output dtype %d", out_dtype);
@@ -565,6 +605,22 @@ AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype,
     return out_dtype == AP_F32                                                                           \
                ? launch_tc<BN, float, CL>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, stream)       \
                : launch_tc<BN, bf16, CL>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, stream)
+#define GOP(BN, CL) return launch_tc<BN, bf16, CL, true>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, stream)
+    if (pairs && cluster) {
+        switch (bn) {
+            case 16: GOP(16, true);
+            case 32: GOP(32, true);
+            default: GOP(64, true);
+        }
+    }
+    if (pairs) {
+        switch (bn) {
+            case 16: GOP(16, false);
+            case 32: GOP(32, false);
+            default: GOP(64, false);
+        }
+    }
+#undef GOP
     if (cluster) {
         switch (bn) {
             case 16: GO(16, true);

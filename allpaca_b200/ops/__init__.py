@@ -182,13 +182,14 @@ def tensor_core_gemm_available() -> bool:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1,
-            reduce: bool = False) -> None:
+            reduce: bool = False, pairs: bool = False) -> None:
     """bfloat16 ``a[M,K] @ w[N,K]^T`` on the tcgen05 tensor cores.
 
     ``nsplit`` K slices run as separate CTAs.  With ``reduce`` they add up inside a
     thread-block cluster (at most 8 slices, at most 64 rows) and ``out`` is the finished
     ``[M,N]`` in bfloat16 or float32; without it ``out`` is float32 ``[nsplit, M, N]`` partial
-    sums (``[M,N]`` for ``nsplit == 1``).
+    sums (``[M,N]`` for ``nsplit == 1``).  ``pairs`` (at most 64 rows, finished sums, bfloat16
+    out): the rows of ``w`` alternate gate and up, and ``out[M,N/2] = silu(gate) * up``.
     """
     _check(a, "a", torch.bfloat16, 2)
     _check(w, "w", torch.bfloat16, 2)
@@ -197,7 +198,11 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError("gemm_tc: inner sizes disagree")
-    if nsplit == 1 or reduce:
+    if pairs:
+        if tuple(out.shape) != (M, N // 2) or N % 2:
+            raise KernelError("gemm_tc: out must be [M,N/2] for alternating gate and up rows")
+        stride = 0
+    elif nsplit == 1 or reduce:
         if tuple(out.shape) != (M, N):
             raise KernelError("gemm_tc: out must be [M,N]")
         stride = 0
@@ -206,7 +211,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1
             raise KernelError("gemm_tc: partial sums must be float32 [nsplit,M,N]")
         stride = M * N
     call(core(), "ap_gemm_tc", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
-         M, N, K, K, K, N, nsplit, stride, 1 if reduce else 0, stream_handle())
+         M, N, K, K, K, N // 2 if pairs else N, nsplit, stride, 1 if reduce else 0, 1 if pairs else 0,
+         stream_handle())
 
 
 def gemm_tc_dual(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:

@@ -33,8 +33,8 @@ _CORE_SIGNATURES = {
     "ap_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
 }
 _OPTIONAL_CORE_SIGNATURES = {
-    # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, stream)
-    "ap_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _L, _I, _P],
+    # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, pairs, stream)
+    "ap_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _L, _I, _I, _P],
     "ap_gemm_tc_dual": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P],
     "ap_gemm_tc_persistent": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P],
     "ap_gemm_tc_plan": [_I, _I, _I],

@@ -73,8 +73,12 @@ class Linear:
         kernel, ``[T, out/2]`` in the activation type; None when the shape is not one the fused
         kernel is used for (the caller then multiplies and activates separately)."""
         T = a.shape[0]
-        if not self.uses_tensor_cores() or T <= 64 or self.out_features % 2:
+        if not self.uses_tensor_cores() or self.out_features % 2:
             return None
         out = self.env.workspace.get(buffer_name, (T, self.out_features // 2), self.env.dtype)
-        ops.gemm_tc_persistent(a, self.weight, out, pairs=True)
+        if T > 64:
+            ops.gemm_tc_persistent(a, self.weight, out, pairs=True)
+        else:
+            nsplit = ops.gemm_tc_splits(T, self.out_features, self.in_features)
+            ops.gemm_tc(a, self.weight, out, nsplit, reduce=nsplit > 1, pairs=True)
         return out

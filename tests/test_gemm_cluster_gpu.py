@@ -46,3 +46,24 @@ def test_cluster_reduction_refuses_too_many_slices():
     out = torch.empty(4, 128, device="cuda")
     with pytest.raises(ops.KernelError, match="cluster"):
         ops.gemm_tc(a, w, out, 9, reduce=True)
+
+
+@pytest.mark.parametrize("M,I,K,nsplit", [(1, 64, 512, 1), (8, 200, 512, 4), (8, 1409, 1024, 8), (33, 96, 256, 2),
+                                          (64, 300, 512, 1), (5, 7168, 256, 1)])
+def test_gated_epilogue_over_alternating_rows(M, I, K, nsplit):
+    """Few rows: silu(gate) * up straight from the product, gate and up rows alternating, with
+    the K slices added in a cluster or none at all."""
+    from allpaca_b200 import ops
+    g = torch.Generator().manual_seed(M + I + K)
+    a = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    gate = (torch.randn(I, K, generator=g) * 0.3).bfloat16()
+    up = (torch.randn(I, K, generator=g) * 0.3).bfloat16()
+    w = torch.stack([gate, up], dim=1).reshape(2 * I, K).contiguous()
+    out = torch.full((M, I), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_tc(a.cuda(), w.cuda(), out, nsplit, reduce=nsplit > 1, pairs=True)
+    ops.check_kernel_status()
+    gv = (a.double() @ gate.double().T).float().bfloat16().double()
+    uv = (a.double() @ up.double().T).float().bfloat16().double()
+    ref = gv / (1.0 + torch.exp(-gv)) * uv
+    assert torch.isfinite(out).all()
+    assert float((out.cpu().double() - ref).abs().max() / ref.abs().max()) < 1e-2
