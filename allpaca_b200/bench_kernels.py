@@ -1,6 +1,6 @@
 """Times one kernel in isolation, cold in L2, and prints its rate against the roofline.
 
-    python -m allpaca_b200.bench_kernels gemm --m 8 --n 6144 --k 4096 [--splits S] [--partials]
+    python -m allpaca_b200.bench_kernels gemm --m 8 --n 6144 --k 4096 [--splits S] [--partials] [--swiglu]
     python -m allpaca_b200.bench_kernels attention --batch 8 --context 4096
     python -m allpaca_b200.bench_kernels prefill-attention --tokens 2048
 
@@ -53,16 +53,23 @@ def bench_gemm(args) -> dict:
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     S = args.splits or ops.gemm_tc_splits(M, N, K)
     odt = torch.float32 if args.out == "float32" else torch.bfloat16
-    if args.persistent:
-        n_out = N // 2 if args.swiglu else N
-        out = torch.empty(M, n_out, device="cuda", dtype=odt)
+    kernel = "gemm_tc"
+    if M > 64 and not args.dual and not args.single:
+        # the persistent kernel; with --swiglu the rows of w alternate gate and up
+        kernel = "gemm_tc_persistent"
+        out = torch.empty(M, N // 2 if args.swiglu else N, device="cuda", dtype=odt)
         fn = lambda i: ops.gemm_tc_persistent(a, ws[i % copies], out, pairs=args.swiglu)   # noqa: E731
         S = 1
-    elif args.dual or args.swiglu:
-        n_out = N // 2 if args.swiglu else N
-        out = torch.empty(M, n_out, device="cuda", dtype=odt)
+    elif args.dual:
+        # two weight tiles per CTA; with --swiglu w is [gate; up]
+        kernel = "gemm_tc_dual"
+        out = torch.empty(M, N // 2 if args.swiglu else N, device="cuda", dtype=odt)
         fn = lambda i: ops.gemm_tc_dual(a, ws[i % copies], out, swiglu=args.swiglu)   # noqa: E731
         S = 1
+    elif args.swiglu:
+        # few rows: the gated activation in the epilogue of the (cluster) kernel
+        out = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
+        fn = lambda i: ops.gemm_tc(a, ws[i % copies], out, S, reduce=S > 1, pairs=True)      # noqa: E731
     elif args.partials and S > 1:
         out = torch.empty(S, M, N, device="cuda", dtype=torch.float32)
         fn = lambda i: ops.gemm_tc(a, ws[i % copies], out, S, reduce=False)      # noqa: E731
@@ -73,7 +80,7 @@ def bench_gemm(args) -> dict:
     ops.check_kernel_status()
     nbytes = N * K * 2 + M * K * 2 + out.numel() * out.element_size()
     flops = 2.0 * M * N * K
-    return {"kernel": "gemm_tc_persistent" if args.persistent else "gemm_tc_dual" if (args.dual or args.swiglu) else "gemm_tc", "M": M, "N": N, "K": K, "splits": S, "partials": bool(args.partials),
+    return {"kernel": kernel, "M": M, "N": N, "K": K, "splits": S, "partials": bool(args.partials),
             "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
@@ -118,10 +125,11 @@ def bench_attention(args) -> dict:
         cache, table = caches[i % copies]
         ops.attention(q, out, cache, table, seq, pos, nh, nkv, hd, 1.0 / math.sqrt(hd), 0, seq_start=start,
                       query_lens=[1] * B, max_context=C, scratch=scratch,
-                      zero_scratch=None if args.separate_merge else zero_scratch)
+                      zero_scratch=zero_scratch if args.fused_merge else None, use_tma=not args.cp_async)
     us = _time(fn, args.iters, args.warmup, not args.no_graph)
-    return {"kernel": "attention_split+merge", "batch": B, "context": C, "heads": nh, "kv_heads": nkv,
-            "head_dim": hd, "splits": ops.decode_splits(B, nh, nkv, C), "us": round(us, 2),
+    return {"kernel": "attention_split+merge" if args.cp_async else "attention_split_tma+merge", "batch": B, "context": C, "heads": nh, "kv_heads": nkv,
+            "head_dim": hd, "splits": ops.decode_splits(B, nh, nkv, C, slots=444 if args.cp_async else 296),
+            "us": round(us, 2),
             "GBps": round(per / us / 1e3, 1)}
 
 
@@ -159,10 +167,9 @@ def main(argv=None) -> int:
             s.add_argument("--splits", type=int, default=0, help="K slices (0: the kernel's own plan)")
             s.add_argument("--partials", action="store_true", help="write partial sums instead of adding in a cluster")
             s.add_argument("--out", choices=["float32", "bfloat16"], default="bfloat16")
-            s.add_argument("--dual", action="store_true", help="two weight tiles per CTA")
-            s.add_argument("--swiglu", action="store_true", help="w is [gate; up]: fused gated activation")
-            s.add_argument("--persistent", action="store_true",
-                           help="the persistent kernel (with --swiglu: gate and up rows alternate)")
+            s.add_argument("--dual", action="store_true", help="more than 64 rows: two weight tiles per CTA")
+            s.add_argument("--single", action="store_true", help="more than 64 rows: one tile per CTA, not persistent")
+            s.add_argument("--swiglu", action="store_true", help="w holds gate and up rows: fused gated activation")
         else:
             s.add_argument("--heads", type=int, default=32)
             s.add_argument("--kv-heads", type=int, default=8)
@@ -171,7 +178,9 @@ def main(argv=None) -> int:
             s.add_argument("--batch", type=int, default=8)
             s.add_argument("--context", type=int, default=4096)
             s.add_argument("--tokens", type=int, default=2048)
-            s.add_argument("--separate-merge", action="store_true", help="combine key slices in a second kernel")
+            s.add_argument("--fused-merge", action="store_true",
+                           help="cp.async kernel: the last slice to arrive combines them all")
+            s.add_argument("--cp-async", action="store_true", help="decode: the cp.async kernel instead of the TMA one")
             s.add_argument("--splits", type=int, default=0, help="key slices (0: the kernel's own plan)")
             s.add_argument("--mma-sync", action="store_true", help="prompt attention with the mma.sync tile kernel")
     args = p.parse_args(argv)

@@ -123,9 +123,19 @@ __device__ __forceinline__ void fetch_tile(uint8_t* smem, int stage, int k0, int
     }
 }
 
+// Where 16-byte chunk `chunk` of key `key` lies in a K or V tile.  Padded rows (filled by
+// cp.async) or, SWZ, what TMA writes with the 128-byte swizzle: one [64 keys x 128 bytes]
+// block per 64 columns of the head, the chunk index XORed with the key's low bits.  Both
+// give conflict-free ldmatrix.
+#define SWZ_HALF_BYTES (BKV * 128)
+template <bool SWZ> __device__ __forceinline__ uint32_t tile_offset(int key, int chunk) {
+    if (SWZ) return (uint32_t)((chunk >> 3) * SWZ_HALF_BYTES + key * 128 + (((chunk & 7) ^ (key & 7)) << 4));
+    return (uint32_t)(key * ROW_BYTES + chunk * 16);
+}
+
 // One warp's share of a tile: NT n-tiles of 8 keys starting at key `key0` of the tile.
 // Updates the running maximum (log2 domain), the per-thread partial sums and the output.
-template <int NT>
+template <int NT, bool SWZ = false>
 __device__ __forceinline__ void process_keys(const uint8_t* ks, const uint8_t* vs, int key0, int k0,
                                              const uint32_t (&qf)[KSTEPS][4], float (&o)[DTILES][4],
                                              float (&m)[2], float (&l)[2], const int (&qpos)[2],
@@ -144,7 +154,7 @@ __device__ __forceinline__ void process_keys(const uint8_t* ks, const uint8_t* v
         for (int np = 0; np < NT / 2; ++np) {
             uint32_t b[4];
             const int key = key0 + np * 16 + (mi >> 1) * 8 + r8;
-            ldmatrix_x4(b, ks_base + key * ROW_BYTES + (kk * 2 + (mi & 1)) * 16);
+            ldmatrix_x4(b, ks_base + tile_offset<SWZ>(key, kk * 2 + (mi & 1)));
             mma_16816(s[2 * np], qf[kk], b[0], b[1]);
             mma_16816(s[2 * np + 1], qf[kk], b[2], b[3]);
         }
@@ -213,7 +223,7 @@ __device__ __forceinline__ void process_keys(const uint8_t* ks, const uint8_t* v
         for (int dp = 0; dp < DTILES / 2; ++dp) {
             uint32_t b[4];
             const int key = key0 + ksx * 16 + (mi & 1) * 8 + r8;
-            ldmatrix_x4_trans(b, vs_base + key * ROW_BYTES + (dp * 2 + (mi >> 1)) * 16);
+            ldmatrix_x4_trans(b, vs_base + tile_offset<SWZ>(key, dp * 2 + (mi >> 1)));
             mma_16816(o[2 * dp], a, b[0], b[1]);
             mma_16816(o[2 * dp + 1], a, b[2], b[3]);
         }
@@ -600,6 +610,306 @@ AP_EXPORT int ap_attention_tc_tokens_per_tile(int nh, int nkv) {
     const int hc = reps < 64 ? reps : 64;
     return 64 / hc;
 }
+
+// ---------------------------------------------------------------------------
+// The split kernel fed by TMA, for head sizes 64 and 128 and pages of 8, 16, 32 or 64 keys.
+// A decode step's attention only streams the cache, so what matters is how many bytes are in
+// flight: here a producer warp (one lane per page of a tile, the page ids read from the block
+// table one tile ahead) keeps a ring of three 64-key tiles of K and V loading by
+// cp.async.bulk.tensor (128-byte swizzle), with no address arithmetic in the consumer warps
+// and no round trip to the block table inside the loop.  The four consumer warps take 16 keys
+// of every tile each, as in attention_split_kernel, and the slices are combined the same way.
+// Every barrier wait is bounded; on expiry a status word is raised and the CTA leaves.
+// ---------------------------------------------------------------------------
+#if (AP_HEAD_DIM == 64 || AP_HEAD_DIM == 128)
+#include "tcgen05.cuh"
+#include <cuda.h>
+
+#define DT_STAGES 3
+#define DT_THREADS 160                        // four consumer warps, one producer warp
+#define DT_NHALF (HD / 64)
+#define DT_KV_BYTES (DT_NHALF * SWZ_HALF_BYTES)   // K (or V) of one tile
+#define DT_STAGE_BYTES (2 * DT_KV_BYTES)
+#define DT_ERR_WAIT 6
+
+static __device__ int g_dt_status;
+
+struct DtSmem {
+    static constexpr int kBars = DT_STAGES * DT_STAGE_BYTES;
+    static constexpr int kUsed = kBars + 128;
+    static constexpr int kMerge = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
+    static constexpr int kTotal = (kUsed > kMerge ? kUsed : kMerge) + 1024;   // + alignment slack
+};
+
+__global__ void __launch_bounds__(DT_THREADS)
+attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + DtSmem::kBars);
+    uint64_t* empty = full + DT_STAGES;
+    volatile int* abort_flag = (volatile int*)(empty + DT_STAGES);
+    if (*(volatile int*)&g_dt_status != 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < DT_STAGES; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], 4);
+        }
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::prefetch_tensormap(&tmap_kv);
+    }
+    // V starts as zeros: what a skipped page leaves in a stage must be finite, because a
+    // probability of zero times a NaN would poison the row
+    for (int s = 0; s < DT_STAGES; ++s)
+        for (int i = threadIdx.x; i < DT_KV_BYTES / 16; i += DT_THREADS)
+            reinterpret_cast<uint4*>(smem + s * DT_STAGE_BYTES + DT_KV_BYTES)[i] = make_uint4(0, 0, 0, 0);
+    tc::fence_proxy_async();
+    __syncthreads();
+    ap_pdl_trigger();
+    ap_pdl_wait();
+
+    const int row = blockIdx.x;              // row == sequence index
+    const int reps = p.nh / p.nkv;
+    const int kvh = blockIdx.y / p.n_chunks, chunk = blockIdx.y - kvh * p.n_chunks;
+    const int HC = p.heads_per_chunk;       // <= 16
+    const int head0 = kvh * reps + chunk * HC;
+    const int nheads = min(HC, reps - chunk * HC);
+    const int pos = p.positions[row];
+    const int kmax = pos;
+    const int kmin = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int* table = p.block_table + (size_t)row * p.max_blocks;
+    const int t_first = kmin / BKV, t_last = kmax / BKV;
+    const int ntiles = t_last - t_first + 1;
+    const int per = (ntiles + p.nsplit - 1) / p.nsplit;
+    const int t_lo = t_first + blockIdx.z * per;
+    const int t_hi = min(t_last, t_lo + per - 1);
+    const int n = t_hi - t_lo + 1;            // tiles of this slice (<= 0: none)
+
+    float o[DTILES][4];
+#pragma unroll
+    for (int j = 0; j < DTILES; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    if (warp == 4) {
+        // producer: lane j owns page j of every tile
+        const int pages_per_tile = BKV / p.P;
+        const int page_bytes = p.P * 128;                 // one page, 64 columns of the head
+        auto page_of = [&](int it) {
+            const int lp = (t_lo + it) * pages_per_tile + lane;
+            if (it >= n || lane >= pages_per_tile || lp >= p.max_blocks || lp * p.P > kmax ||
+                lp * p.P + p.P - 1 < kmin)
+                return -1;
+            return table[lp];
+        };
+        int page = page_of(0);
+        for (int it = 0; it < n; ++it) {
+            const int s = it % DT_STAGES;
+            const uint32_t ph = (uint32_t)((it / DT_STAGES) & 1);
+            const int next_page = page_of(it + 1);        // in flight while this tile's loads go out
+            const int valid = __popc(__ballot_sync(0xffffffffu, page >= 0));
+            int fine = 1;
+            if (lane == 0) {
+                if (*abort_flag) fine = 0;
+                if (fine && !tc::mbar_wait(&empty[s], ph ^ 1)) {
+                    *abort_flag = 1;
+                    atomicExch(&g_dt_status, DT_ERR_WAIT);
+                    fine = 0;
+                }
+                if (fine) tc::mbar_expect_tx(&full[s], (uint32_t)(valid * page_bytes * DT_NHALF * 2));
+            }
+            fine = __shfl_sync(0xffffffffu, fine, 0);
+            if (!fine) break;
+            if (page >= 0) {
+                uint8_t* dst = smem + s * DT_STAGE_BYTES + lane * page_bytes;
+                const int krow = ((page * 2 + 0) * p.nkv + kvh) * p.P;
+                const int vrow = ((page * 2 + 1) * p.nkv + kvh) * p.P;
+#pragma unroll
+                for (int h = 0; h < DT_NHALF; ++h) {
+                    tc::tma_load_2d(dst + h * SWZ_HALF_BYTES, &tmap_kv, h * 64, krow, &full[s]);
+                    tc::tma_load_2d(dst + DT_KV_BYTES + h * SWZ_HALF_BYTES, &tmap_kv, h * 64, vrow, &full[s]);
+                }
+            }
+            page = next_page;
+        }
+    } else {
+        int qpos[2] = {pos, pos};
+        bool rvalid[2];
+        const bf16* qptr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = (lane >> 2) + h * 8;
+            rvalid[h] = r < nheads;
+            qptr[h] = rvalid[h] ? p.q + ((size_t)row * p.nh + head0 + r) * HD : nullptr;
+        }
+        uint32_t qf[KSTEPS][4];
+        load_q_frags(qf, qptr[0], qptr[1]);
+        for (int it = 0; it < n; ++it) {
+            const int s = it % DT_STAGES;
+            const uint32_t ph = (uint32_t)((it / DT_STAGES) & 1);
+            // ldmatrix and mma are warp-wide: the whole warp goes on, or none of it
+            if (!__all_sync(0xffffffffu, tc::mbar_wait(&full[s], ph))) {
+                if (!*abort_flag) {
+                    *abort_flag = 1;
+                    atomicExch(&g_dt_status, DT_ERR_WAIT);
+                }
+                break;
+            }
+            const int t = t_lo + it;
+            const uint8_t* ks = smem + s * DT_STAGE_BYTES;
+            if (t * BKV + warp * 16 <= kmax)
+                process_keys<2, true>(ks, ks + DT_KV_BYTES, warp * 16, t * BKV, qf, o, m, l, qpos, rvalid, p.window,
+                                      p.scale_log2);
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&empty[s]);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+            l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+        }
+    }
+    // merge the four consumer warps (each saw a quarter of the keys) through shared memory;
+    // every load has landed (each was waited for), so the stages can be written over
+    __syncthreads();
+    if (*abort_flag) return;
+    float* so = reinterpret_cast<float*>(smem);                 // [4][16][HD]
+    float* sm = so + 4 * 16 * HD;                               // [4][16]
+    float* sl = sm + 4 * 16;                                    // [4][16]
+    if (warp < 4) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = (lane >> 2) + h * 8;
+            float* dst = so + ((size_t)warp * 16 + r) * HD;
+#pragma unroll
+            for (int j = 0; j < DTILES; ++j) {
+                const int d = j * 8 + (lane & 3) * 2;
+                dst[d] = o[j][2 * h];
+                dst[d + 1] = o[j][2 * h + 1];
+            }
+            if ((lane & 3) == 0) {
+                sm[warp * 16 + r] = m[h];
+                sl[warp * 16 + r] = l[h];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nheads * HD; idx += DT_THREADS) {
+        const int r = idx / HD, d = idx - r * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + r]);
+        float L = 0.f, O = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = exp2f(sm[w * 16 + r] - M);
+                L += sl[w * 16 + r] * f;
+                O += so[((size_t)w * 16 + r) * HD + d] * f;
+            }
+        }
+        const float val = L > 0.f ? O / L : 0.f;
+        const size_t orow = (size_t)row * p.nh + head0 + r;
+        if (p.nsplit == 1) {
+            p.out[orow * HD + d] = __float2bfloat16_rn(val);
+        } else {
+            const size_t prow = (size_t)blockIdx.z * p.T * p.nh + orow;
+            p.part_o[prow * HD + d] = val;
+            if (d == 0) {
+                p.part_ml[prow * 2] = M;
+                p.part_ml[prow * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+typedef CUresult (*DtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static DtEncodeFn dt_encode_fn() {
+    static DtEncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (DtEncodeFn)ptr;
+    }
+    return fn;
+}
+
+// 1 when ap_attention_decode_tma takes this shape, else 0 (the caller then uses ap_attention_tc)
+AP_EXPORT int ap_attention_decode_tma_supports(int nh, int nkv, int hd, int P) {
+    if (hd != HD || nkv <= 0 || nh % nkv) return 0;
+    if (P < 8 || P > BKV || BKV % P) return 0;
+    return dt_encode_fn() != nullptr;
+}
+
+// The split kernel with TMA loads: one row per sequence, `nsplit` key slices; part_o/part_ml
+// as for ap_attention_tc (unused for nsplit == 1).  `num_pages`: pages in `cache`, which must
+// be contiguous ([page][2][nkv][P][hd]).  Unwritten slots of the cache must hold finite values.
+AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cache, long long num_pages,
+                                      const int* block_table, int max_blocks, const int* positions, int T,
+                                      int nh, int nkv, int hd, int P, long long page_stride, float scale,
+                                      int window, int nsplit, float* part_o, float* part_ml, cudaStream_t stream) {
+    AP_REQUIRE(ap_attention_decode_tma_supports(nh, nkv, hd, P), "attention (decode, TMA): shape not supported: "
+               "heads=%d kv_heads=%d head_dim=%d page=%d", nh, nkv, hd, P);
+    AP_REQUIRE(page_stride == 2LL * nkv * P * HD, "attention (decode, TMA): pages must be contiguous");
+    AP_REQUIRE(T >= 0 && max_blocks > 0 && num_pages > 0, "attention (decode, TMA): bad sizes");
+    if (T == 0) return AP_OK;
+    AP_REQUIRE(((uintptr_t)cache & 15) == 0, "attention (decode, TMA): the cache must be 16-byte aligned");
+    AP_REQUIRE(nsplit >= 1 && nsplit <= 65535, "attention: bad number of key slices %d", nsplit);
+    AP_REQUIRE(nsplit == 1 || (part_o && part_ml), "attention: key slices need scratch memory");
+    CUtensorMap mkv;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)(num_pages * 2 * nkv * P)};
+        cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)P};
+        cuuint32_t es[2] = {1, 1};
+        AP_REQUIRE(dt_encode_fn()(&mkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides,
+                                  box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
+                   "attention (decode, TMA): cannot encode the cache tensor map");
+    }
+    static bool configured = false;
+    if (!configured) {
+        int rc = configure_smem((const void*)attention_split_tma_kernel, DtSmem::kTotal);
+        if (rc != AP_OK) return rc;
+        configured = true;
+    }
+    AttnTcParams p;
+    p.q = (const bf16*)q; p.out = (bf16*)out; p.cache = (const bf16*)cache;
+    p.block_table = block_table; p.seq_start = nullptr; p.positions = positions;
+    p.part_o = part_o; p.part_ml = part_ml; p.counters = nullptr; p.page_stride = (size_t)page_stride;
+    p.max_blocks = max_blocks; p.nseq = T; p.T = T; p.nh = nh; p.nkv = nkv; p.P = P; p.window = window;
+    p.scale_log2 = scale * LOG2E;
+    const int reps = nh / nkv;
+    p.heads_per_chunk = reps < 16 ? reps : 16;
+    p.n_chunks = (reps + p.heads_per_chunk - 1) / p.heads_per_chunk;
+    p.tokens_per_tile = 1;
+    p.nsplit = nsplit;
+    AP_REQUIRE(nkv * p.n_chunks <= 65535, "attention: too many KV heads for the grid");
+    dim3 grid(T, nkv * p.n_chunks, nsplit);
+    AP_CHECK_PDL_LAUNCH("attention_split_tma", ap_launch_pdl(attention_split_tma_kernel, grid, dim3(DT_THREADS),
+                                                             (size_t)DtSmem::kTotal, stream, mkv, p));
+    if (nsplit > 1) {
+        dim3 mgrid(T, nh);
+        AP_CHECK_PDL_LAUNCH("attention_merge",
+                            ap_launch_pdl(attention_merge_kernel, mgrid, dim3(HD < 128 ? 64 : 128), 0, stream,
+                                          (const float*)part_o, (const float*)part_ml, (bf16*)out, T, nh, nsplit));
+    }
+    return AP_OK;
+}
+
+AP_EXPORT int ap_attention_decode_tma_status(void) {
+    int v = -1;
+    if (cudaMemcpyFromSymbol(&v, g_dt_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+#else
+AP_EXPORT int ap_attention_decode_tma_supports(int, int, int, int) { return 0; }
+#endif
 
 // ---------------------------------------------------------------------------
 // The split kernel for callers that cannot allocate: its scratch is a fixed array in this

@@ -257,7 +257,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: int = 0, seq_start: Optional[torch.Tensor] = None,
               query_lens: Optional[Sequence[int]] = None, max_context: int = 0,
-              scratch=None, zero_scratch=None, use_tcgen05: bool = True) -> None:
+              scratch=None, zero_scratch=None, use_tcgen05: bool = True, use_tma: bool = True) -> None:
     """Causal attention of every row of ``q [T, nh*hd]`` over its sequence's cached keys.
 
     float32 runs the general CUDA-core kernel (the true 32-bit path).  bfloat16 runs on the
@@ -289,8 +289,23 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
         if seq_start.shape[0] != nseq + 1 or sum(query_lens) != T:
             raise KernelError("attention: seq_start/query_lens do not describe the rows")
         if all(n == 1 for n in query_lens):
-            nsplit = decode_splits(T, num_heads, num_kv_heads, max_context, window)
+            tma = (use_tma and hasattr(lib, "ap_attention_decode_tma")
+                   and bool(lib.ap_attention_decode_tma_supports(num_heads, num_kv_heads, head_dim, P))
+                   and cache_layer.stride(0) == 2 * num_kv_heads * P * head_dim)
+            nsplit = decode_splits(T, num_heads, num_kv_heads, max_context, window, slots=296 if tma else 444)
             po = pm = pc = 0
+            if tma:
+                # the split kernel fed by TMA: a ring of tiles in flight, two CTAs per SM
+                if nsplit > 1:
+                    if scratch is None:
+                        raise KernelError("attention: key slices need a scratch provider")
+                    po = scratch("attn.part_o", (nsplit, T, num_heads, head_dim), torch.float32).data_ptr()
+                    pm = scratch("attn.part_ml", (nsplit, T, num_heads, 2), torch.float32).data_ptr()
+                call(lib, "ap_attention_decode_tma", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
+                     cache_layer.shape[0], block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), T,
+                     num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0), float(scale), int(window or 0),
+                     nsplit, po, pm, stream_handle())
+                return
             if nsplit > 1:
                 if scratch is None:
                     raise KernelError("attention: key slices need a scratch provider")
@@ -328,10 +343,11 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
          float(scale), int(window or 0), stream_handle())
 
 
-def decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: int, window: int = 0) -> int:
+def decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: int, window: int = 0,
+                  slots: int = 444) -> int:
     """Key slices for the split kernel.
 
-    The kernel runs three CTAs per SM (444 at a time); a slice walks ``tiles / slices`` 64-key
+    The kernel runs three CTAs per SM (444 at a time; two, 296, when fed by TMA); a slice walks ``tiles / slices`` 64-key
     tiles plus a fixed set-up and merge worth about four tiles, and every slice adds a little
     to the combining pass.  The count that makes ``waves * (tiles per slice + 4) + 0.15 *
     slices`` smallest is taken (measured on B200: 7 for 8 rows, 16 for one row at 4096 keys).
@@ -343,7 +359,7 @@ def decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: int
     tiles = max(1, -(-max(keys, 1) // 64))
     best, best_cost = 1, None
     for ns in range(1, min(64, tiles) + 1):
-        waves = max(1, -(-int(ctas * ns / 1.02) // 444))
+        waves = max(1, -(-int(ctas * ns / 1.02) // slots))
         cost = waves * (-(-tiles // ns) + 4) + 0.15 * ns
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = ns, cost
@@ -407,6 +423,9 @@ def check_kernel_status() -> None:
         if hasattr(lib, "ap_attention_tcgen05_status") and int(lib.ap_attention_tcgen05_status()) != 0:
             raise KernelError(f"the tcgen05 attention kernel (head size {hd}) gave up waiting on its pipeline; "
                               f"its results are void")
+        if hasattr(lib, "ap_attention_decode_tma_status") and int(lib.ap_attention_decode_tma_status()) != 0:
+            raise KernelError(f"the TMA-fed decode attention kernel (head size {hd}) gave up waiting on its "
+                              f"pipeline; its results are void")
     code = gemm_tc_status()
     if code != 0:
         raise KernelError(f"the tensor-core matrix product gave up waiting (code {code}: "

@@ -114,6 +114,11 @@ _OPTIONAL_ATTN_SIGNATURES: Dict[str, list] = {
     "ap_attention_tcgen05_supports": [_I, _I, _I, _I],
     "ap_attention_tcgen05_tokens_per_tile": [_I, _I],
     "ap_attention_tcgen05_status": [],
+    # int ap_attention_decode_tma(q, out, cache, num_pages, block_table, max_blocks, positions, T, nh, nkv, hd, P,
+    #                             page_stride, scale, window, nsplit, part_o, part_ml, stream)
+    "ap_attention_decode_tma": [_P, _P, _P, _L, _P, _I, _P, _I, _I, _I, _I, _I, _L, _F, _I, _I, _P, _P, _P],
+    "ap_attention_decode_tma_supports": [_I, _I, _I, _I],
+    "ap_attention_decode_tma_status": [],
 }
 
 
