@@ -128,7 +128,8 @@ def bench_attention(args) -> dict:
                       zero_scratch=zero_scratch if args.fused_merge else None, use_tma=not args.cp_async)
     us = _time(fn, args.iters, args.warmup, not args.no_graph)
     return {"kernel": "attention_split+merge" if args.cp_async else "attention_split_tma+merge", "batch": B, "context": C, "heads": nh, "kv_heads": nkv,
-            "head_dim": hd, "splits": ops.decode_splits(B, nh, nkv, C, slots=444 if args.cp_async else 296),
+            "head_dim": hd, "splits": ops.decode_splits(B, nh, nkv, C, slots=444 if args.cp_async else 296,
+                                        cluster_sizes=() if args.cp_async else (2, 4, 8)),
             "us": round(us, 2),
             "GBps": round(per / us / 1e3, 1)}
 

@@ -618,8 +618,13 @@ AP_EXPORT int ap_attention_tc_tokens_per_tile(int nh, int nkv) {
 // table one tile ahead) keeps a ring of three 64-key tiles of K and V loading by
 // cp.async.bulk.tensor (128-byte swizzle), with no address arithmetic in the consumer warps
 // and no round trip to the block table inside the loop.  The four consumer warps take 16 keys
-// of every tile each, as in attention_split_kernel, and the slices are combined the same way.
-// Every barrier wait is bounded; on expiry a status word is raised and the CTA leaves.
+// of every tile each, as in attention_split_kernel.  CLUSTER: the key slices of one row and KV
+// head form a thread-block cluster (2, 4 or 8 CTAs) and hand their results to its first CTA
+// through distributed shared memory, which combines them and writes the row: no partial
+// results in global memory and no second kernel.  Otherwise the slices are combined as for
+// attention_split_kernel.
+// Every barrier wait is bounded; on expiry a status word is raised and the CTA does no more
+// (in a cluster it still walks to the cluster barriers, or its peers would wait).
 // ---------------------------------------------------------------------------
 #if (AP_HEAD_DIM == 64 || AP_HEAD_DIM == 128)
 #include "tcgen05.cuh"
@@ -639,8 +644,15 @@ struct DtSmem {
     static constexpr int kUsed = kBars + 128;
     static constexpr int kMerge = (4 * 16 * HD + 2 * 4 * 16) * (int)sizeof(float);
     static constexpr int kTotal = (kUsed > kMerge ? kUsed : kMerge) + 1024;   // + alignment slack
+    // cluster: the slices' results [slice][head][HD + 2] in the first CTA, behind its own merge
+    // buffers and before the barriers
+    static constexpr int kXchRow = HD + 2;
+    static __host__ __device__ constexpr bool exchange_fits(int nsplit, int heads) {
+        return kMerge + nsplit * heads * kXchRow * (int)sizeof(float) <= kBars;
+    }
 };
 
+template <bool CLUSTER>
 __global__ void __launch_bounds__(DT_THREADS)
 attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -648,7 +660,8 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const At
     uint64_t* full = (uint64_t*)(smem + DtSmem::kBars);
     uint64_t* empty = full + DT_STAGES;
     volatile int* abort_flag = (volatile int*)(empty + DT_STAGES);
-    if (*(volatile int*)&g_dt_status != 0) return;
+    const bool skip = *(volatile int*)&g_dt_status != 0;
+    if (!CLUSTER && skip) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < DT_STAGES; ++s) {
@@ -684,7 +697,7 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const At
     const int per = (ntiles + p.nsplit - 1) / p.nsplit;
     const int t_lo = t_first + blockIdx.z * per;
     const int t_hi = min(t_last, t_lo + per - 1);
-    const int n = t_hi - t_lo + 1;            // tiles of this slice (<= 0: none)
+    const int n = skip ? 0 : t_hi - t_lo + 1; // tiles of this slice (<= 0: none)
 
     float o[DTILES][4];
 #pragma unroll
@@ -771,12 +784,15 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const At
     }
     // merge the four consumer warps (each saw a quarter of the keys) through shared memory;
     // every load has landed (each was waited for), so the stages can be written over
+    if (CLUSTER) tc::cluster_arrive();        // nothing is loaded into this CTA's shared memory any more
     __syncthreads();
-    if (*abort_flag) return;
+    const bool dead = skip || *abort_flag != 0;
+    if (!CLUSTER && dead) return;
     float* so = reinterpret_cast<float*>(smem);                 // [4][16][HD]
     float* sm = so + 4 * 16 * HD;                               // [4][16]
     float* sl = sm + 4 * 16;                                    // [4][16]
-    if (warp < 4) {
+    float* xch = reinterpret_cast<float*>(smem + DtSmem::kMerge);   // cluster: [slice][head][HD + 2]
+    if (warp < 4 && !dead) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = (lane >> 2) + h * 8;
@@ -794,7 +810,12 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const At
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < nheads * HD; idx += DT_THREADS) {
+    uint32_t xch0 = 0;
+    if (CLUSTER) {
+        tc::cluster_wait();                   // ... nor into any other CTA's of the cluster
+        xch0 = tc::map_to_rank(tc::smem_addr(xch), 0u);
+    }
+    for (int idx = threadIdx.x; idx < nheads * HD && !dead; idx += DT_THREADS) {
         const int r = idx / HD, d = idx - r * HD;
         float M = -INFINITY;
 #pragma unroll
@@ -810,7 +831,14 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const At
         }
         const float val = L > 0.f ? O / L : 0.f;
         const size_t orow = (size_t)row * p.nh + head0 + r;
-        if (p.nsplit == 1) {
+        if (CLUSTER) {
+            const uint32_t at = xch0 + (uint32_t)((blockIdx.z * HC + r) * DtSmem::kXchRow) * 4u;
+            tc::st_cluster_f32(at + (uint32_t)d * 4u, val);
+            if (d == 0) {
+                tc::st_cluster_f32(at + (uint32_t)HD * 4u, M);
+                tc::st_cluster_f32(at + (uint32_t)(HD + 1) * 4u, L);
+            }
+        } else if (p.nsplit == 1) {
             p.out[orow * HD + d] = __float2bfloat16_rn(val);
         } else {
             const size_t prow = (size_t)blockIdx.z * p.T * p.nh + orow;
@@ -819,6 +847,27 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const At
                 p.part_ml[prow * 2] = M;
                 p.part_ml[prow * 2 + 1] = L;
             }
+        }
+    }
+    if (CLUSTER) {
+        tc::cluster_sync();                   // every slice has delivered
+        if (blockIdx.z != 0 || dead) return;
+        for (int idx = threadIdx.x; idx < nheads * HD; idx += DT_THREADS) {
+            const int r = idx / HD, d = idx - r * HD;
+            float M = -INFINITY;
+            for (int z = 0; z < p.nsplit; ++z) M = fmaxf(M, xch[(z * HC + r) * DtSmem::kXchRow + HD]);
+            float L = 0.f, O = 0.f;
+            if (M != -INFINITY) {
+                for (int z = 0; z < p.nsplit; ++z) {                      // slices in order
+                    const float* rowz = xch + (z * HC + r) * DtSmem::kXchRow;
+                    const float lz = rowz[HD + 1];
+                    if (lz <= 0.f) continue;
+                    const float f = lz * exp2f(rowz[HD] - M);
+                    L += f;
+                    O += rowz[d] * f;
+                }
+            }
+            p.out[((size_t)row * p.nh + head0 + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
         }
     }
 }
@@ -846,8 +895,16 @@ AP_EXPORT int ap_attention_decode_tma_supports(int nh, int nkv, int hd, int P) {
     return dt_encode_fn() != nullptr;
 }
 
+// 1 when `nsplit` key slices are combined inside a thread-block cluster (no scratch needed)
+AP_EXPORT int ap_attention_decode_tma_in_cluster(int nh, int nkv, int nsplit) {
+    if (nkv <= 0 || nh % nkv) return 0;
+    const int reps = nh / nkv;
+    const int hc = reps < 16 ? reps : 16;
+    return (nsplit == 2 || nsplit == 4 || nsplit == 8) && DtSmem::exchange_fits(nsplit, hc);
+}
+
 // The split kernel with TMA loads: one row per sequence, `nsplit` key slices; part_o/part_ml
-// as for ap_attention_tc (unused for nsplit == 1).  `num_pages`: pages in `cache`, which must
+// as for ap_attention_tc (unused for nsplit == 1 and where the slices form a cluster).  `num_pages`: pages in `cache`, which must
 // be contiguous ([page][2][nkv][P][hd]).  Unwritten slots of the cache must hold finite values.
 AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cache, long long num_pages,
                                       const int* block_table, int max_blocks, const int* positions, int T,
@@ -860,7 +917,8 @@ AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cach
     if (T == 0) return AP_OK;
     AP_REQUIRE(((uintptr_t)cache & 15) == 0, "attention (decode, TMA): the cache must be 16-byte aligned");
     AP_REQUIRE(nsplit >= 1 && nsplit <= 65535, "attention: bad number of key slices %d", nsplit);
-    AP_REQUIRE(nsplit == 1 || (part_o && part_ml), "attention: key slices need scratch memory");
+    const bool cluster = ap_attention_decode_tma_in_cluster(nh, nkv, nsplit) != 0;
+    AP_REQUIRE(nsplit == 1 || cluster || (part_o && part_ml), "attention: key slices need scratch memory");
     CUtensorMap mkv;
     {
         cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)(num_pages * 2 * nkv * P)};
@@ -874,7 +932,9 @@ AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cach
     }
     static bool configured = false;
     if (!configured) {
-        int rc = configure_smem((const void*)attention_split_tma_kernel, DtSmem::kTotal);
+        int rc = configure_smem((const void*)attention_split_tma_kernel<false>, DtSmem::kTotal);
+        if (rc != AP_OK) return rc;
+        rc = configure_smem((const void*)attention_split_tma_kernel<true>, DtSmem::kTotal);
         if (rc != AP_OK) return rc;
         configured = true;
     }
@@ -891,7 +951,25 @@ AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cach
     p.nsplit = nsplit;
     AP_REQUIRE(nkv * p.n_chunks <= 65535, "attention: too many KV heads for the grid");
     dim3 grid(T, nkv * p.n_chunks, nsplit);
-    AP_CHECK_PDL_LAUNCH("attention_split_tma", ap_launch_pdl(attention_split_tma_kernel, grid, dim3(DT_THREADS),
+    if (cluster) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(DT_THREADS);
+        cfg.dynamicSmemBytes = DtSmem::kTotal;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = nsplit;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = ap_pdl_enabled() ? 2 : 1;
+        AP_CHECK_PDL_LAUNCH("attention_split_tma", cudaLaunchKernelEx(&cfg, attention_split_tma_kernel<true>, mkv, p));
+        return AP_OK;
+    }
+    AP_CHECK_PDL_LAUNCH("attention_split_tma", ap_launch_pdl(attention_split_tma_kernel<false>, grid, dim3(DT_THREADS),
                                                              (size_t)DtSmem::kTotal, stream, mkv, p));
     if (nsplit > 1) {
         dim3 mgrid(T, nh);
@@ -909,6 +987,7 @@ AP_EXPORT int ap_attention_decode_tma_status(void) {
 }
 #else
 AP_EXPORT int ap_attention_decode_tma_supports(int, int, int, int) { return 0; }
+AP_EXPORT int ap_attention_decode_tma_in_cluster(int, int, int) { return 0; }
 #endif
 
 // ---------------------------------------------------------------------------

@@ -292,11 +292,13 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
             tma = (use_tma and hasattr(lib, "ap_attention_decode_tma")
                    and bool(lib.ap_attention_decode_tma_supports(num_heads, num_kv_heads, head_dim, P))
                    and cache_layer.stride(0) == 2 * num_kv_heads * P * head_dim)
-            nsplit = decode_splits(T, num_heads, num_kv_heads, max_context, window, slots=296 if tma else 444)
+            nsplit = decode_splits(T, num_heads, num_kv_heads, max_context, window, slots=296 if tma else 444,
+                                   cluster_sizes=(2, 4, 8) if tma else ())
             po = pm = pc = 0
             if tma:
-                # the split kernel fed by TMA: a ring of tiles in flight, two CTAs per SM
-                if nsplit > 1:
+                # the split kernel fed by TMA: a ring of tiles in flight, two CTAs per SM; 2, 4 or 8
+                # slices are combined inside a thread-block cluster and need no scratch
+                if nsplit > 1 and not lib.ap_attention_decode_tma_in_cluster(num_heads, num_kv_heads, nsplit):
                     if scratch is None:
                         raise KernelError("attention: key slices need a scratch provider")
                     po = scratch("attn.part_o", (nsplit, T, num_heads, head_dim), torch.float32).data_ptr()
@@ -344,13 +346,15 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
 
 
 def decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: int, window: int = 0,
-                  slots: int = 444) -> int:
-    """Key slices for the split kernel.
+                  slots: int = 444, cluster_sizes: Sequence[int] = ()) -> int:
+    """Key slices for the split kernels.
 
-    The kernel runs three CTAs per SM (444 at a time; two, 296, when fed by TMA); a slice walks ``tiles / slices`` 64-key
-    tiles plus a fixed set-up and merge worth about four tiles, and every slice adds a little
-    to the combining pass.  The count that makes ``waves * (tiles per slice + 4) + 0.15 *
-    slices`` smallest is taken (measured on B200: 7 for 8 rows, 16 for one row at 4096 keys).
+    The cp.async kernel runs three CTAs per SM (``slots`` 444), the one fed by TMA two (296).
+    A slice walks ``tiles / slices`` 64-key tiles plus a fixed set-up and merge worth about
+    four tiles, and every slice adds a little to the combining pass.  Slice counts in
+    ``cluster_sizes`` are combined inside the kernel; the others pay for a second kernel and a
+    round trip of the partial results, counted as ten tiles.  The count with the smallest
+    ``waves * (tiles per slice + 4) + 0.15 * slices (+ 10)`` is taken.
     """
     reps = num_heads // num_kv_heads
     chunks = -(-reps // min(reps, 16))
@@ -361,6 +365,8 @@ def decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: int
     for ns in range(1, min(64, tiles) + 1):
         waves = max(1, -(-int(ctas * ns / 1.02) // slots))
         cost = waves * (-(-tiles // ns) + 4) + 0.15 * ns
+        if cluster_sizes and ns > 1 and ns not in cluster_sizes:
+            cost += 10
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = ns, cost
     return best

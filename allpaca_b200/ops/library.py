@@ -118,6 +118,7 @@ _OPTIONAL_ATTN_SIGNATURES: Dict[str, list] = {
     #                             page_stride, scale, window, nsplit, part_o, part_ml, stream)
     "ap_attention_decode_tma": [_P, _P, _P, _L, _P, _I, _P, _I, _I, _I, _I, _I, _L, _F, _I, _I, _P, _P, _P],
     "ap_attention_decode_tma_supports": [_I, _I, _I, _I],
+    "ap_attention_decode_tma_in_cluster": [_I, _I, _I],
     "ap_attention_decode_tma_status": [],
 }
 
