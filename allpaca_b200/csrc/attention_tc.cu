@@ -680,7 +680,11 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const At
     tc::fence_proxy_async();
     __syncthreads();
     ap_pdl_trigger();
-    ap_pdl_wait();
+    // The step's positions and block tables were uploaded before any kernel of the step ran,
+    // and of the cache only the newest key of each row is written by the kernel before this
+    // one: the producer starts loading older keys at once and waits for the kernels before
+    // this one only where it comes to the tile that holds the newest key; the consumers wait
+    // before they read the queries.
 
     const int row = blockIdx.x;              // row == sequence index
     const int reps = p.nh / p.nkv;
@@ -716,9 +720,17 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const At
             return table[lp];
         };
         int page = page_of(0);
+        // tiles that may be loaded before the kernels ahead of this one are done: the first ring
+        // fill, short of the tile with the newest key
+        const int early = min(min(n, DT_STAGES), t_last - t_lo);
+        bool waited = false;
         for (int it = 0; it < n; ++it) {
             const int s = it % DT_STAGES;
             const uint32_t ph = (uint32_t)((it / DT_STAGES) & 1);
+            if (!waited && it >= early) {
+                ap_pdl_wait();
+                waited = true;
+            }
             const int next_page = page_of(it + 1);        // in flight while this tile's loads go out
             const int valid = __popc(__ballot_sync(0xffffffffu, page >= 0));
             int fine = 1;
@@ -745,7 +757,9 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const At
             }
             page = next_page;
         }
+        if (!waited) ap_pdl_wait();
     } else {
+        ap_pdl_wait();
         int qpos[2] = {pos, pos};
         bool rvalid[2];
         const bf16* qptr[2];

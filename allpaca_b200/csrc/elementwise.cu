@@ -32,14 +32,16 @@ AP_EXPORT int ap_embed_gather(const int* tokens, const void* table, int table_dt
     AP_REQUIRE(T >= 0 && H > 0 && V > 0, "embed_gather: bad sizes T=%d H=%d V=%d", T, H, V);
     if (T == 0) return AP_OK;
     const int threads = H >= 1024 ? 256 : 128;
+    // The first kernel of a step is launched in plain stream order: it starts when everything
+    // before it on the stream has finished.  Kernels later in the step may therefore read what
+    // earlier steps wrote (the cache) ahead of their own dependency wait.
     if (table_dtype == AP_F32)
-        AP_CHECK_PDL_LAUNCH("embed_gather", ap_launch_pdl(embed_gather_kernel<float>, dim3(T), dim3(threads), 0,
-                                                          stream, tokens, (const float*)table, x, H, V));
+        embed_gather_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, x, H, V);
     else if (table_dtype == AP_BF16)
-        AP_CHECK_PDL_LAUNCH("embed_gather", ap_launch_pdl(embed_gather_kernel<bf16>, dim3(T), dim3(threads), 0,
-                                                          stream, tokens, (const bf16*)table, x, H, V));
+        embed_gather_kernel<bf16><<<T, threads, 0, stream>>>(tokens, (const bf16*)table, x, H, V);
     else
         AP_REQUIRE(false, "embed_gather: unknown table dtype %d", table_dtype);
+    AP_CHECK_LAUNCH("embed_gather");
     return AP_OK;
 }
 
