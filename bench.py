@@ -276,7 +276,7 @@ def main() -> int:
     step_bytes = 2.0 * linear_elems + args.batch * ctx_mid * kv_per_token
     achieved = step_bytes / (ms / 1e3) / 1e9
     result = {
-        "metric": "decode tok/s (8B shape, bf16)", "value": round(value, 2), "unit": "tok/s",
+        "metric": f"decode tok/s ({'8B shape' if args.preset == 'llama-3.1-8b' else args.preset}, bf16)", "value": round(value, 2), "unit": "tok/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "impl": "ours",
