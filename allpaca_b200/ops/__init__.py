@@ -252,6 +252,66 @@ def gemm_tc_persistent(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pair
          M, N, K, K, K, n_out, 1 if pairs else 0, stream_handle())
 
 
+def _decode_attention(lib, q, out, cache_layer, block_table, positions, rows, num_heads, num_kv_heads, head_dim, P,
+                      scale, window, max_context, scratch, zero_scratch, use_tma) -> None:
+    """The first ``rows`` rows of the batch, one per sequence: the split kernels."""
+    tma = (use_tma and hasattr(lib, "ap_attention_decode_tma")
+           and bool(lib.ap_attention_decode_tma_supports(num_heads, num_kv_heads, head_dim, P))
+           and cache_layer.stride(0) == 2 * num_kv_heads * P * head_dim)
+    nsplit = decode_splits(rows, num_heads, num_kv_heads, max_context, window, slots=296 if tma else 444,
+                           cluster_sizes=(2, 4, 8) if tma else ())
+    po = pm = pc = 0
+    needs_scratch = nsplit > 1 and not (tma and lib.ap_attention_decode_tma_in_cluster(num_heads, num_kv_heads, nsplit))
+    if needs_scratch:
+        if scratch is None:
+            raise KernelError("attention: key slices need a scratch provider")
+        po = scratch("attn.part_o", (nsplit, rows, num_heads, head_dim), torch.float32).data_ptr()
+        pm = scratch("attn.part_ml", (nsplit, rows, num_heads, 2), torch.float32).data_ptr()
+    if tma:
+        # fed by TMA: a ring of tiles in flight, two CTAs per SM; 2, 4 or 8 slices are combined
+        # inside a thread-block cluster and need no scratch
+        call(lib, "ap_attention_decode_tma", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
+             cache_layer.shape[0], block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), rows,
+             num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0), float(scale), int(window or 0),
+             nsplit, po, pm, stream_handle())
+        return
+    if needs_scratch and zero_scratch is not None:
+        # arrival counters of the slices: zero now, and left zero by every launch
+        reps = num_heads // num_kv_heads
+        chunks = -(-reps // min(reps, 16))
+        pc = zero_scratch("attn.counters", (rows * num_kv_heads * chunks,), torch.int32).data_ptr()
+    call(lib, "ap_attention_tc", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
+         block_table.data_ptr(), block_table.shape[1], 0, positions.data_ptr(),
+         rows, rows, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0), float(scale),
+         int(window or 0), 1, 0, nsplit, po, pm, pc, stream_handle())
+
+
+def _prompt_attention(lib, q, out, cache_layer, block_table, seq_start, positions, first_seq, query_lens, T,
+                      num_heads, num_kv_heads, head_dim, P, scale, window, use_tcgen05) -> None:
+    """The sequences from ``first_seq`` on (their rows follow those of the sequences before):
+    the tcgen05 kernel for 64 rows or more of a shape it takes, else the mma.sync tile kernel.
+    Rows are addressed through ``seq_start``, so only it and the block table are offset."""
+    nseq = len(query_lens)
+    table_ptr = block_table.data_ptr() + first_seq * block_table.shape[1] * 4
+    start_ptr = seq_start.data_ptr() + first_seq * 4
+    if (use_tcgen05 and sum(query_lens) >= 64 and hasattr(lib, "ap_attention_tcgen05")
+            and lib.ap_attention_tcgen05_supports(num_heads, num_kv_heads, head_dim, P)
+            and cache_layer.stride(0) == 2 * num_kv_heads * P * head_dim):
+        tpt = int(lib.ap_attention_tcgen05_tokens_per_tile(num_heads, num_kv_heads))
+        tiles = sum(-(-n // tpt) for n in query_lens)
+        call(lib, "ap_attention_tcgen05", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
+             cache_layer.shape[0], table_ptr, block_table.shape[1], start_ptr,
+             positions.data_ptr(), nseq, T, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0),
+             float(scale), int(window or 0), tiles, stream_handle())
+        return
+    tpt = int(lib.ap_attention_tc_tokens_per_tile(num_heads, num_kv_heads))
+    tiles = sum(-(-n // tpt) for n in query_lens)
+    call(lib, "ap_attention_tc", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
+         table_ptr, block_table.shape[1], start_ptr, positions.data_ptr(),
+         nseq, T, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0), float(scale),
+         int(window or 0), 0, tiles, 1, 0, 0, 0, stream_handle())
+
+
 def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
               block_table: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
@@ -288,56 +348,19 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
         nseq = len(query_lens)
         if seq_start.shape[0] != nseq + 1 or sum(query_lens) != T:
             raise KernelError("attention: seq_start/query_lens do not describe the rows")
-        if all(n == 1 for n in query_lens):
-            tma = (use_tma and hasattr(lib, "ap_attention_decode_tma")
-                   and bool(lib.ap_attention_decode_tma_supports(num_heads, num_kv_heads, head_dim, P))
-                   and cache_layer.stride(0) == 2 * num_kv_heads * P * head_dim)
-            nsplit = decode_splits(T, num_heads, num_kv_heads, max_context, window, slots=296 if tma else 444,
-                                   cluster_sizes=(2, 4, 8) if tma else ())
-            po = pm = pc = 0
-            if tma:
-                # the split kernel fed by TMA: a ring of tiles in flight, two CTAs per SM; 2, 4 or 8
-                # slices are combined inside a thread-block cluster and need no scratch
-                if nsplit > 1 and not lib.ap_attention_decode_tma_in_cluster(num_heads, num_kv_heads, nsplit):
-                    if scratch is None:
-                        raise KernelError("attention: key slices need a scratch provider")
-                    po = scratch("attn.part_o", (nsplit, T, num_heads, head_dim), torch.float32).data_ptr()
-                    pm = scratch("attn.part_ml", (nsplit, T, num_heads, 2), torch.float32).data_ptr()
-                call(lib, "ap_attention_decode_tma", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
-                     cache_layer.shape[0], block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), T,
-                     num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0), float(scale), int(window or 0),
-                     nsplit, po, pm, stream_handle())
-                return
-            if nsplit > 1:
-                if scratch is None:
-                    raise KernelError("attention: key slices need a scratch provider")
-                po = scratch("attn.part_o", (nsplit, T, num_heads, head_dim), torch.float32).data_ptr()
-                pm = scratch("attn.part_ml", (nsplit, T, num_heads, 2), torch.float32).data_ptr()
-                if zero_scratch is not None:
-                    # arrival counters of the slices: zero now, and left zero by every launch
-                    reps = num_heads // num_kv_heads
-                    chunks = -(-reps // min(reps, 16))
-                    pc = zero_scratch("attn.counters", (T * num_kv_heads * chunks,), torch.int32).data_ptr()
-            mode, tiles = 1, 0
-        else:
-            if (use_tcgen05 and T >= 64 and hasattr(lib, "ap_attention_tcgen05")
-                    and lib.ap_attention_tcgen05_supports(num_heads, num_kv_heads, head_dim, P)
-                    and cache_layer.stride(0) == 2 * num_kv_heads * P * head_dim):
-                # prompt portions on the tcgen05 tensor cores
-                tpt = int(lib.ap_attention_tcgen05_tokens_per_tile(num_heads, num_kv_heads))
-                tiles = sum(-(-n // tpt) for n in query_lens)
-                call(lib, "ap_attention_tcgen05", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
-                     cache_layer.shape[0], block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(),
-                     positions.data_ptr(), nseq, T, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0),
-                     float(scale), int(window or 0), tiles, stream_handle())
-                return
-            tpt = int(lib.ap_attention_tc_tokens_per_tile(num_heads, num_kv_heads))
-            tiles = sum(-(-n // tpt) for n in query_lens)
-            mode, nsplit, po, pm, pc = 0, 1, 0, 0, 0
-        call(lib, "ap_attention_tc", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
-             block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(), positions.data_ptr(),
-             nseq, T, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0), float(scale),
-             int(window or 0), mode, tiles, nsplit, po, pm, pc, stream_handle())
+        # Sequences that bring one row each (decoding) go to the split kernel, prompt portions to
+        # the tile kernels.  A mixed batch whose one-row sequences come first (the scheduler's
+        # order) is two launches over disjoint rows; one-row sequences further back ride along
+        # with the portions.
+        nd = 0
+        while nd < nseq and query_lens[nd] == 1:
+            nd += 1
+        if nd > 0:
+            _decode_attention(lib, q, out, cache_layer, block_table, positions, nd, num_heads, num_kv_heads,
+                              head_dim, P, scale, window, max_context, scratch, zero_scratch, use_tma)
+        if nd < nseq:
+            _prompt_attention(lib, q, out, cache_layer, block_table, seq_start, positions, nd, query_lens[nd:], T,
+                              num_heads, num_kv_heads, head_dim, P, scale, window, use_tcgen05)
         return
     call(lib, "ap_attention_rows", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
          dtype_code(q.dtype), block_table.data_ptr(), block_table.shape[1], token_seq.data_ptr(),

@@ -117,3 +117,19 @@ def test_scores_that_rise_or_fall_along_the_sequence(ops, rising):
     ops.check_kernel_status()
     ref = reference_attention(case, seqs, nh, hd, None, scale=1.0)
     assert rel_err(got, ref) < 1.5e-2
+
+
+@pytest.mark.parametrize("nh,nkv,hd,P", [(32, 8, 128, 16), (16, 2, 64, 32)])
+def test_decoding_sequences_beside_prompt_portions(ops, nh, nkv, hd, P):
+    """A mixed batch in the scheduler's order, one-row sequences first: they run on the split
+    kernel, the portions on the tcgen05 kernel, over disjoint rows of the same tensors."""
+    seqs = [(900, 1), (17, 1), (2048, 1), (1, 1), (640, 1), (700, 512), (300, 300), (129, 1)]
+    case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=21)
+    scale = 1.0 / math.sqrt(hd)
+    got = run_attention(ops, case, nh, nkv, hd, scale, 0, tensor_cores=True)
+    ops.check_kernel_status()
+    ref = reference_attention(case, seqs, nh, hd, None, scale=scale)
+    assert rel_err(got, ref) < 1.5e-2
+    # row by row: a row the wrong kernel wrote, or none wrote, shows here
+    per_row = (got.double() - ref).abs().amax(dim=1) / ref.abs().max()
+    assert float(per_row.max()) < 1.5e-2

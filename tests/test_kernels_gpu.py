@@ -358,6 +358,7 @@ ATT_SHAPES = [  # heads, kv heads, head size, page size
     (4, 2, 16, 16), (3, 1, 32, 8), (6, 3, 48, 4), (8, 8, 64, 16), (8, 2, 128, 16), (5, 1, 80, 32),
     (20, 1, 16, 16)]
 MIXED = [(700, 1), (129, 129), (64, 2), (333, 40), (1, 1), (65, 65), (200, 1)]
+DECODE_FIRST = [(700, 1), (300, 1), (1, 1), (1500, 1), (129, 129), (64, 2), (333, 40), (77, 1), (65, 65)]
 DECODE = [(700, 1), (129, 1), (64, 1), (1, 1), (65, 1), (1500, 1)]
 
 
@@ -374,9 +375,9 @@ def test_attention_float32(ops, nh, nkv, hd, P, window):
 
 @pytest.mark.parametrize("nh,nkv,hd,P", ATT_SHAPES)
 @pytest.mark.parametrize("window", [0, 37, 200])
-@pytest.mark.parametrize("mode", ["mixed", "decode", "rows"])
+@pytest.mark.parametrize("mode", ["mixed", "decode_first", "decode", "rows"])
 def test_attention_bfloat16(ops, nh, nkv, hd, P, window, mode):
-    seqs = DECODE if mode == "decode" else MIXED
+    seqs = DECODE if mode == "decode" else DECODE_FIRST if mode == "decode_first" else MIXED
     case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=hd + P + 1)
     scale = 0.7 / math.sqrt(hd)
     got = run_attention(ops, case, nh, nkv, hd, scale, window, tensor_cores=(mode != "rows"))
