@@ -118,14 +118,12 @@ def cmd_generate(args) -> int:
         model_path = tmp.name
     if not model_path:
         raise SystemExit("allpaca generate: give --model DIR or --synthetic [PRESET]")
-    longest = max(len(p) for p in prompts) + params.max_tokens
     llm = LLM(model=model_path, dtype=args.dtype or "bfloat16", seed=seed,
               page_size=pick(args.page_tokens, sec("kv").get("page_tokens", 16)),
               prefill_chunk=pick(args.chunk_tokens, sec("prefill").get("chunk_tokens", 512)),
               max_num_seqs=pick(args.max_active_requests, sec("engine").get("max_active_requests", 64)),
               max_cache_tokens=pick(args.max_cache_tokens, None),
               device=str(sec("engine").get("target_device", "cuda:0")).replace("auto", "cuda:0"))
-    del longest
     for out in llm.generate(prompts, params):
         if args.json:
             print(json.dumps({"token_ids": out.token_ids, "prompt_tokens": out.prompt_tokens,
