@@ -138,9 +138,7 @@ class DecoderModel:
         R = step.num_logit_rows
         logits = ws.get("model.logits", (R, s.vocab_size), torch.float32)
         if R == 0:
-            if delta is not None:
-                ops.residual_add(x, delta)   # keeps x complete; nothing else to do
-            return logits
+            return logits            # a portion nobody wants logits of: the cache is written, that is all
         h = ws.get("model.final_normed", (R, s.hidden_size), self.env.dtype)
         self.final_norm.forward(x, h, delta=delta, rows=step.logit_rows)
         out = self.head.forward(h, "model.logits", "float32")
