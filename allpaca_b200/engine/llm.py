@@ -95,7 +95,7 @@ class LLM:
         entries = []
         sampling = []
         for r in out.rows:
-            toks = r.request.all_token_ids[r.start:r.start + r.count]
+            toks = r.request.token_slice(r.start, r.count)
             entries.append(BatchEntry(r.request.request_id, toks, [r.count - 1] if r.samples else []))
             if r.samples:
                 sampling.append(r.request)

@@ -64,6 +64,17 @@ class Request:
     def all_token_ids(self) -> List[int]:
         return self.prompt_token_ids + self.output_token_ids
 
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """``all_token_ids[start:start + count]`` without joining the two lists (a decode step
+        asks for one token of a sequence that may be very long)."""
+        n = len(self.prompt_token_ids)
+        end = start + count
+        if end <= n:
+            return self.prompt_token_ids[start:end]
+        if start >= n:
+            return self.output_token_ids[start - n:end - n]
+        return self.prompt_token_ids[start:] + self.output_token_ids[:end - n]
+
     @property
     def num_tokens(self) -> int:
         return len(self.prompt_token_ids) + len(self.output_token_ids)

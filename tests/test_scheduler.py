@@ -183,3 +183,13 @@ def test_abort_removes_a_request():
     cache.free("a")
     assert r.request_id == "a" and [x.request_id for x in s.running] == ["b"]
     assert s.abort("zzz") is None
+
+
+def test_token_slice_equals_slicing_the_joined_list():
+    from allpaca_b200.engine.scheduler import Request
+    from allpaca_b200.sampling.params import SamplingParams
+    req = Request("r", [1, 2, 3, 4, 5], SamplingParams())
+    req.output_token_ids = [6, 7, 8]
+    for start in range(0, 9):
+        for count in range(0, 9 - start):
+            assert req.token_slice(start, count) == req.all_token_ids[start:start + count]
