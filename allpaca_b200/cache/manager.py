@@ -76,6 +76,23 @@ def host_library() -> ctypes.CDLL:
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                                          c_void_p]
         lib.apc_prepare_step.restype = c_int
+        lib.aps_create.argtypes = [c_void_p, c_int, c_int64, c_int64, c_int64]
+        lib.aps_create.restype = c_void_p
+        lib.aps_destroy.argtypes = [c_void_p]
+        lib.aps_destroy.restype = None
+        for name, args in {
+            "aps_add": [c_void_p, c_int64, c_int64, c_int64, POINTER(c_int), c_int],
+            "aps_adopt_running": [c_void_p, c_int64, c_int64, c_int64, c_int64],
+            "aps_has_unfinished": [c_void_p], "aps_schedule": [c_void_p, POINTER(c_int)],
+            "aps_advance": [c_void_p, POINTER(c_int), c_int, POINTER(c_int)], "aps_abort": [c_void_p, c_int64],
+            "aps_list": [c_void_p, c_int, POINTER(c_int64), c_int],
+        }.items():
+            getattr(lib, name).argtypes = args
+            getattr(lib, name).restype = c_int
+        lib.aps_planned.argtypes = [c_void_p, POINTER(c_int64), POINTER(c_int64), POINTER(c_int64)]
+        lib.aps_planned.restype = None
+        lib.aps_finished.argtypes = [c_void_p, POINTER(c_int64), POINTER(c_int)]
+        lib.aps_finished.restype = None
         _lib = lib
     return _lib
 
@@ -158,7 +175,9 @@ class CacheManager:
             arr(*[(g.window or -1) for g in self.groups]), self.max_seqs)
         if not self._h:
             raise CacheError("the cache manager could not be created")
-        self._handles: Dict[Hashable, int] = {}
+        self._handles: Dict[Hashable, int] = {}      # requests that hold cache -> their number
+        self._numbers: Dict[Hashable, int] = {}      # every request that has been given a number
+        self._pinned = set()                          # numbers a scheduler keeps across preemption
         self._next = 0
         self._ints = (c_int * max(n, 1))()
 
@@ -176,6 +195,27 @@ class CacheManager:
     def native(self) -> int:
         """The C++ object, for other native code (the step builder)."""
         return self._h
+
+    def number(self, req: Hashable) -> int:
+        """The number native code knows the request by, given out on first asking.  It stays the
+        same until the request's cache is freed (or, when pinned, until it is unpinned)."""
+        n = self._numbers.get(req)
+        if n is None:
+            n = self._numbers[req] = self._next
+            self._next += 1
+        return n
+
+    def pin(self, req: Hashable) -> int:
+        """Keep the request's number across :meth:`free` (a scheduler that may preempt and
+        recompute it); returns the number."""
+        n = self.number(req)
+        self._pinned.add(req)
+        return n
+
+    def unpin(self, req: Hashable) -> None:
+        self._pinned.discard(req)
+        if req not in self._handles:
+            self._numbers.pop(req, None)
 
     def _need(self, req: Hashable) -> int:
         try:
@@ -197,32 +237,38 @@ class CacheManager:
         """Register a request and give it a state slot.  Returns the slot."""
         if req in self._handles:
             raise CacheError(f"request {req!r} already holds a cache")
-        h = self._next
+        known = req in self._numbers
+        h = self.number(req)
         slot = c_int(-1)
         rc = self._lib.apc_cache_begin(self._h, h, ctypes.byref(slot))
         if rc != _OK:
+            if not known:
+                self._numbers.pop(req, None)
             _raise(rc)
-        self._next += 1
         self._handles[req] = h
         return slot.value
 
     def adopt(self, req: Hashable) -> int:
         """Reserve the handle a new request will get from native code that begins it
         (the step builder); returns it."""
-        h = self._next
-        self._next += 1
+        h = self.number(req)
         self._handles[req] = h
         return h
 
     def forget(self, req: Hashable) -> None:
-        """Drop a handle reserved with :meth:`adopt` whose request never began."""
+        """Drop a handle reserved with :meth:`adopt` whose request never began, or one whose
+        cache native code has freed itself (a preemption by the scheduler)."""
         self._handles.pop(req, None)
+        if req not in self._pinned:
+            self._numbers.pop(req, None)
 
     def free(self, req: Hashable) -> None:
         """Give back everything the request holds."""
         h = self._handles.pop(req, None)
         if h is None:
             raise CacheError(f"request {req!r} holds no cache (freed twice?)")
+        if req not in self._pinned:
+            self._numbers.pop(req, None)
         rc = self._lib.apc_cache_free(self._h, h)
         if rc != _OK:
             _raise(rc, f"request {req!r}")

@@ -1,11 +1,13 @@
 // Flat C interface of the host library (called from Python through ctypes).  Handles are
 // opaque pointers; every function returns a status (0 ok, 1 misuse, 2 out of pages) unless it
 // says otherwise, and apc_last_error() gives the text of the last failure on this thread.
+#include <algorithm>
 #include <cstring>
 #include <string>
 #include <vector>
 
 #include "cache_manager.hpp"
+#include "scheduler.hpp"
 #include "step_builder.hpp"
 
 #define APC_EXPORT extern "C" __attribute__((visibility("default")))
@@ -104,4 +106,64 @@ APC_EXPORT int apc_prepare_step(void* c, int vocab, int64_t max_model_len, int64
     layout->off_slot = L.off_slot; layout->off_rows = L.off_rows;
     for (int g = 0; g < 8; ++g) { layout->off_table[g] = L.off_table[g]; layout->width[g] = L.width[g]; }
     return kOk;
+}
+
+// ---- scheduler -----------------------------------------------------------------------------
+APC_EXPORT void* aps_create(void* cache, int max_num_seqs, int64_t token_budget, int64_t prefill_chunk,
+                            int64_t max_model_len) {
+    if (!cache || max_num_seqs <= 0 || token_budget <= 0 || prefill_chunk <= 0 || max_model_len <= 0) return nullptr;
+    return new Scheduler((CacheManager*)cache, max_num_seqs, token_budget, prefill_chunk, max_model_len);
+}
+APC_EXPORT void aps_destroy(void* s) { delete (Scheduler*)s; }
+static int sdone(Scheduler* s, int rc) {
+    if (rc != kOk) g_error = s->error();
+    return rc;
+}
+APC_EXPORT int aps_add(void* s, int64_t id, int64_t prompt_len, int64_t max_tokens, const int* stop_ids, int num_stop) {
+    return sdone((Scheduler*)s, ((Scheduler*)s)->add(id, prompt_len, max_tokens, stop_ids, num_stop));
+}
+APC_EXPORT int aps_adopt_running(void* s, int64_t id, int64_t prompt_len, int64_t max_tokens, int64_t num_computed) {
+    return sdone((Scheduler*)s, ((Scheduler*)s)->adopt_running(id, prompt_len, max_tokens, num_computed));
+}
+APC_EXPORT int aps_has_unfinished(void* s) { return ((Scheduler*)s)->has_unfinished() ? 1 : 0; }
+// Plans a step.  counts[0..2] receive the numbers of rows, preempted and admitted requests.
+APC_EXPORT int aps_schedule(void* s, int* counts) {
+    Scheduler* sc = (Scheduler*)s;
+    const int rc = sdone(sc, sc->schedule());
+    counts[0] = (int)sc->rows().size();
+    counts[1] = (int)sc->preempted().size();
+    counts[2] = (int)sc->admitted().size();
+    return rc;
+}
+// The planned step: rows as (id, start, count, samples) quadruples, then the ids preempted and admitted.
+APC_EXPORT void aps_planned(void* s, int64_t* rows, int64_t* preempted, int64_t* admitted) {
+    Scheduler* sc = (Scheduler*)s;
+    size_t k = 0;
+    for (const ScheduledRows& r : sc->rows()) {
+        rows[k++] = r.id;
+        rows[k++] = r.start;
+        rows[k++] = r.count;
+        rows[k++] = r.samples;
+    }
+    std::copy(sc->preempted().begin(), sc->preempted().end(), preempted);
+    std::copy(sc->admitted().begin(), sc->admitted().end(), admitted);
+}
+// Records the step; *num_finished receives how many requests are done.
+APC_EXPORT int aps_advance(void* s, const int* sampled, int num_sampled, int* num_finished) {
+    Scheduler* sc = (Scheduler*)s;
+    const int rc = sdone(sc, sc->advance(sampled, num_sampled));
+    *num_finished = rc == kOk ? (int)sc->finished().size() : 0;
+    return rc;
+}
+APC_EXPORT void aps_finished(void* s, int64_t* ids, int* reasons) {
+    Scheduler* sc = (Scheduler*)s;
+    std::copy(sc->finished().begin(), sc->finished().end(), ids);
+    std::copy(sc->reasons().begin(), sc->reasons().end(), reasons);
+}
+APC_EXPORT int aps_abort(void* s, int64_t id) { return ((Scheduler*)s)->abort(id); }
+// running (which = 0) or waiting (1) ids in their order; returns how many there are
+APC_EXPORT int aps_list(void* s, int which, int64_t* out, int cap) {
+    const std::vector<int64_t> v = ((Scheduler*)s)->list(which);
+    for (int i = 0; i < (int)v.size() && i < cap; ++i) out[i] = v[i];
+    return (int)v.size();
 }

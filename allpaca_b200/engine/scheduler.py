@@ -1,5 +1,10 @@
 """Continuous batching: which requests run which tokens in the next step.
 
+The decisions are made by the C++ scheduler (``csrc/host/scheduler.cpp``, part of the host
+library that also holds the cache manager and the step builder); this module keeps the
+requests' token lists and sampling parameters, which native code never needs, and mirrors
+the few fields callers read (status, tokens computed, preemptions).
+
 Every step is one batch under a token budget: first one row for each running request
 that is decoding, then portions of running prompts, then newly admitted requests, in
 order of arrival.  A prompt is cut into portions of at most ``prefill_chunk`` tokens
@@ -25,11 +30,13 @@ of this engine.
 from __future__ import annotations
 
 import enum
-from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional
+from typing import Dict, Hashable, List, Optional
+
+import ctypes
 
 from ..cache import CacheManager
+from ..cache.manager import host_library
 from ..sampling.params import SamplingParams
 
 
@@ -99,6 +106,10 @@ class SchedulerOutput:
 
 
 class Scheduler:
+    """The Python face of the native scheduler."""
+
+    _REASONS = {1: FinishReason.STOP, 2: FinishReason.LENGTH}
+
     def __init__(self, cache: CacheManager, max_num_seqs: int, max_num_batched_tokens: int,
                  prefill_chunk: int, max_model_len: int):
         self.cache = cache
@@ -106,186 +117,136 @@ class Scheduler:
         self.token_budget = max_num_batched_tokens
         self.prefill_chunk = prefill_chunk
         self.max_model_len = max_model_len
-        self.waiting: Deque[Request] = deque()
-        self.running: List[Request] = []
+        self._lib = host_library()
+        self._h = self._lib.aps_create(cache.native, int(max_num_seqs), int(max_num_batched_tokens),
+                                       int(prefill_chunk), int(max_model_len))
+        if not self._h:
+            raise ValueError("the scheduler needs a positive number of sequences, token budget, portion "
+                             "size and length limit")
+        self._requests: Dict[int, Request] = {}          # number -> request, while running or waiting
         self._arrivals = 0
+        self._counts = (ctypes.c_int * 3)()
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.aps_destroy(self._h)
+            self._h = None
+
+    def _error(self) -> str:
+        return self._lib.apc_last_error().decode()
 
     # ---- adding ---------------------------------------------------------
     def add(self, request: Request) -> None:
-        n = len(request.prompt_token_ids)
-        if n == 0:
-            raise AdmissionError("a request needs at least one prompt token")
-        if n >= self.max_model_len:
-            raise AdmissionError(f"a prompt of {n} tokens leaves no room under the model's "
-                                 f"length limit {self.max_model_len}")
-        longest = min(n + request.params.max_tokens, self.max_model_len)
-        for g, layout in enumerate(self.cache.groups):
-            need = -(-longest // layout.page_size)
-            if layout.window is not None:
-                # a windowed group keeps at most the window plus one step's rows alive
-                span = layout.window + min(self.prefill_chunk, self.token_budget) + layout.page_size
-                need = min(need, -(-span // layout.page_size) + 1)
-            if need > layout.num_pages:
-                raise AdmissionError(
-                    f"request {request.request_id!r} may hold {longest} tokens = {need} pages of "
-                    f"cache group {g}, whose pool has {layout.num_pages}")
+        known = request.request_id in self.cache._pinned
+        n = self.cache.pin(request.request_id)
+        stops = request.params.stop_token_ids
+        arr = (ctypes.c_int * max(len(stops), 1))(*stops)
+        rc = self._lib.aps_add(self._h, n, len(request.prompt_token_ids), int(request.params.max_tokens),
+                               arr, len(stops))
+        if rc != 0:
+            if not known:
+                self.cache.unpin(request.request_id)
+            raise AdmissionError(f"request {request.request_id!r}: {self._error()}")
         request.arrival = self._arrivals
         self._arrivals += 1
         request.status = RequestStatus.WAITING
-        self.waiting.append(request)
+        self._requests[n] = request
+
+    def adopt_running(self, request: Request, num_computed: int) -> None:
+        """A request whose first ``num_computed`` prompt tokens are already in the cache (put
+        there by the caller) joins the running requests."""
+        n = self.cache.pin(request.request_id)
+        rc = self._lib.aps_adopt_running(self._h, n, len(request.prompt_token_ids),
+                                         int(request.params.max_tokens), int(num_computed))
+        if rc != 0:
+            self.cache.unpin(request.request_id)
+            raise AdmissionError(f"request {request.request_id!r}: {self._error()}")
+        request.arrival = self._arrivals
+        self._arrivals += 1
+        request.num_computed = int(num_computed)
+        request.status = RequestStatus.RUNNING
+        self._requests[n] = request
 
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.aps_has_unfinished(self._h))
+
+    def _listed(self, which: int) -> List[Request]:
+        cap = max(len(self._requests), 1)
+        buf = (ctypes.c_int64 * cap)()
+        n = self._lib.aps_list(self._h, which, buf, cap)
+        return [self._requests[buf[i]] for i in range(min(n, cap))]
+
+    @property
+    def running(self) -> List[Request]:
+        """The running requests in the scheduler's order (a copy)."""
+        return self._listed(0)
+
+    @property
+    def waiting(self) -> List[Request]:
+        """The waiting requests, the next to be admitted first (a copy)."""
+        return self._listed(1)
 
     # ---- one step -------------------------------------------------------
     def schedule(self) -> SchedulerOutput:
-        budget = self.token_budget
-        rows: List[ScheduledRows] = []
-        preempted: List[Request] = []
-        reserved = [0] * len(self.cache.groups)
-
-        def fits(req: Request, count: int) -> bool:
-            key = req.request_id if self.cache.has(req.request_id) else None
-            return self.cache.can_append(key, count, reserved)
-
-        def reserve(req: Request, count: int) -> None:
-            key = req.request_id if self.cache.has(req.request_id) else None
-            for g, m in enumerate(self.cache.pages_missing(key, count)):
-                reserved[g] += m
-
-        # 1. decode rows of running requests, oldest first; preempt the youngest on shortage
-        self.running.sort(key=lambda r: r.arrival)
-        decoding = [r for r in self.running if r.num_tokens - r.num_computed == 1]
-        i = 0
-        while i < len(decoding):
-            req = decoding[i]
-            if budget <= 0:
-                break
-            if fits(req, 1):
-                reserve(req, 1)
-                rows.append(ScheduledRows(req, req.num_computed, 1, True))
-                budget -= 1
-                i += 1
-                continue
-            victim = max(self.running, key=lambda r: r.arrival)
-            self._preempt(victim)
-            preempted.append(victim)
-            # drop rows already planned for the victim and what they had reserved
-            if any(r.request is victim for r in rows):
-                rows = [r for r in rows if r.request is not victim]
-                budget = self.token_budget - sum(r.count for r in rows)
-                reserved = [0] * len(self.cache.groups)
-                for r in rows:
-                    reserve(r.request, r.count)
-            decoding = [r for r in decoding if r is not victim]
-            if victim is req:
-                continue
-
-        # 2. portions of running prompts; if every running request is starved of pages,
-        #    preempt the youngest and try again
-        while True:
-            for req in self.running:
-                if budget <= 0:
-                    break
-                left = req.num_tokens - req.num_computed
-                if left <= 1:
-                    continue
-                count = self._largest_fit(req, min(left, budget, self.prefill_chunk), reserved)
-                if count <= 0:
-                    continue
-                reserve(req, count)
-                rows.append(ScheduledRows(req, req.num_computed, count, count == left))
-                budget -= count
-            if rows or not self.running:
-                break
-            victim = max(self.running, key=lambda r: r.arrival)
-            self._preempt(victim)
-            preempted.append(victim)
-
-        # 3. admit waiting requests in order while all the tokens they hold would fit;
-        #    stop at the first that does not
-        while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs \
-                and self.cache.can_begin():
-            req = self.waiting[0]
-            left = req.num_tokens - req.num_computed
-            if not self.cache.can_append(None, left, reserved):
-                break
-            count = min(left, budget, self.prefill_chunk)
-            self.waiting.popleft()
-            req.status = RequestStatus.RUNNING
-            self.running.append(req)
-            reserve(req, count)
-            rows.append(ScheduledRows(req, req.num_computed, count, count == left))
-            budget -= count
-
-        if not rows and self.has_unfinished() and not preempted:
-            raise RuntimeError("the scheduler found nothing to run although requests are pending")
+        rc = self._lib.aps_schedule(self._h, self._counts)
+        if rc != 0:
+            raise RuntimeError(self._error())
+        nrows, npre, nadm = self._counts[0], self._counts[1], self._counts[2]
+        rows_buf = (ctypes.c_int64 * max(4 * nrows, 1))()
+        pre_buf = (ctypes.c_int64 * max(npre, 1))()
+        adm_buf = (ctypes.c_int64 * max(nadm, 1))()
+        self._lib.aps_planned(self._h, rows_buf, pre_buf, adm_buf)
+        reqs = self._requests
+        preempted = []
+        for i in range(npre):
+            req = reqs[pre_buf[i]]
+            req.num_computed = 0
+            req.status = RequestStatus.WAITING
+            req.num_preemptions += 1
+            self.cache.forget(req.request_id)        # native code has freed its pages and slot
+            preempted.append(req)
+        for i in range(nadm):
+            reqs[adm_buf[i]].status = RequestStatus.RUNNING
+        rows = [ScheduledRows(reqs[rows_buf[4 * i]], rows_buf[4 * i + 1], rows_buf[4 * i + 2],
+                              bool(rows_buf[4 * i + 3])) for i in range(nrows)]
         return SchedulerOutput(rows, preempted)
-
-    def _largest_fit(self, req: Request, want: int, reserved) -> int:
-        """The most tokens up to ``want`` whose pages are free (0 if not even one)."""
-        key = req.request_id if self.cache.has(req.request_id) else None
-        if want <= 0:
-            return 0
-        if self.cache.can_append(key, want, reserved):
-            return want
-        lo, hi = 0, want                     # can_append(lo) holds or lo == 0
-        while lo < hi:
-            mid = (lo + hi + 1) // 2
-            if self.cache.can_append(key, mid, reserved):
-                lo = mid
-            else:
-                hi = mid - 1
-        return lo
-
-    def _preempt(self, req: Request) -> None:
-        self.running.remove(req)
-        if self.cache.has(req.request_id):
-            self.cache.free(req.request_id)
-        req.num_computed = 0
-        req.status = RequestStatus.WAITING
-        req.num_preemptions += 1
-        self.waiting.appendleft(req)
 
     # ---- after the step -------------------------------------------------
     def advance(self, output: SchedulerOutput, sampled: Dict[Hashable, int]) -> List[Request]:
         """Record the step: rows are now cached; sampled tokens are appended; requests that
         are done are taken out (their cache is the caller's to free).  Returns them."""
-        finished: List[Request] = []
+        toks = [int(sampled[r.request.request_id]) for r in output.rows if r.samples]
+        arr = (ctypes.c_int * max(len(toks), 1))(*toks)
+        nfin = ctypes.c_int(0)
+        rc = self._lib.aps_advance(self._h, arr, len(toks), ctypes.byref(nfin))
+        if rc != 0:
+            raise RuntimeError(self._error())
+        k = 0
         for r in output.rows:
-            req = r.request
-            req.num_computed += r.count
-            if not r.samples:
-                continue
-            tok = sampled[req.request_id]
-            req.output_token_ids.append(int(tok))
-            reason = self._finish_reason(req, int(tok))
-            if reason is not None:
-                req.finish_reason = reason
+            r.request.num_computed += r.count
+            if r.samples:
+                r.request.output_token_ids.append(toks[k])
+                k += 1
+        finished: List[Request] = []
+        if nfin.value:
+            ids = (ctypes.c_int64 * nfin.value)()
+            reasons = (ctypes.c_int * nfin.value)()
+            self._lib.aps_finished(self._h, ids, reasons)
+            for i in range(nfin.value):
+                req = self._requests.pop(ids[i])
+                req.finish_reason = self._REASONS[reasons[i]]
                 req.status = RequestStatus.FINISHED
-                self.running.remove(req)
+                self.cache.unpin(req.request_id)
                 finished.append(req)
         return finished
 
-    def _finish_reason(self, req: Request, tok: int) -> Optional[FinishReason]:
-        # stop wins over length (crates/allpaca-core/src/engine.rs:4607-4621)
-        if tok in req.params.stop_token_ids:
-            return FinishReason.STOP
-        if len(req.output_token_ids) >= req.params.max_tokens:
-            return FinishReason.LENGTH
-        if req.num_tokens >= self.max_model_len:
-            return FinishReason.LENGTH
-        return None
-
     def abort(self, request_id: Hashable) -> Optional[Request]:
-        for req in list(self.running):
-            if req.request_id == request_id:
-                self.running.remove(req)
-                req.status = RequestStatus.FINISHED
-                return req
-        for req in list(self.waiting):
-            if req.request_id == request_id:
-                self.waiting.remove(req)
-                req.status = RequestStatus.FINISHED
-                return req
-        return None
+        """Take a request out, running or waiting; its cache is the caller's to free."""
+        n = self.cache._numbers.get(request_id)
+        if n is None or n not in self._requests:
+            return None
+        self._lib.aps_abort(self._h, n)
+        req = self._requests.pop(n)
+        req.status = RequestStatus.FINISHED
+        self.cache.unpin(request_id)
+        return req

@@ -145,6 +145,7 @@ def main() -> int:
     from allpaca_b200.config.presets import preset_config
     from allpaca_b200.engine.batch import BatchEntry
     from allpaca_b200.engine.runner import ModelRunner
+    from allpaca_b200.engine.scheduler import Request
     from allpaca_b200.ops import library
     from allpaca_b200.parts import BuildEnv, Workspace
     from allpaca_b200.weights.random_model import random_model_on_device
@@ -184,17 +185,13 @@ def main() -> int:
         """Requests that already hold `start_len - 1` tokens of (synthetic, zero) cache: the
         next step runs their last prompt token and decoding goes on from there."""
         ids = []
-        for _ in range(batch):
+        for i in range(batch):
             prompt = torch.randint(0, cfg.vocab_size, (start_len,), generator=gen).tolist()
-            rid = llm.add_request(prompt, SamplingParams.greedy_params(max_tokens=10 ** 6))
-            ids.append(rid)
-        for req in list(llm.scheduler.waiting):
-            llm.scheduler.waiting.remove(req)
-            llm.scheduler.running.append(req)
-            req.status = type(req.status).RUNNING
+            req = Request(("bench", i), prompt, SamplingParams.greedy_params(max_tokens=10 ** 6))
+            llm.scheduler.adopt_running(req, start_len - 1)
             runner.cache.begin(req.request_id)
             runner.cache.append(req.request_id, start_len - 1)
-            req.num_computed = start_len - 1
+            ids.append(req.request_id)
         return ids
 
     def drain(llm):
@@ -220,7 +217,7 @@ def main() -> int:
         reqs = list(llm.scheduler.running)
         tokens = [r.all_token_ids[-1] for r in reqs]
         for r in reqs:                        # the scheduler no longer drives these requests
-            llm.scheduler.running.remove(r)
+            llm.scheduler.abort(r.request_id)
         out = torch.empty(batch, dtype=torch.int32, device=device)
 
         def one_step(toks):
