@@ -153,7 +153,12 @@ class ModelRunner:
             gs.graph.replay()
             library.add_launches(gs.num_kernels)
             return gs.logits
-        # first use (or buffers moved): run eagerly, which also sizes every buffer, then record
+        # A batch size that shows up once or twice (requests finishing one after another) is
+        # run as it is: recording costs about two steps.  From the third use on: run eagerly,
+        # which also sizes every buffer, then record.
+        gs.uses += 1
+        if gs.uses < 3:
+            return self.model.forward(batch)
         logits = self.model.forward(batch)
         torch.cuda.current_stream().synchronize()
         before = library.launch_count()
@@ -241,3 +246,4 @@ class _DecodeGraph:
         self.logits = None
         self.generation = -1
         self.num_kernels = 0
+        self.uses = 0                 # steps of this size so far that found no valid graph

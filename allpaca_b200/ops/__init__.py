@@ -6,6 +6,7 @@ consumer a 32-bit tensor ``[S, T, N]``; consumers add the S slices in order.
 """
 from __future__ import annotations
 
+import functools
 from typing import Optional, Sequence
 
 import torch
@@ -370,6 +371,14 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
 
 def decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: int, window: int = 0,
                   slots: int = 444, cluster_sizes: Sequence[int] = ()) -> int:
+    """Key slices for the split kernels (see :func:`_decode_splits`; results are remembered)."""
+    return _decode_splits(int(rows), int(num_heads), int(num_kv_heads), int(max_context), int(window or 0),
+                          int(slots), tuple(cluster_sizes))
+
+
+@functools.lru_cache(maxsize=4096)
+def _decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: int, window: int,
+                   slots: int, cluster_sizes: tuple) -> int:
     """Key slices for the split kernels.
 
     The cp.async kernel runs three CTAs per SM (``slots`` 444), the one fed by TMA two (296).

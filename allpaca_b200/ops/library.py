@@ -133,9 +133,20 @@ def call(lib: ctypes.CDLL, name: str, *args) -> None:
         raise KernelError(f"{name} failed (status {rc}): {msg.decode() if msg else 'no message'}")
 
 
+_raw_stream = None
+
+
 def stream_handle() -> int:
-    import torch
-    return torch.cuda.current_stream().cuda_stream
+    """The CUDA stream torch currently launches on, as the integer the C entry points take."""
+    global _raw_stream
+    if _raw_stream is None:
+        import torch
+        fast = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+        if fast is not None:
+            _raw_stream = lambda: fast(torch.cuda.current_device())          # noqa: E731
+        else:
+            _raw_stream = lambda: torch.cuda.current_stream().cuda_stream    # noqa: E731
+    return _raw_stream()
 
 
 _launches = 0

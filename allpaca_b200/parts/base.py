@@ -85,9 +85,14 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._buffers: Dict[str, torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}     # (name, shape, dtype) -> the view last handed out
         self.generation = 0          # grows whenever a buffer is replaced (its address changes)
 
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        vkey = (name, tuple(shape), dtype)
+        view = self._views.get(vkey)
+        if view is not None:
+            return view                  # the same shape as before: the same view of the same memory
         n = 1
         for s in shape:
             n *= int(s)
@@ -98,7 +103,13 @@ class Workspace:
             buf = torch.empty(grow, dtype=dtype, device=self.device)
             self._buffers[key] = buf
             self.generation += 1
-        return buf[:n].view(*shape)
+            # views of the buffer this one replaces are stale
+            self._views = {k: v for k, v in self._views.items() if not (k[0] == name and k[2] == dtype)}
+        view = buf[:n].view(*shape)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[vkey] = view
+        return view
 
     def get_zeroed(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         """Like :meth:`get`, but the memory is zero when it is first handed out (and after
@@ -112,6 +123,7 @@ class Workspace:
             buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buf
             self.generation += 1
+            self._views = {k: v for k, v in self._views.items() if not (k[0] == name and k[2] == dtype)}
         return buf[:n].view(*shape)
 
     def bytes(self) -> int:

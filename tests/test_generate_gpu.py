@@ -159,7 +159,8 @@ def test_cuda_graphs_do_not_change_the_tokens(tmp_path):
         llm = LLM(runner=runner)
         outs.append([o.token_ids for o in llm.generate(prompts, SamplingParams.greedy_params(max_tokens=24))])
         if graphs:
-            assert runner._graphs and all(g.graph is not None for g in runner._graphs.values())
+            # batch sizes that were used three times or more have been recorded
+            assert runner._graphs and any(g.graph is not None for g in runner._graphs.values())
     assert outs[0] == outs[1]
 
 
