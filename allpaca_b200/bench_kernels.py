@@ -58,7 +58,8 @@ def bench_gemm(args) -> dict:
         # the persistent kernel; with --swiglu the rows of w alternate gate and up
         kernel = "gemm_tc_persistent"
         out = torch.empty(M, N // 2 if args.swiglu else N, device="cuda", dtype=odt)
-        fn = lambda i: ops.gemm_tc_persistent(a, ws[i % copies], out, pairs=args.swiglu)   # noqa: E731
+        fn = lambda i: ops.gemm_tc_persistent(a, ws[i % copies], out, pairs=args.swiglu,   # noqa: E731
+                                              share_tiles=not args.whole_tiles)
         S = 1
     elif args.dual:
         # two weight tiles per CTA; with --swiglu w is [gate; up]
@@ -170,6 +171,8 @@ def main(argv=None) -> int:
             s.add_argument("--out", choices=["float32", "bfloat16"], default="bfloat16")
             s.add_argument("--dual", action="store_true", help="more than 64 rows: two weight tiles per CTA")
             s.add_argument("--single", action="store_true", help="more than 64 rows: one tile per CTA, not persistent")
+            s.add_argument("--whole-tiles", action="store_true",
+                           help="persistent kernel: never share a tile's K among several CTAs")
             s.add_argument("--swiglu", action="store_true", help="w holds gate and up rows: fused gated activation")
         else:
             s.add_argument("--heads", type=int, default=32)

@@ -700,29 +700,82 @@ AP_EXPORT int ap_gemm_tc_prefers_dual(int M, int N, int K) {
 }
 
 // ---------------------------------------------------------------------------
-// Many rows (prompt portions): a persistent kernel, one CTA per SM, that walks output tiles of
-// 128 weight rows x BN tokens.  The accumulator is double-buffered in tensor memory (2 x BN
-// columns), so the four epilogue warps read tile j out and write it while the tensor cores
-// are already on tile j+1; the operand ring keeps running across tiles.  Consecutive tiles
-// differ in the token tile first, so the CTAs that run at the same time share weight tiles
-// and the whole activation matrix stays in L2.
+// Many rows (prompt portions): a persistent kernel, one CTA per SM, over output tiles of 128
+// weight rows x BN tokens, dealt out round robin (consecutive tiles differ in the token tile
+// first, so the CTAs that run side by side share weight tiles through L2).
+//
+// Fewer tiles than half the SMs and a long K (a portion of a few hundred tokens against the
+// down projection): every tile is shared by `split` CTAs, each taking an equal range of K.  CTA g works on tile
+// g % tiles and range g / tiles, so the CTAs of one range run side by side as before.  The
+// CTAs of ranges 1.. hand their partial sums over in a scratch buffer ([token][weight row],
+// 32-bit) and raise a flag; the CTA of range 0, which has worked just as long, adds them in
+// range order and writes the tile.  The flags are left zero for the next product.
+//
+// The accumulator is double-buffered in tensor memory (2 x BN columns), so the four epilogue
+// warps read one segment out while the tensor cores are on the next; the operand ring keeps
+// running across segments.
 //
 // PAIRS: the weight's rows alternate gate, up, gate, up ... (row 2i and 2i+1 belong to output
 // column i).  Neighbouring lanes exchange their values by shuffle and the epilogue writes
 // silu(gate) * up to out[M, N/2]: the gated activation never makes a round trip to memory.
 // ---------------------------------------------------------------------------
+#define TC_ERR_PEER_WAIT 5
+#define PERSIST_MAX_CTAS 256                 // flags at the head of the scratch buffer
+
 template <int BN> struct PersistCfg {
     static constexpr int kStages = BN >= 256 ? 4 : 6;
     static constexpr int kBBytes = BN * TILE_K * 2;
     static constexpr int kStageBytes = A_TILE_BYTES + kBBytes;
     static constexpr int kTmemCols = 2 * BN;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr long long kPartialFloats = (long long)TILE_W * BN;       // per CTA
 };
+
+// A CTA's next piece of work: blocks [kb0, kb1) of K of one output tile.
+struct Segment { int tile, kb0, kb1; };
+
+// The work of CTA g of G in the order it is done.  split == 1: whole tiles g, g + G, ...;
+// split > 1 (G == tiles * split): range g / tiles of the K blocks of tile g % tiles.
+struct WorkList {
+    int next_tile, tiles, G, nkb, split, g;
+    bool done;
+    __device__ __forceinline__ WorkList(int tiles_, int nkb_, int G_, int g_, int split_)
+        : next_tile(g_), tiles(tiles_), G(G_), nkb(nkb_), split(split_), g(g_), done(false) {}
+    __device__ __forceinline__ bool next(Segment& s) {
+        if (split > 1) {
+            if (done || g >= tiles * split) return false;
+            done = true;
+            const int slice = g / tiles;
+            s.tile = g - slice * tiles;
+            s.kb0 = (int)((long long)nkb * slice / split);
+            s.kb1 = (int)((long long)nkb * (slice + 1) / split);
+            return s.kb1 > s.kb0;
+        }
+        if (next_tile >= tiles) return false;
+        s.tile = next_tile;
+        s.kb0 = 0;
+        s.kb1 = nkb;
+        next_tile += G;
+        return true;
+    }
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// the four epilogue warps among themselves (barrier 1; barrier 0 is __syncthreads)
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <int BN, typename TO, bool PAIRS>
 __global__ void __launch_bounds__(192)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
-                          TO* __restrict__ out, int M, int N, int K, long long ldc, int tiles_m, int tiles_total) {
+                          TO* __restrict__ out, int M, int N, int K, long long ldc, int tiles_m, int tiles_total,
+                          int split, int* __restrict__ flags, float* __restrict__ partials) {
     using Cfg = PersistCfg<BN>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -735,12 +788,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
     uint64_t* acc_empty = acc_full + 2;        // [accumulator buffer]
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    volatile int* peer_ok = (volatile int*)(tmem_slot + 2);
 
     if (*(volatile int*)&g_tc_status != 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nkb = (K + TILE_K - 1) / TILE_K;
-    const int my_tiles = ((int)blockIdx.x < tiles_total) ? (tiles_total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-
+    const int G = gridDim.x, g = blockIdx.x;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             tc::mbar_init(&full[s], 1);
@@ -762,30 +815,31 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0 && my_tiles > 0) {
-            const long long total = (long long)my_tiles * nkb;
-            // the weight does not depend on earlier kernels: fill the ring with the first tile's
-            // weight blocks, then wait for the kernels that produce the activations
-            const int pre = (int)min((long long)STAGES, (long long)nkb);
-            {
-                const int t = blockIdx.x;
-                const int n0 = (t / tiles_m) * TILE_W;
-                for (int i = 0; i < pre; ++i) {
-                    tc::mbar_expect_tx(&full[i], Cfg::kStageBytes);
-                    tc::tma_load_2d(w_tiles + i * A_TILE_BYTES, &tmap_w, i * TILE_K, n0, &full[i]);
+        if (lane == 0) {
+            WorkList work(tiles_total, nkb, G, g, split);
+            Segment sg;
+            long long idx = 0, issued = 0;
+            bool first = true;
+            while (!*abort_flag && work.next(sg)) {
+                const int n0 = (sg.tile / tiles_m) * TILE_W, m0 = (sg.tile % tiles_m) * BN;
+                int kb = sg.kb0;
+                if (first) {
+                    // the weight does not depend on earlier kernels: fill the ring with this
+                    // segment's first weight blocks, then wait for the kernels that produce
+                    // the activations
+                    first = false;
+                    const int pre = min(STAGES, sg.kb1 - sg.kb0);
+                    for (int i = 0; i < pre; ++i) {
+                        tc::mbar_expect_tx(&full[i], Cfg::kStageBytes);
+                        tc::tma_load_2d(w_tiles + i * A_TILE_BYTES, &tmap_w, (kb + i) * TILE_K, n0, &full[i]);
+                    }
+                    ap_pdl_wait();
+                    for (int i = 0; i < pre; ++i)
+                        tc::tma_load_2d(a_tiles + i * Cfg::kBBytes, &tmap_a, (kb + i) * TILE_K, m0, &full[i]);
+                    kb += pre;
+                    idx = issued = pre;
                 }
-                ap_pdl_wait();
-                const int m0 = (t % tiles_m) * BN;
-                for (int i = 0; i < pre; ++i)
-                    tc::tma_load_2d(a_tiles + i * Cfg::kBBytes, &tmap_a, i * TILE_K, m0, &full[i]);
-            }
-            long long issued = pre;
-            long long idx = 0;
-            for (int j = 0; j < my_tiles && !*abort_flag; ++j) {
-                const int t = blockIdx.x + j * gridDim.x;
-                const int n0 = (t / tiles_m) * TILE_W, m0 = (t % tiles_m) * BN;
-                for (int kb = 0; kb < nkb; ++kb, ++idx) {
-                    if (idx < pre) continue;
+                for (; kb < sg.kb1; ++kb, ++idx) {
                     const int s = (int)(idx % STAGES);
                     const uint32_t ph = (uint32_t)((idx / STAGES) & 1);
                     if (*abort_flag) break;
@@ -800,7 +854,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
                     issued = idx + 1;
                 }
             }
-            (void)total;
             if (*abort_flag) {
                 // let the loads that are still in flight land before the CTA's memory goes away
                 for (long long i = max(0LL, issued - STAGES); i < issued; ++i)
@@ -812,9 +865,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
             constexpr uint32_t idesc = tc::instr_desc_bf16_f32(TILE_W, BN);
             bool ok = true;
             long long idx = 0;
-            for (int j = 0; j < my_tiles && ok; ++j) {
+            WorkList work(tiles_total, nkb, G, g, split);
+            Segment sg;
+            for (int j = 0; ok && work.next(sg); ++j) {
                 const int b = j & 1;
-                // the epilogue warps have read this buffer's tile of two rounds ago
+                // the epilogue warps have read this buffer's segment of two rounds ago
                 if (!tc::mbar_wait(&acc_empty[b], (uint32_t)(((j >> 1) & 1) ^ 1))) {
                     *abort_flag = 1;
                     atomicExch(&g_tc_status, TC_ERR_ACCUM_WAIT);
@@ -823,7 +878,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
                 }
                 tc::fence_after_sync();
                 const uint32_t acc = tmem_base + (uint32_t)(b * BN);
-                for (int kb = 0; kb < nkb; ++kb, ++idx) {
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++idx) {
                     const int s = (int)(idx % STAGES);
                     const uint32_t ph = (uint32_t)((idx / STAGES) & 1);
                     if (*abort_flag) { ok = false; break; }
@@ -838,7 +893,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
                     const uint64_t ad = tc::smem_desc_k_major_sw128(a_tiles + s * Cfg::kBBytes);
 #pragma unroll
                     for (int k = 0; k < TILE_K / 16; ++k)
-                        tc::mma_bf16(acc, wd + 2 * k, ad + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        tc::mma_bf16(acc, wd + 2 * k, ad + 2 * k, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
                     tc::mma_commit(&empty[s]);
                 }
                 if (ok) tc::mma_commit(&acc_full[b]);
@@ -848,11 +903,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
         // epilogue: warp q reads lanes 32q..32q+31 = weight rows n0 + 32q + lane
         const int q = warp & 3;
         const int row = q * 32 + lane;
+        const int et = threadIdx.x - 64;                 // 0..127 among the epilogue threads
         ap_pdl_wait();          // `out` may still be read by an earlier kernel
         bool ok = true;
-        for (int j = 0; j < my_tiles && ok; ++j) {
-            const int t = blockIdx.x + j * gridDim.x;
-            const int n0 = (t / tiles_m) * TILE_W, m0 = (t % tiles_m) * BN;
+        WorkList work(tiles_total, nkb, G, g, split);
+        Segment sg;
+        for (int j = 0; ok && work.next(sg); ++j) {
+            const int n0 = (sg.tile / tiles_m) * TILE_W, m0 = (sg.tile % tiles_m) * BN;
             const int b = j & 1;
             // tcgen05.ld is warp-wide: the whole warp goes on, or none of it
             if (!__all_sync(0xffffffffu, tc::mbar_wait(&acc_full[b], (uint32_t)((j >> 1) & 1)))) {
@@ -866,12 +923,62 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
             tc::fence_after_sync();
             const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN);
             const int n = n0 + row;
+            const int cols = min(BN, M - m0);           // token rows of this tile that exist
+            if (sg.kb0 > 0) {
+                // not the tile's first block: hand the partial sums over, [token][weight row]
+                float* mine = partials + (size_t)g * Cfg::kPartialFloats;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                if (m0 + c >= M) break;
+                for (int c = 0; c < cols; c += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld_x32(acc + (uint32_t)c, v);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) mine[(size_t)(c + jj) * TILE_W + row] = __uint_as_float(v[jj]);
+                }
+                __threadfence();
+                tc::fence_before_sync();
+                tc::mbar_arrive(&acc_empty[b]);
+                epilogue_sync();
+                if (et == 0) st_release_gpu(&flags[g], 1);
+                continue;
+            }
+            // the tile's first blocks are here: CTAs g + tiles, g + 2 tiles, ... hold the rest of its K
+            int peers = 0;
+            if (sg.kb1 < nkb) {
+                peers = split - 1;
+                if (et == 0) {
+                    int fine = 1;
+                    const long long t0 = clock64();
+                    for (int pi = 0; pi < peers && fine; ++pi) {
+                        while (ld_acquire_gpu(&flags[g + (1 + pi) * tiles_total]) == 0) {
+                            if (clock64() - t0 > 2000000000LL || *abort_flag) { fine = 0; break; }
+                        }
+                        if (fine) flags[g + (1 + pi) * tiles_total] = 0;          // ready for the next product
+                    }
+                    *peer_ok = fine;
+                }
+                epilogue_sync();
+                if (!*peer_ok) {
+                    if (et == 0 && !*abort_flag) {
+                        *abort_flag = 1;
+                        atomicExch(&g_tc_status, TC_ERR_PEER_WAIT);
+                    }
+                    ok = false;
+                    break;
+                }
+            }
+#pragma unroll 1
+            for (int c = 0; c < cols; c += 32) {
                 uint32_t v[32];
                 tc::tmem_ld_x32(acc + (uint32_t)c, v);
                 tc::tmem_ld_wait();
+                for (int pi = 0; pi < peers; ++pi) {
+                    const float* theirs = partials + (size_t)(g + (1 + pi) * tiles_total) * Cfg::kPartialFloats +
+                                          (size_t)c * TILE_W + row;
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj)
+                        v[jj] = __float_as_uint(__uint_as_float(v[jj]) + __ldcg(theirs + (size_t)jj * TILE_W));
+                }
                 if (PAIRS) {
                     // even lane: gate of column n/2, odd lane: up.  The even lane finishes rows
                     // c..c+15, the odd lane rows c+16..c+31, each with the other's half.
@@ -882,11 +989,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
                         const uint32_t other = __shfl_xor_sync(0xffffffffu, odd ? v[jj] : v[16 + jj], 1);
                         // the gate and the up value pass through the storage type, as when the
                         // activation is a kernel of its own
-                        const float g = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? other : v[jj])));
-                        const float u = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? v[16 + jj] : other)));
+                        const float gt = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? other : v[jj])));
+                        const float up = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? v[16 + jj] : other)));
                         const int m = m0 + c + (odd ? 16 : 0) + jj;
                         if (m < M && n < N)
-                            dst[(size_t)jj * ldc] = ap_from_float<TO>(__fdividef(g, 1.0f + __expf(-g)) * u);
+                            dst[(size_t)jj * ldc] = ap_from_float<TO>(__fdividef(gt, 1.0f + __expf(-gt)) * up);
                     }
                 } else if (n < N) {
 #pragma unroll
@@ -911,7 +1018,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
 
 template <int BN, typename TO, bool PAIRS>
 static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K,
-                             long long ldc, cudaStream_t stream) {
+                             long long ldc, void* scratch, long long scratch_bytes, cudaStream_t stream) {
     using Cfg = PersistCfg<BN>;
     auto kern = gemm_tc_persistent_kernel<BN, TO, PAIRS>;
     static bool configured = false;
@@ -929,17 +1036,49 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& ma, void*
     const int tiles_m = (M + BN - 1) / BN;
     const long long tiles = (long long)tiles_m * ((N + TILE_W - 1) / TILE_W);
     AP_REQUIRE(tiles < (1LL << 30), "gemm_tc: too many output tiles");
-    dim3 grid((unsigned)min((long long)sms, tiles), 1, 1);
+    // Fewer tiles than half the SMs, a scratch buffer at hand and enough K to share: `split`
+    // CTAs per tile.  Else whole tiles, round robin.
+    const int max_ctas = min(sms, PERSIST_MAX_CTAS);
+    const int nkb = (K + TILE_K - 1) / TILE_K;
+    int split = 1;
+    if (scratch && tiles * 2 <= max_ctas) {
+        split = (int)min((long long)8, (long long)max_ctas / tiles);
+        // handing partial sums over costs about as much as fifty blocks of K: share a tile only
+        // where every CTA keeps about that many
+        split = min(split, nkb / 48);
+        if (split < 1) split = 1;
+        const long long need = (long long)PERSIST_MAX_CTAS * 4 + tiles * split * Cfg::kPartialFloats * 4;
+        if (split > 1 && scratch_bytes < need) split = 1;
+    }
+    const int ctas = split > 1 ? (int)tiles * split : (int)min((long long)max_ctas, tiles);
+    int* flags = nullptr;
+    float* partials = nullptr;
+    if (split > 1) {
+        AP_REQUIRE(((uintptr_t)scratch & 15) == 0, "gemm_tc: the scratch buffer must be 16-byte aligned");
+        flags = (int*)scratch;
+        partials = (float*)((char*)scratch + PERSIST_MAX_CTAS * 4);
+    }
+    dim3 grid((unsigned)ctas, 1, 1);
     AP_CHECK_PDL_LAUNCH("gemm_tc_persistent", ap_launch_pdl(kern, grid, dim3(192), (size_t)Cfg::kSmemBytes, stream, mw,
-                                                            ma, (TO*)out, M, N, K, ldc, tiles_m, (int)tiles));
+                                                            ma, (TO*)out, M, N, K, ldc, tiles_m, (int)tiles, split,
+                                                            flags, partials));
     return AP_OK;
+}
+
+// Bytes of scratch with which ap_gemm_tc_persistent shares few tiles among all SMs.  The
+// buffer must be zero when first used and belongs to one stream; the kernel leaves its head
+// (the flags) zero again.
+AP_EXPORT long long ap_gemm_tc_persistent_scratch_bytes(void) {
+    return (long long)PERSIST_MAX_CTAS * 4 + (long long)PERSIST_MAX_CTAS * PersistCfg<256>::kPartialFloats * 4;
 }
 
 // The persistent kernel (see gemm_tc_persistent_kernel), for products with more than 64 rows.
 //   pairs == 0: out[M, N] = a * w^T for w [N, K].
 //   pairs != 0: w [N, K] has gate and up rows alternating; out[M, N/2] = silu(gate) * up.
+//   scratch: null, or ap_gemm_tc_persistent_scratch_bytes() bytes (see there).
 AP_EXPORT int ap_gemm_tc_persistent(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K,
-                                    long long lda, long long ldw, long long ldc, int pairs, cudaStream_t stream) {
+                                    long long lda, long long ldw, long long ldc, int pairs, void* scratch,
+                                    long long scratch_bytes, cudaStream_t stream) {
     AP_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     if (M == 0) return AP_OK;
     AP_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
@@ -952,9 +1091,10 @@ AP_EXPORT int ap_gemm_tc_persistent(const void* a, const void* w, void* out, int
     CUtensorMap mw, ma;
     AP_REQUIRE(make_map(&mw, w, N, K, ldw, TILE_W), "gemm_tc: cannot encode the weight's tensor map");
     AP_REQUIRE(make_map(&ma, a, M, K, lda, bn), "gemm_tc: cannot encode the activations' tensor map");
-#define GO(BN, PR)                                                                                 \
-    return out_dtype == AP_F32 ? launch_persistent<BN, float, PR>(mw, ma, out, M, N, K, ldc, stream) \
-                               : launch_persistent<BN, bf16, PR>(mw, ma, out, M, N, K, ldc, stream)
+#define GO(BN, PR)                                                                                                  \
+    return out_dtype == AP_F32                                                                                      \
+               ? launch_persistent<BN, float, PR>(mw, ma, out, M, N, K, ldc, scratch, scratch_bytes, stream)        \
+               : launch_persistent<BN, bf16, PR>(mw, ma, out, M, N, K, ldc, scratch, scratch_bytes, stream)
     if (pairs) {
         if (bn == 128) GO(128, true);
         GO(256, true);

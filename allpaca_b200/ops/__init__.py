@@ -233,9 +233,28 @@ def gemm_tc_dual(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bo
          M, N, K, K, K, N, 1 if swiglu else 0, stream_handle())
 
 
-def gemm_tc_persistent(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pairs: bool = False) -> None:
+_persistent_scratch = {}
+
+
+def _scratch_for_persistent(device: torch.device) -> torch.Tensor:
+    """The buffer through which CTAs of the persistent product that share a tile hand partial
+    sums to one another: one per (device, stream), zero when made; the kernel leaves its
+    flags zero again."""
+    key = (device.index, stream_handle())
+    buf = _persistent_scratch.get(key)
+    if buf is None:
+        nbytes = int(core().ap_gemm_tc_persistent_scratch_bytes())
+        buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        _persistent_scratch[key] = buf
+    return buf
+
+
+def gemm_tc_persistent(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pairs: bool = False,
+                       share_tiles: bool = True) -> None:
     """The persistent tensor-core product for more than 64 rows: one CTA per SM walks the
-    output tiles, and a tile is written out while the next one is being computed.
+    output tiles, and a tile is written out while the next one is being computed.  With
+    ``share_tiles`` a product of fewer tiles than half the SMs splits every tile's K among
+    several CTAs.
 
     ``pairs`` False: ``out[M,N] = a[M,K] @ w[N,K]^T``.  True: the rows of ``w [N,K]`` alternate
     gate, up, gate, up ... and ``out[M,N/2] = silu(gate) * up``.
@@ -249,8 +268,10 @@ def gemm_tc_persistent(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pair
     if w.shape[1] != K or tuple(out.shape) != (M, n_out) or (pairs and N % 2):
         raise KernelError(f"gemm_tc_persistent: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, "
                           f"out {tuple(out.shape)}")
+    scratch = _scratch_for_persistent(a.device) if share_tiles else None
     call(core(), "ap_gemm_tc_persistent", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
-         M, N, K, K, K, n_out, 1 if pairs else 0, stream_handle())
+         M, N, K, K, K, n_out, 1 if pairs else 0, scratch.data_ptr() if scratch is not None else 0,
+         scratch.numel() if scratch is not None else 0, stream_handle())
 
 
 def _decode_attention(lib, q, out, cache_layer, block_table, positions, rows, num_heads, num_kv_heads, head_dim, P,

@@ -36,7 +36,7 @@ _OPTIONAL_CORE_SIGNATURES = {
     # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, pairs, stream)
     "ap_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _L, _I, _I, _P],
     "ap_gemm_tc_dual": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P],
-    "ap_gemm_tc_persistent": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P],
+    "ap_gemm_tc_persistent": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P, _L, _P],
     "ap_gemm_tc_plan": [_I, _I, _I],
     "ap_gemm_tc_prefers_dual": [_I, _I, _I],
     "ap_gemm_tc_prefers_persistent": [_I, _I, _I],
@@ -65,6 +65,9 @@ def _declare(lib: ctypes.CDLL, signatures, optional=False) -> None:
         fn.restype = c_int
     lib.ap_last_error.restype = c_char_p
     lib.ap_last_error.argtypes = []
+    if hasattr(lib, "ap_gemm_tc_persistent_scratch_bytes"):
+        lib.ap_gemm_tc_persistent_scratch_bytes.restype = c_longlong
+        lib.ap_gemm_tc_persistent_scratch_bytes.argtypes = []
 
 
 def _require_cuda() -> None:

@@ -18,12 +18,13 @@ SHAPES = [(65, 128, 64), (128, 384, 256), (200, 1000, 520), (257, 4096, 1024), (
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_plain_product(ops, M, N, K, out_dtype):
+@pytest.mark.parametrize("share", [True, False])
+def test_plain_product(ops, M, N, K, out_dtype, share):
     g = torch.Generator().manual_seed(M + N + K)
     a = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
     w = (torch.randn(N, K, generator=g) * 0.5).bfloat16()
     out = torch.full((M, N), float("nan"), device="cuda", dtype=out_dtype)
-    ops.gemm_tc_persistent(a.cuda(), w.cuda(), out)
+    ops.gemm_tc_persistent(a.cuda(), w.cuda(), out, share_tiles=share)
     ops.check_kernel_status()
     ref = a.double() @ w.double().T
     tol = 1e-5 if out_dtype == torch.float32 else 5e-3
@@ -45,6 +46,29 @@ def test_gated_activation_over_alternating_rows(ops, M, I, K):
     ref = gv / (1.0 + torch.exp(-gv)) * uv
     assert torch.isfinite(out).all()
     assert float((out.cpu().double() - ref).abs().max() / ref.abs().max()) < 1e-2
+
+
+def test_shared_tiles_repeat_bit_for_bit_and_agree_with_whole_tiles(ops):
+    """Few tiles, much K: every tile is shared by several CTAs that hand partial sums over.
+    The flags must be left ready for the next product, the sums must not depend on timing, and
+    the result must agree with whole tiles."""
+    g = torch.Generator().manual_seed(3)
+    for M, N, K, pairs in ((300, 2176, 4160, False), (576, 2048, 8192, False), (130, 512, 2048, True)):
+        a = (torch.randn(M, K, generator=g) * 0.5).bfloat16().cuda()
+        w = (torch.randn(N, K, generator=g) * 0.5).bfloat16().cuda()
+        n_out = N // 2 if pairs else N
+        outs = []
+        for _ in range(3):
+            out = torch.full((M, n_out), float("nan"), device="cuda", dtype=torch.float32)
+            ops.gemm_tc_persistent(a, w, out, pairs=pairs)
+            outs.append(out)
+        ops.check_kernel_status()
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+        whole = torch.empty_like(outs[0])
+        ops.gemm_tc_persistent(a, w, whole, pairs=pairs, share_tiles=False)
+        scale = float(whole.abs().max())
+        assert torch.isfinite(outs[0]).all()
+        assert float((outs[0] - whole).abs().max()) / scale < (2e-2 if pairs else 1e-5)
 
 
 def test_a_view_with_a_leading_dimension_is_refused_or_right(ops):
