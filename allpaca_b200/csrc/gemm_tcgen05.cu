@@ -775,7 +775,7 @@ template <int BN, typename TO, bool PAIRS>
 __global__ void __launch_bounds__(192)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                           TO* __restrict__ out, int M, int N, int K, long long ldc, int tiles_m, int tiles_total,
-                          int split, int* __restrict__ flags, float* __restrict__ partials) {
+                          int bn, int split, int* __restrict__ flags, float* __restrict__ partials) {
     using Cfg = PersistCfg<BN>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -793,6 +793,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
     if (*(volatile int*)&g_tc_status != 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nkb = (K + TILE_K - 1) / TILE_K;
+    // A tile holds `bn` <= BN tokens (a multiple of 16 chosen by the host so that the tiles of
+    // a product are evenly filled); shared memory and tensor memory are laid out for BN.
+    const uint32_t stage_bytes = (uint32_t)(A_TILE_BYTES + bn * TILE_K * 2);
     const int G = gridDim.x, g = blockIdx.x;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -821,7 +824,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
             long long idx = 0, issued = 0;
             bool first = true;
             while (!*abort_flag && work.next(sg)) {
-                const int n0 = (sg.tile / tiles_m) * TILE_W, m0 = (sg.tile % tiles_m) * BN;
+                const int n0 = (sg.tile / tiles_m) * TILE_W, m0 = (sg.tile % tiles_m) * bn;
                 int kb = sg.kb0;
                 if (first) {
                     // the weight does not depend on earlier kernels: fill the ring with this
@@ -830,7 +833,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
                     first = false;
                     const int pre = min(STAGES, sg.kb1 - sg.kb0);
                     for (int i = 0; i < pre; ++i) {
-                        tc::mbar_expect_tx(&full[i], Cfg::kStageBytes);
+                        tc::mbar_expect_tx(&full[i], stage_bytes);
                         tc::tma_load_2d(w_tiles + i * A_TILE_BYTES, &tmap_w, (kb + i) * TILE_K, n0, &full[i]);
                     }
                     ap_pdl_wait();
@@ -848,7 +851,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
                         atomicExch(&g_tc_status, TC_ERR_EMPTY_WAIT);
                         break;
                     }
-                    tc::mbar_expect_tx(&full[s], Cfg::kStageBytes);
+                    tc::mbar_expect_tx(&full[s], stage_bytes);
                     tc::tma_load_2d(w_tiles + s * A_TILE_BYTES, &tmap_w, kb * TILE_K, n0, &full[s]);
                     tc::tma_load_2d(a_tiles + s * Cfg::kBBytes, &tmap_a, kb * TILE_K, m0, &full[s]);
                     issued = idx + 1;
@@ -862,7 +865,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = tc::instr_desc_bf16_f32(TILE_W, BN);
+            const uint32_t idesc = tc::instr_desc_bf16_f32(TILE_W, bn);
             bool ok = true;
             long long idx = 0;
             WorkList work(tiles_total, nkb, G, g, split);
@@ -909,7 +912,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
         WorkList work(tiles_total, nkb, G, g, split);
         Segment sg;
         for (int j = 0; ok && work.next(sg); ++j) {
-            const int n0 = (sg.tile / tiles_m) * TILE_W, m0 = (sg.tile % tiles_m) * BN;
+            const int n0 = (sg.tile / tiles_m) * TILE_W, m0 = (sg.tile % tiles_m) * bn;
             const int b = j & 1;
             // tcgen05.ld is warp-wide: the whole warp goes on, or none of it
             if (!__all_sync(0xffffffffu, tc::mbar_wait(&acc_full[b], (uint32_t)((j >> 1) & 1)))) {
@@ -923,7 +926,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
             tc::fence_after_sync();
             const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN);
             const int n = n0 + row;
-            const int cols = min(BN, M - m0);           // token rows of this tile that exist
+            const int cols = min(bn, M - m0);           // token rows of this tile that exist
             if (sg.kb0 > 0) {
                 // not the tile's first block: hand the partial sums over, [token][weight row]
                 float* mine = partials + (size_t)g * Cfg::kPartialFloats;
@@ -991,15 +994,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
                         // activation is a kernel of its own
                         const float gt = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? other : v[jj])));
                         const float up = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? v[16 + jj] : other)));
-                        const int m = m0 + c + (odd ? 16 : 0) + jj;
-                        if (m < M && n < N)
+                        const int col = c + (odd ? 16 : 0) + jj;
+                        if (col < cols && n < N)
                             dst[(size_t)jj * ldc] = ap_from_float<TO>(__fdividef(gt, 1.0f + __expf(-gt)) * up);
                     }
                 } else if (n < N) {
 #pragma unroll
                     for (int jj = 0; jj < 32; ++jj) {
-                        const int m = m0 + c + jj;
-                        if (m < M) out[(size_t)m * ldc + n] = ap_from_float<TO>(__uint_as_float(v[jj]));
+                        if (c + jj < cols) out[(size_t)(m0 + c + jj) * ldc + n] = ap_from_float<TO>(__uint_as_float(v[jj]));
                     }
                 }
             }
@@ -1018,7 +1020,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
 
 template <int BN, typename TO, bool PAIRS>
 static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K,
-                             long long ldc, void* scratch, long long scratch_bytes, cudaStream_t stream) {
+                             long long ldc, int bn, void* scratch, long long scratch_bytes, cudaStream_t stream) {
     using Cfg = PersistCfg<BN>;
     auto kern = gemm_tc_persistent_kernel<BN, TO, PAIRS>;
     static bool configured = false;
@@ -1033,7 +1035,7 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& ma, void*
                    "gemm_tc: cannot read the number of SMs");
         configured = true;
     }
-    const int tiles_m = (M + BN - 1) / BN;
+    const int tiles_m = (M + bn - 1) / bn;
     const long long tiles = (long long)tiles_m * ((N + TILE_W - 1) / TILE_W);
     AP_REQUIRE(tiles < (1LL << 30), "gemm_tc: too many output tiles");
     // Fewer tiles than half the SMs, a scratch buffer at hand and enough K to share: `split`
@@ -1060,8 +1062,8 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& ma, void*
     }
     dim3 grid((unsigned)ctas, 1, 1);
     AP_CHECK_PDL_LAUNCH("gemm_tc_persistent", ap_launch_pdl(kern, grid, dim3(192), (size_t)Cfg::kSmemBytes, stream, mw,
-                                                            ma, (TO*)out, M, N, K, ldc, tiles_m, (int)tiles, split,
-                                                            flags, partials));
+                                                            ma, (TO*)out, M, N, K, ldc, tiles_m, (int)tiles, bn,
+                                                            split, flags, partials));
     return AP_OK;
 }
 
@@ -1087,19 +1089,23 @@ AP_EXPORT int ap_gemm_tc_persistent(const void* a, const void* w, void* out, int
     AP_REQUIRE(!pairs || N % 2 == 0, "gemm_tc: gate and up rows alternate, so the weight has an even number of rows");
     AP_REQUIRE(lda >= K && ldw >= K && ldc >= (pairs ? N / 2 : N), "gemm_tc: a leading dimension is below its row length");
     AP_REQUIRE(out_dtype == AP_F32 || out_dtype == AP_BF16, "gemm_tc: unknown output dtype %d", out_dtype);
-    const int bn = M <= 128 ? 128 : 256;
+    // token tiles: as many as tiles of the full width (128 for up to 128 rows, else 256) would
+    // take, but evenly filled: their width is the smallest multiple of 16 that covers the rows
+    const int cap = M <= 128 ? 128 : 256;
+    const int tiles_m = (M + cap - 1) / cap;
+    const int bn = ((M + tiles_m - 1) / tiles_m + 15) / 16 * 16;
     CUtensorMap mw, ma;
     AP_REQUIRE(make_map(&mw, w, N, K, ldw, TILE_W), "gemm_tc: cannot encode the weight's tensor map");
     AP_REQUIRE(make_map(&ma, a, M, K, lda, bn), "gemm_tc: cannot encode the activations' tensor map");
 #define GO(BN, PR)                                                                                                  \
     return out_dtype == AP_F32                                                                                      \
-               ? launch_persistent<BN, float, PR>(mw, ma, out, M, N, K, ldc, scratch, scratch_bytes, stream)        \
-               : launch_persistent<BN, bf16, PR>(mw, ma, out, M, N, K, ldc, scratch, scratch_bytes, stream)
+               ? launch_persistent<BN, float, PR>(mw, ma, out, M, N, K, ldc, bn, scratch, scratch_bytes, stream)    \
+               : launch_persistent<BN, bf16, PR>(mw, ma, out, M, N, K, ldc, bn, scratch, scratch_bytes, stream)
     if (pairs) {
-        if (bn == 128) GO(128, true);
+        if (cap == 128) GO(128, true);
         GO(256, true);
     }
-    if (bn == 128) GO(128, false);
+    if (cap == 128) GO(128, false);
     GO(256, false);
 #undef GO
 }
