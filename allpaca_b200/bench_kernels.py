@@ -54,7 +54,7 @@ def bench_gemm(args) -> dict:
     S = args.splits or ops.gemm_tc_splits(M, N, K)
     odt = torch.float32 if args.out == "float32" else torch.bfloat16
     kernel = "gemm_tc"
-    if M > 64 and not args.dual and not args.single:
+    if M > 64 and not args.dual and not args.single and (S == 1 or args.whole_tiles):
         # the persistent kernel; with --swiglu the rows of w alternate gate and up
         kernel = "gemm_tc_persistent"
         out = torch.empty(M, N // 2 if args.swiglu else N, device="cuda", dtype=odt)
@@ -68,7 +68,7 @@ def bench_gemm(args) -> dict:
         fn = lambda i: ops.gemm_tc_dual(a, ws[i % copies], out, swiglu=args.swiglu)   # noqa: E731
         S = 1
     elif args.swiglu:
-        # few rows: the gated activation in the epilogue of the (cluster) kernel
+        # up to 256 rows: the gated activation in the epilogue of the (cluster) kernel
         out = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
         fn = lambda i: ops.gemm_tc(a, ws[i % copies], out, S, reduce=S > 1, pairs=True)      # noqa: E731
     elif args.partials and S > 1:

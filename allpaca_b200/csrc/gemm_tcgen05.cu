@@ -41,7 +41,10 @@ template <int BN, bool CLUSTER = false> struct TileCfg {
     // cluster reduction buffer: [slices][BN][rows per slice], at most 136 rows in all
     static constexpr int kReduceBytes = (TILE_W + 8) * BN * 4;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + kBarrierBytes;
-    static constexpr int kSmemBytesCluster = kSmemBytes + kReduceBytes;
+    // 128 tokens and more: the reduction buffer lies over the stages, which are idle by then
+    static constexpr bool kReduceOverStages = BN >= 128;
+    static constexpr int kSmemBytesCluster = kSmemBytes + (kReduceOverStages ? 0 : kReduceBytes);
+    static_assert(!kReduceOverStages || kReduceBytes <= kStages * kStageBytes, "the reduction buffer must fit the stages");
 };
 
 // CLUSTER: the gridDim.z K-slices of one output tile form a thread-block cluster and add
@@ -69,7 +72,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     uint64_t* accum = empty + STAGES;
     uint32_t* tmem_slot = (uint32_t*)(accum + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    float* reduce = (float*)(smem + STAGES * Cfg::kStageBytes + Cfg::kBarrierBytes);
+    // CLUSTER with 128 tokens or more: the buffer the slices' partial sums are gathered in lies
+    // over the operand stages, and a cluster barrier makes sure every CTA is done with them
+    constexpr bool REUSE = CLUSTER && Cfg::kReduceOverStages;
+    float* reduce = REUSE ? (float*)smem : (float*)(smem + STAGES * Cfg::kStageBytes + Cfg::kBarrierBytes);
+    bool have_acc = false;          // epilogue threads: the accumulator is complete and may be read
 
     // once a wait has expired anywhere, later CTAs do nothing: the product is void anyway.
     // (In a cluster every CTA still walks to the cluster barrier, or its peers would wait.)
@@ -189,7 +196,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             }
             tc::fence_after_sync();
         }
-        if (CLUSTER) {
+        have_acc = have;
+        if (REUSE) {
+            // the hand-over follows below, once no CTA of the cluster reads its stages any more
+        } else if (CLUSTER) {
             // hand this row's partial sums to the CTA that finishes its band of rows
             const int S = gridDim.z;
             const int band = (TILE_W + S - 1) / S;
@@ -242,6 +252,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             for (int c = 0; c < BN; ++c) {
                 const int m = m0 + c;
                 if (m < M) out[(size_t)m * ldc + (PAIRS ? n >> 1 : n)] = ap_from_float<TO>(0.f);
+            }
+        }
+    }
+    if (REUSE) {
+        // The epilogue warps come here after the last MMA of this CTA has finished, that is,
+        // after every load into its stages has been consumed: once all threads of the cluster
+        // have arrived, every CTA's stages are free to receive partial sums.
+        __syncwarp();
+        tc::cluster_arrive();
+        tc::cluster_wait();
+        if (warp >= 2) {
+            const int q = warp & 3;
+            const int row = q * 32 + lane;
+            const int S = gridDim.z;
+            const int band = (TILE_W + S - 1) / S;
+            const int dest = row / band, slot = row - dest * band;
+            const uint32_t base = tc::map_to_rank(tc::smem_addr(reduce), (uint32_t)dest) +
+                                  (uint32_t)((blockIdx.z * BN) * band + slot) * 4u;
+            const int mcols = min(BN, M - m0);
+#pragma unroll 1
+            for (int c = 0; c < mcols; c += 16) {
+                uint32_t v[16];
+                if (have_acc) {
+                    tc::tmem_ld_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+                    tc::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0u;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    tc::st_cluster_f32(base + (uint32_t)((c + j) * band) * 4u, __uint_as_float(v[j]));
             }
         }
     }
@@ -503,15 +545,20 @@ AP_EXPORT int ap_gemm_tc_plan(int M, int N, int K) {
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     const int bn = pick_bn(M);
     const long long tiles = (long long)((N + TILE_W - 1) / TILE_W) * ((M + bn - 1) / bn);
-    if (M > 64 || tiles >= 148) return 1;
-    // as many slices as keep the whole grid resident at once (two CTAs per SM, a little
-    // slack so that the clusters find room side by side)
-    int ns = (int)(288 / tiles);
-    ns = min(ns, kb_total / 4);
-    ns = min(ns, max(1, K / (16 * M)));    // more rows: fewer, longer slices
+    if (M > 256 || tiles >= 148) return 1;
+    // as many slices as keep the whole grid resident at once (two CTAs per SM, or one from 65
+    // rows on, whose tiles fill an SM's shared memory; a little slack so that the clusters
+    // find room side by side)
+    int ns = (int)((M > 64 ? 148 : 288) / tiles);
+    if (M > 64) ns = min(ns, kb_total / 8);
+    else {
+        ns = min(ns, kb_total / 4);
+        ns = min(ns, max(1, K / (16 * M)));    // more rows: fewer, longer slices
+    }
     ns = min(ns, 8);                       // one thread-block cluster adds the slices
     if (ns < 1) ns = 1;
     while (ns & (ns - 1)) ns &= ns - 1;    // clusters of 2, 4 or 8 CTAs find room side by side; odd sizes do not
+    if (M > 64 && ns < 4) return 1;        // two slices of a wide tile cost more to add than they save
     const int per = (kb_total + ns - 1) / ns;
     return (kb_total + per - 1) / per;
 }
@@ -585,8 +632,8 @@ AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype,
     AP_REQUIRE(lda >= K && ldw >= K && ldc >= (pairs ? N / 2 : N), "gemm_tc: a leading dimension is below its row length");
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     AP_REQUIRE(nsplit >= 1 && nsplit <= kb_total && nsplit <= 65535, "gemm_tc: cannot split K=%d into %d", K, nsplit);
-    AP_REQUIRE(!pairs || (N % 2 == 0 && M <= 64 && out_dtype == AP_BF16 && (nsplit == 1 || reduce)),
-               "gemm_tc: the gated epilogue takes an even number of weight rows, at most 64 rows of a, "
+    AP_REQUIRE(!pairs || (N % 2 == 0 && M <= 256 && out_dtype == AP_BF16 && (nsplit == 1 || reduce)),
+               "gemm_tc: the gated epilogue takes an even number of weight rows, at most 256 rows of a, "
                "bfloat16 output and finished sums");
     AP_REQUIRE((long long)(nsplit - 1) * ((kb_total + nsplit - 1) / nsplit) < kb_total,
                "gemm_tc: %d slices leave an empty one for K=%d", nsplit, K);
@@ -594,8 +641,8 @@ AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype,
     const int bn = pick_bn(M);
     AP_REQUIRE((N + TILE_W - 1) / TILE_W <= 65535, "gemm_tc: %d output features exceed the grid", N);
     const bool cluster = reduce != 0 && nsplit > 1;
-    AP_REQUIRE(!cluster || (nsplit <= AP_MAX_CLUSTER && bn <= 64),
-               "gemm_tc: slices are added in a cluster only for up to %d slices and 64 rows (got %d, %d)",
+    AP_REQUIRE(!cluster || (nsplit <= AP_MAX_CLUSTER && M <= 256),
+               "gemm_tc: slices are added in a cluster only for up to %d slices and 256 rows (got %d, %d)",
                AP_MAX_CLUSTER, nsplit, M);
     AP_REQUIRE(cluster || nsplit == 1 || out_dtype == AP_F32, "gemm_tc: partial sums must be 32-bit");
     CUtensorMap mw, ma;
@@ -610,14 +657,18 @@ AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype,
         switch (bn) {
             case 16: GOP(16, true);
             case 32: GOP(32, true);
-            default: GOP(64, true);
+            case 64: GOP(64, true);
+            case 128: GOP(128, true);
+            default: GOP(256, true);
         }
     }
     if (pairs) {
         switch (bn) {
             case 16: GOP(16, false);
             case 32: GOP(32, false);
-            default: GOP(64, false);
+            case 64: GOP(64, false);
+            case 128: GOP(128, false);
+            default: GOP(256, false);
         }
     }
 #undef GOP
@@ -625,7 +676,9 @@ AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype,
         switch (bn) {
             case 16: GO(16, true);
             case 32: GO(32, true);
-            default: GO(64, true);
+            case 64: GO(64, true);
+            case 128: GO(128, true);
+            default: GO(256, true);
         }
     }
     switch (bn) {

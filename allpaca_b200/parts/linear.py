@@ -58,7 +58,10 @@ class Linear:
         else:
             out = ws.get(buffer_name, (T, N), torch.float32 if kind == "float32" else self.env.dtype)
             target = out
-        if tc and T > 64 and ops.gemm_tc_prefers_persistent(T, N, self.in_features):
+        if tc and T > 64 and nsplit > 1:
+            # 65 to 256 rows against few weight tiles: K slices in a cluster, as for decoding
+            ops.gemm_tc(a, self.weight, target, nsplit, reduce=True)
+        elif tc and T > 64 and ops.gemm_tc_prefers_persistent(T, N, self.in_features):
             ops.gemm_tc_persistent(a, self.weight, target)
         elif tc and nsplit == 1 and ops.gemm_tc_prefers_dual(T, N, self.in_features):
             ops.gemm_tc_dual(a, self.weight, target)
@@ -76,9 +79,9 @@ class Linear:
         if not self.uses_tensor_cores() or self.out_features % 2:
             return None
         out = self.env.workspace.get(buffer_name, (T, self.out_features // 2), self.env.dtype)
-        if T > 64:
+        nsplit = ops.gemm_tc_splits(T, self.out_features, self.in_features)
+        if T > 64 and nsplit == 1:
             ops.gemm_tc_persistent(a, self.weight, out, pairs=True)
         else:
-            nsplit = ops.gemm_tc_splits(T, self.out_features, self.in_features)
             ops.gemm_tc(a, self.weight, out, nsplit, reduce=nsplit > 1, pairs=True)
         return out

@@ -31,12 +31,15 @@ def test_cluster_reduction(M, N, K, S, odtype):
 
 def test_plan_stays_within_a_cluster():
     from allpaca_b200 import ops
-    for M in (1, 8, 16, 33, 64):
+    for M in (1, 8, 16, 33, 64, 65, 128, 200, 256):
         for N, K in ((4096, 4096), (6144, 4096), (28672, 4096), (4096, 14336), (128256, 4096), (96, 64)):
             s = ops.gemm_tc_splits(M, N, K)
             kb = -(-K // 64)
             assert 1 <= s <= 8 and (s - 1) * (-(-kb // s)) < kb
-    assert ops.gemm_tc_splits(65, 4096, 4096) == 1 and ops.gemm_tc_splits(2048, 4096, 4096) == 1
+            assert M <= 64 or s != 2          # from 65 rows on two slices do not pay: four or more, or none
+    # 65 to 256 rows against few weight tiles are still split; more rows never
+    assert ops.gemm_tc_splits(65, 4096, 4096) == 4 and ops.gemm_tc_splits(257, 4096, 4096) == 1
+    assert ops.gemm_tc_splits(2048, 4096, 4096) == 1 and ops.gemm_tc_splits(200, 28672, 4096) == 1
 
 
 def test_cluster_reduction_refuses_too_many_slices():
@@ -61,6 +64,45 @@ def test_gated_epilogue_over_alternating_rows(M, I, K, nsplit):
     w = torch.stack([gate, up], dim=1).reshape(2 * I, K).contiguous()
     out = torch.full((M, I), float("nan"), device="cuda", dtype=torch.bfloat16)
     ops.gemm_tc(a.cuda(), w.cuda(), out, nsplit, reduce=nsplit > 1, pairs=True)
+    ops.check_kernel_status()
+    gv = (a.double() @ gate.double().T).float().bfloat16().double()
+    uv = (a.double() @ up.double().T).float().bfloat16().double()
+    ref = gv / (1.0 + torch.exp(-gv)) * uv
+    assert torch.isfinite(out).all()
+    assert float((out.cpu().double() - ref).abs().max() / ref.abs().max()) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K,nsplit", [(65, 128, 512, 2), (128, 384, 1024, 4), (188, 520, 2048, 8), (256, 256, 4096, 4),
+                                          (200, 1000, 1032, 2), (130, 4096, 4096, 4)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_cluster_reduction_with_up_to_256_rows(M, N, K, nsplit, out_dtype):
+    """65 to 256 rows: the buffer the slices are gathered in lies over the operand stages."""
+    from allpaca_b200 import ops
+    g = torch.Generator().manual_seed(M + N + K)
+    a = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.5).bfloat16()
+    outs = []
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), device="cuda", dtype=out_dtype)
+        ops.gemm_tc(a.cuda(), w.cuda(), out, nsplit, reduce=True)
+        outs.append(out)
+    ops.check_kernel_status()
+    assert torch.equal(outs[0], outs[1])
+    ref = a.double() @ w.double().T
+    tol = 1e-5 if out_dtype == torch.float32 else 5e-3
+    assert float((outs[0].cpu().double() - ref).abs().max() / ref.abs().max()) < tol
+
+
+@pytest.mark.parametrize("M,I,K,nsplit", [(100, 200, 512, 2), (256, 1409, 1024, 4), (129, 64, 2048, 8)])
+def test_gated_epilogue_with_up_to_256_rows(M, I, K, nsplit):
+    from allpaca_b200 import ops
+    g = torch.Generator().manual_seed(M + I + K)
+    a = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    gate = (torch.randn(I, K, generator=g) * 0.3).bfloat16()
+    up = (torch.randn(I, K, generator=g) * 0.3).bfloat16()
+    w = torch.stack([gate, up], dim=1).reshape(2 * I, K).contiguous()
+    out = torch.full((M, I), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_tc(a.cuda(), w.cuda(), out, nsplit, reduce=True, pairs=True)
     ops.check_kernel_status()
     gv = (a.double() @ gate.double().T).float().bfloat16().double()
     uv = (a.double() @ up.double().T).float().bfloat16().double()
