@@ -143,6 +143,11 @@ class LlamaConfig:
             if d.get(moe_key):
                 raise ConfigError(
                     f"{moe_key} is set: mixture-of-experts checkpoints are not a dense Llama")
+        for bias_key in ("attention_bias", "mlp_bias"):
+            if d.get(bias_key):
+                raise ConfigError(
+                    f"{bias_key} is set: projections with biases are not part of this architecture "
+                    f"(the reference's Llama path has none)")
         scaling = d.get("rope_scaling")
         if scaling is not None:
             kind = scaling.get("rope_type", scaling.get("type"))

@@ -44,11 +44,19 @@ def test_head_dim_may_differ_from_hidden_over_heads():
     ({"vocab_size": 0}, "positive"),
     ({"vocab_size": 3.5}, "integer"),
     ({"rms_norm_eps": 0}, "rms_norm_eps"),
+    ({"attention_bias": True}, "attention_bias"),
+    ({"mlp_bias": True}, "mlp_bias"),
 ])
 def test_invalid_configs_are_named(bad, word):
     with pytest.raises(ConfigError) as e:
         LlamaConfig.from_dict(bad)
     assert word in str(e.value)
+
+
+def test_options_that_change_nothing_are_accepted():
+    cfg = LlamaConfig.from_dict({"attention_bias": False, "mlp_bias": False, "rope_scaling": {"rope_type": "default"},
+                                 "attention_dropout": 0.0, "bos_token_id": 1, "use_cache": True})
+    assert cfg.rope_scaling is None
 
 
 def test_registry_resolves_by_architecture_and_model_type(tmp_path):
