@@ -61,7 +61,9 @@ def load_checkpoint(model, path: str, engine_dtype: torch.dtype, device: torch.d
     """Read every tensor the model names from a model folder and hand them to the parts."""
     ckpt = Checkpoint(path)
     targets = model.weight_targets()
-    check_names(targets, {n: ckpt.info(n)[1] for n in ckpt.names()})
+    # buffers some exporters save beside the weights; they are recomputed from the configuration
+    derived = (".rotary_emb.inv_freq",)
+    check_names(targets, {n: ckpt.info(n)[1] for n in ckpt.names() if not n.endswith(derived)})
     tensors: Dict[str, torch.Tensor] = {}
     for name in targets:
         if name not in ckpt:

@@ -181,3 +181,17 @@ def test_command_line_generate(tmp_path):
                           "--seed", "1", "--prompt-ids", "1 2 3", "--max-tokens", "4"],
                          capture_output=True, text=True, timeout=600)
     assert syn.returncode == 0 and "[length]" in syn.stdout, syn.stderr[-3000:]
+
+
+def test_checkpoint_with_saved_rotary_buffers_loads(tmp_path):
+    """Some exporters save ``rotary_emb.inv_freq`` beside the weights; it is derived from the
+    configuration, so it is neither needed nor an error."""
+    from safetensors.torch import load_file, save_file
+    from allpaca_b200 import LLM, SamplingParams
+    config, model, prompts, w = make(tmp_path, "A")
+    path = os.path.join(model, "model.safetensors")
+    tensors = load_file(path)
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    save_file(tensors, path)
+    out = LLM(model, dtype="float32").generate(prompts[:1], SamplingParams.greedy_params(max_tokens=3))
+    assert len(out[0].token_ids) == 3
