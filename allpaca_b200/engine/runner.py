@@ -107,14 +107,19 @@ class ModelRunner:
         return all(reserve[g] <= self.cache.num_free_pages(g) for g in range(len(reserve)))
 
     # ---- the step -------------------------------------------------------
-    def step(self, entries: Sequence[BatchEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[BatchEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run the rows of ``entries`` as one batch; returns ``[wanted, vocab]`` float32 logits
         in the order of the entries and of their ``want`` lists.  The tensor is a view of a
-        buffer that the next step overwrites."""
+        buffer that the next step overwrites.
+
+        ``device_tokens`` (int32 on the device, one per row): the step's token ids are taken
+        from there instead of from the entries, whose tokens are then placeholders.  With it a
+        caller that chooses the next tokens on the GPU can launch the next step without
+        bringing them to the host first."""
         if self._graphable(entries):
-            logits = self._graph_step(entries)
+            logits = self._graph_step(entries, device_tokens)
         else:
-            batch = self.prepare(entries)
+            batch = self.prepare(entries, device_tokens=device_tokens)
             logits = self.model.forward(batch)
         if self.cache.has_windows():
             for en in entries:
@@ -128,7 +133,7 @@ class ModelRunner:
         return (self.engine.use_cuda_graphs and 0 < len(entries) <= self.engine.max_num_seqs
                 and all(len(en.tokens) == 1 and list(en.want) == [0] for en in entries))
 
-    def _graph_step(self, entries: Sequence[BatchEntry]) -> torch.Tensor:
+    def _graph_step(self, entries: Sequence[BatchEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Replay (or first capture) the graph of a decode step with ``len(entries)`` rows.
 
         The graph's kernels read their metadata from buffers at fixed addresses with a
@@ -147,7 +152,7 @@ class ModelRunner:
         gs = self._graphs.get((B, bound))
         if gs is None:
             gs = self._graphs[(B, bound)] = _DecodeGraph(self, B)
-        batch = self.prepare(entries, staging=gs, widths=gs.widths)
+        batch = self.prepare(entries, staging=gs, widths=gs.widths, device_tokens=device_tokens)
         batch.max_context_len = bound
         if gs.graph is not None and gs.generation == self.workspace.generation:
             gs.graph.replay()
@@ -171,7 +176,8 @@ class ModelRunner:
         gs.generation = self.workspace.generation
         return logits
 
-    def prepare(self, entries: Sequence[BatchEntry], staging=None, widths=None) -> StepBatch:
+    def prepare(self, entries: Sequence[BatchEntry], staging=None, widths=None,
+                device_tokens: Optional[torch.Tensor] = None) -> StepBatch:
         """Check the batch, allocate its pages and upload its metadata (into ``staging``'s
         fixed buffers with the given block-table widths, when given).
 
@@ -196,6 +202,10 @@ class ModelRunner:
         total = int(layout.total)
         dev[:total].copy_(host_tensor[:total], non_blocking=True)
         copied.record()
+        if device_tokens is not None:
+            if device_tokens.dtype != torch.int32 or device_tokens.numel() < T or not device_tokens.is_cuda:
+                raise ValueError("device_tokens must be int32 on the device, one per row of the step")
+            dev[layout.off_tokens:layout.off_tokens + T].copy_(device_tokens.reshape(-1)[:T], non_blocking=True)
 
         def view(off, n):
             return dev[off:off + n]

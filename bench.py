@@ -8,7 +8,9 @@ bfloat16 weights drawn on the device, 8 requests decoding at a context of 4096 t
 A step is one decode step of the whole batch.
 
 * ``value``   decoded tokens per second, timed on the device with CUDA events around K steps
-              of the step function with next-token choice on the GPU;
+              of the step function with next-token choice on the GPU; the chosen tokens reach
+              the next step through device memory (``ModelRunner.step(..., device_tokens=)``),
+              the step's positions and tables are still built on the host and uploaded;
 * ``e2e``     the same through ``LLM.step()`` (scheduler, pinned-memory upload of the step's
               tokens and tables, read-back of the chosen tokens), by the host clock;
 * ``prefill`` one prompt of 2048 tokens in one step: tokens/s, ms and the fraction of the
@@ -218,15 +220,16 @@ def main() -> int:
         tokens = [r.all_token_ids[-1] for r in reqs]
         for r in reqs:                        # the scheduler no longer drives these requests
             llm.scheduler.abort(r.request_id)
-        out = torch.empty(batch, dtype=torch.int32, device=device)
+        # the next tokens are chosen on the GPU and handed to the next step on the GPU: no step
+        # waits for the host (the end-to-end figure above is the one with host tokens in and out)
+        out = torch.tensor(tokens, dtype=torch.int32).to(device)
+        entries = [BatchEntry(r.request_id, [0], [0]) for r in reqs]
 
-        def one_step(toks):
-            entries = [BatchEntry(r.request_id, [t_], [0]) for r, t_ in zip(reqs, toks)]
-            logits = runner.step(entries)
+        def one_step():
+            logits = runner.step(entries, device_tokens=out)
             ops.argmax(logits, out)
-            return out.tolist()
         for _ in range(warmup):
-            tokens = one_step(tokens)
+            one_step()
         sampler = ClockSampler()
         if sample_clocks:
             sampler.start()
@@ -235,9 +238,10 @@ def main() -> int:
         torch.cuda.synchronize()
         start.record()
         for _ in range(steps):
-            tokens = one_step(tokens)
+            one_step()
         stop.record()
         torch.cuda.synchronize()
+        tokens = out.tolist()
         ms = start.elapsed_time(stop) / steps
         launches = library.launch_count() - calls0
         clocks = sampler.stop() if sample_clocks else None
@@ -248,7 +252,8 @@ def main() -> int:
 
     def prefill_run(tokens_n):
         best = None
-        for i in range(3):
+        times = []
+        for i in range(5):
             prompt = torch.randint(0, cfg.vocab_size, (tokens_n,), generator=gen).tolist()
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
@@ -258,7 +263,9 @@ def main() -> int:
             torch.cuda.synchronize()
             runner.finish(("prefill", i))
             ms = start.elapsed_time(stop)
+            times.append(round(ms, 3))
             best = ms if best is None or (i > 0 and ms < best) else best
+        print(f"[bench] prefill of {tokens_n} tokens, ms per run (the first warms up): {times}", file=sys.stderr, flush=True)
         flops = 2.0 * tokens_n * layers * per_layer + 2.0 * cfg.vocab_size * cfg.hidden_size \
             + layers * 4.0 * cfg.q_size * tokens_n * (tokens_n + 1) / 2
         return best, flops

@@ -195,3 +195,32 @@ def test_checkpoint_with_saved_rotary_buffers_loads(tmp_path):
     save_file(tensors, path)
     out = LLM(model, dtype="float32").generate(prompts[:1], SamplingParams.greedy_params(max_tokens=3))
     assert len(out[0].token_ids) == 3
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+def test_tokens_handed_over_on_the_device_give_the_same_sequence(tmp_path, graphs):
+    """Decoding with the next token chosen on the GPU and read by the next step from device
+    memory, without a visit to the host, produces the tokens ``LLM.generate`` produces."""
+    from allpaca_b200 import LLM, SamplingParams, ops
+    from allpaca_b200.config import EngineConfig
+    from allpaca_b200.engine.batch import BatchEntry
+    from allpaca_b200.engine.runner import ModelRunner
+    config, model, prompts, w = make(tmp_path, "B", "bfloat16")
+    prompts = prompts[:3]
+    new = 20
+    engine = EngineConfig(dtype="bfloat16", page_size=8, max_cache_tokens=1024, max_num_seqs=4,
+                          max_num_batched_tokens=256, use_cuda_graphs=graphs)
+    want = [o.token_ids for o in LLM(runner=ModelRunner(model, engine)).generate(
+        prompts, SamplingParams.greedy_params(max_tokens=new))]
+    runner = ModelRunner(model, engine)
+    out = torch.empty(len(prompts), dtype=torch.int32, device="cuda")
+    logits = runner.step([BatchEntry(i, p, [len(p) - 1]) for i, p in enumerate(prompts)])
+    ops.argmax(logits, out)
+    got = [out.clone()]
+    entries = [BatchEntry(i, [0], [0]) for i in range(len(prompts))]
+    for _ in range(new - 1):
+        logits = runner.step(entries, device_tokens=out)
+        ops.argmax(logits, out)
+        got.append(out.clone())
+    got = torch.stack(got).T.tolist()
+    assert got == want
