@@ -85,6 +85,8 @@ def host_library() -> ctypes.CDLL:
             "aps_adopt_running": [c_void_p, c_int64, c_int64, c_int64, c_int64],
             "aps_has_unfinished": [c_void_p], "aps_schedule": [c_void_p, POINTER(c_int)],
             "aps_advance": [c_void_p, POINTER(c_int), c_int, POINTER(c_int)], "aps_abort": [c_void_p, c_int64],
+            "aps_advance_counts": [c_void_p], "aps_resolve": [c_void_p, POINTER(c_int), c_int, POINTER(c_int)],
+            "aps_unresolved_steps": [c_void_p],
             "aps_list": [c_void_p, c_int, POINTER(c_int64), c_int],
         }.items():
             getattr(lib, name).argtypes = args

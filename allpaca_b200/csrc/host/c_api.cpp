@@ -155,6 +155,15 @@ APC_EXPORT int aps_advance(void* s, const int* sampled, int num_sampled, int* nu
     *num_finished = rc == kOk ? (int)sc->finished().size() : 0;
     return rc;
 }
+// The two halves of aps_advance (see Scheduler::advance_counts and Scheduler::resolve).
+APC_EXPORT int aps_advance_counts(void* s) { return sdone((Scheduler*)s, ((Scheduler*)s)->advance_counts()); }
+APC_EXPORT int aps_resolve(void* s, const int* sampled, int num_sampled, int* num_finished) {
+    Scheduler* sc = (Scheduler*)s;
+    const int rc = sdone(sc, sc->resolve(sampled, num_sampled));
+    *num_finished = rc == kOk ? (int)sc->finished().size() : 0;
+    return rc;
+}
+APC_EXPORT int aps_unresolved_steps(void* s) { return ((Scheduler*)s)->unresolved_steps(); }
 APC_EXPORT void aps_finished(void* s, int64_t* ids, int* reasons) {
     Scheduler* sc = (Scheduler*)s;
     std::copy(sc->finished().begin(), sc->finished().end(), ids);

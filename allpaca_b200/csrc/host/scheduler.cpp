@@ -192,7 +192,7 @@ int Scheduler::schedule() {
         budget -= count;
     }
 
-    if (rows_.empty() && has_unfinished() && preempted_.empty()) {
+    if (rows_.empty() && (!waiting_.empty() || !running_.empty()) && preempted_.empty()) {
         error_ = "the scheduler found nothing to run although requests are pending";
         return kMisuse;
     }
@@ -200,8 +200,6 @@ int Scheduler::schedule() {
 }
 
 int Scheduler::advance(const int* sampled, int num_sampled) {
-    finished_.clear();
-    reasons_.clear();
     int need = 0;
     for (const ScheduledRows& row : rows_) need += row.samples;
     if (need != num_sampled) {
@@ -209,28 +207,68 @@ int Scheduler::advance(const int* sampled, int num_sampled) {
                  " tokens were given";
         return kMisuse;
     }
-    int k = 0;
+    if (!unresolved_.empty()) {
+        error_ = "advance: an earlier step is not resolved yet";
+        return kMisuse;
+    }
+    const int rc = advance_counts();
+    return rc != kOk ? rc : resolve(sampled, num_sampled);
+}
+
+int Scheduler::advance_counts() {
+    std::vector<int64_t> sampled_ids;
     for (const ScheduledRows& row : rows_) {
-        SchedRequest& r = reqs_[row.id];
+        auto it = reqs_.find(row.id);
+        if (row.samples) sampled_ids.push_back(row.id);
+        if (it == reqs_.end()) continue;          // ended by a stop token after this step was planned
+        SchedRequest& r = it->second;
         r.num_computed += row.count;
         if (!row.samples) continue;
-        const int tok = sampled[k++];
         r.output_len += 1;
-        // stop wins over length (crates/allpaca-core/src/engine.rs:4607-4621)
-        int reason = kNotFinished;
-        if (std::find(r.stop_ids.begin(), r.stop_ids.end(), tok) != r.stop_ids.end()) reason = kStop;
-        else if (r.output_len >= r.max_tokens) reason = kLength;
-        else if (r.num_tokens() >= max_model_len_) reason = kLength;
-        if (reason != kNotFinished) {
-            finished_.push_back(row.id);
-            reasons_.push_back(reason);
+        if (r.output_len >= r.max_tokens || r.num_tokens() >= max_model_len_) {
+            r.closing = true;                     // no further step; its last token's value is still to come
+            auto at = std::find(running_.begin(), running_.end(), row.id);
+            if (at != running_.end()) running_.erase(at);
         }
     }
+    unresolved_.push_back(std::move(sampled_ids));
+    rows_.clear();
+    return kOk;
+}
+
+int Scheduler::resolve(const int* sampled, int num_sampled) {
+    finished_.clear();
+    reasons_.clear();
+    if (unresolved_.empty()) {
+        error_ = "resolve: no step is waiting for its tokens";
+        return kMisuse;
+    }
+    const std::vector<int64_t>& ids = unresolved_.front();
+    if ((int)ids.size() != num_sampled) {
+        error_ = "resolve: " + std::to_string(ids.size()) + " rows were sampled, " + std::to_string(num_sampled) +
+                 " tokens were given";
+        return kMisuse;
+    }
+    for (int k = 0; k < num_sampled; ++k) {
+        auto it = reqs_.find(ids[k]);
+        if (it == reqs_.end()) continue;          // already ended (a stop token one step earlier, or aborted)
+        SchedRequest& r = it->second;
+        // stop wins over length (crates/allpaca-core/src/engine.rs:4607-4621)
+        int reason = kNotFinished;
+        if (std::find(r.stop_ids.begin(), r.stop_ids.end(), sampled[k]) != r.stop_ids.end()) reason = kStop;
+        else if (r.closing) reason = kLength;
+        if (reason == kNotFinished) continue;
+        finished_.push_back(ids[k]);
+        reasons_.push_back(reason);
+    }
     for (int64_t id : finished_) {
-        running_.erase(std::find(running_.begin(), running_.end(), id));
+        auto at = std::find(running_.begin(), running_.end(), id);
+        if (at != running_.end()) running_.erase(at);
+        auto w = std::find(waiting_.begin(), waiting_.end(), id);
+        if (w != waiting_.end()) waiting_.erase(w);
         reqs_.erase(id);
     }
-    rows_.clear();
+    unresolved_.pop_front();
     return kOk;
 }
 

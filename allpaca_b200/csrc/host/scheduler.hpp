@@ -44,6 +44,7 @@ struct SchedRequest {
     int64_t max_tokens = 0;
     int64_t arrival = 0;
     int preemptions = 0;
+    bool closing = false;        // reached its length limit; waits for the value of its last token
     std::vector<int> stop_ids;
     int64_t num_tokens() const { return prompt_len + output_len; }
 };
@@ -64,7 +65,7 @@ public:
     int add(int64_t id, int64_t prompt_len, int64_t max_tokens, const int* stop_ids, int num_stop);
     // a request that already holds `num_computed` tokens of cache joins the running ones
     int adopt_running(int64_t id, int64_t prompt_len, int64_t max_tokens, int64_t num_computed);
-    bool has_unfinished() const { return !waiting_.empty() || !running_.empty(); }
+    bool has_unfinished() const { return !waiting_.empty() || !running_.empty() || !unresolved_.empty(); }
 
     // Plans the next step.  kOk, or kMisuse when nothing can run although requests are pending.
     int schedule();
@@ -74,8 +75,18 @@ public:
 
     // Records the planned step: its rows are now cached; `sampled` holds one token per row with
     // `samples`, in the order of rows().  finished()/reasons() name the requests that are done;
-    // their cache is the caller's to free.
+    // their cache is the caller's to free.  It is advance_counts() followed by resolve().
     int advance(const int* sampled, int num_sampled);
+    // The same in two halves, for a caller that launches the next step before the tokens of
+    // this one have reached the host.  advance_counts(): the planned step has been launched;
+    // its rows count as cached and every sampled row's request as one token longer.  Requests
+    // that thereby reach their length limit are planned no more.  resolve(): the token values
+    // of the oldest step not yet resolved, one per sampled row in order; decides who is done
+    // (a stop token ends a request, also one that a later step has already been planned for:
+    // that row is then run for nothing and its token must be dropped by the caller).
+    int advance_counts();
+    int resolve(const int* sampled, int num_sampled);
+    int unresolved_steps() const { return (int)unresolved_.size(); }
     const std::vector<int64_t>& finished() const { return finished_; }
     const std::vector<int>& reasons() const { return reasons_; }
 
@@ -106,6 +117,7 @@ private:
     std::vector<ScheduledRows> rows_;
     std::vector<int64_t> preempted_, admitted_, finished_;
     std::vector<int> reasons_;
+    std::deque<std::vector<int64_t>> unresolved_;     // per launched step: the requests of its sampled rows
     std::string error_;
 };
 

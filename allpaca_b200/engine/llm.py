@@ -18,7 +18,7 @@ from ..config import EngineConfig
 from ..sampling import SamplingParams, uniform
 from .batch import BatchEntry
 from .runner import ModelRunner
-from .scheduler import Request, Scheduler
+from .scheduler import Request, RequestStatus, Scheduler
 
 
 @dataclass
@@ -36,6 +36,14 @@ class RequestOutput:
     @property
     def completion_tokens(self) -> int:
         return len(self.token_ids)
+
+
+class _InFlight:
+    """A launched step whose tokens have not been read yet: what was planned, the requests of
+    its sampled rows (as planned, and those that were actually run) and the sampler's handle."""
+
+    def __init__(self, out, sampling, live, pending):
+        self.out, self.sampling, self.live, self.pending = out, sampling, live, pending
 
 
 class LLM:
@@ -67,6 +75,7 @@ class LLM:
         from ..sampling.sampler import Sampler
         self.sampler = Sampler(runner.device, e.max_num_seqs)
         self._ids = itertools.count()
+        self._inflight: Optional[_InFlight] = None
         self.stats = {"steps": 0, "prompt_tokens": 0, "tokens_generated": 0, "preemptions": 0,
                       "batched_rows": 0}
 
@@ -84,37 +93,96 @@ class LLM:
         return rid
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._inflight is not None
 
     def step(self) -> List[RequestOutput]:
-        """Run one batch; returns the requests that finished in it."""
+        """Launch one batch; returns the requests found finished.
+
+        One step is kept in flight: while the GPU runs the batch launched here, the host reads
+        the tokens of the batch before it, appends them and decides who is done.  In steady
+        decoding (the same requests, one row each, as in the step before) the new step takes
+        its token ids straight from the device, where the step before left them, so the GPU
+        never waits for the host.  A request that a stop token ended is therefore known one
+        step late: the row it still had in the step in flight is run for nothing and its
+        token dropped.  Requests reach the caller one call after the step that finished them;
+        :meth:`flush` brings everything up to date."""
+        prev = self._inflight
+        finished: List[Request] = []
+        if prev is not None:
+            self.scheduler.advance_counts(prev.out)
+            if any(self._at_length_limit(q) for q in prev.live):
+                # a request has reached its length limit: it is planned no more, but holds its
+                # pages until its last token is here.  Fetch the tokens first, so that the pages
+                # are free for the step about to be planned (once per request: no loss).
+                finished = self._resolve(prev)
+                prev = None
         out = self.scheduler.schedule()
         self.stats["preemptions"] += len(out.preempted)
         if not out.rows:
-            return []
-        entries = []
-        sampling = []
-        for r in out.rows:
-            toks = r.request.token_slice(r.start, r.count)
-            entries.append(BatchEntry(r.request.request_id, toks, [r.count - 1] if r.samples else []))
-            if r.samples:
-                sampling.append(r.request)
-        logits = self.runner.step(entries)
+            if prev is not None:
+                finished = finished + self._resolve(prev)
+            return self._outputs(finished)
+        sampling = [r.request for r in out.rows if r.samples]
+        steady = (prev is not None and len(sampling) == len(out.rows) and len(sampling) == len(prev.sampling)
+                  and all(r.count == 1 for r in out.rows)
+                  and all(a is b for a, b in zip(sampling, prev.sampling)))
+        if steady:
+            entries = [BatchEntry(r.request.request_id, [0], [0]) for r in out.rows]
+            logits = self.runner.step(entries, device_tokens=prev.pending.device)
+        else:
+            if prev is not None:
+                finished = finished + self._resolve(prev)          # the rows planned need the token values
+                prev = None
+            entries = [BatchEntry(r.request.request_id, r.request.token_slice(r.start, r.count),
+                                  [r.count - 1] if r.samples else [])
+                       for r in out.rows if r.request.status is not RequestStatus.FINISHED]
+            # (a stop token may just have ended a request this step had planned a row for: that
+            # row is dropped; the scheduler still counts it among the planned ones)
+            logits = self.runner.step(entries) if entries else None
         seed_default = self.runner.engine.seed
+        live = [q for q in sampling if q.status is not RequestStatus.FINISHED] if not steady else sampling
         us = [uniform(q.params.seed if q.params.seed is not None else seed_default,
-                      len(q.output_token_ids)) for q in sampling]
-        tokens = self.sampler.sample(logits, [q.params for q in sampling], us)
-        sampled = {q.request_id: t for q, t in zip(sampling, tokens)}
-        finished = self.scheduler.advance(out, sampled)
+                      len(q.output_token_ids) + q.num_pending) for q in live]
+        pending = self.sampler.launch(logits, [q.params for q in live], us) if logits is not None else None
         self.stats["steps"] += 1
         self.stats["batched_rows"] += out.num_tokens
+        if steady:
+            finished = finished + self._resolve(prev)   # while the GPU runs the step just launched
+        self._inflight = _InFlight(out, sampling, live, pending)
+        return self._outputs(finished)
+
+    def _at_length_limit(self, q: Request) -> bool:
+        n = len(q.output_token_ids) + q.num_pending
+        return n >= q.params.max_tokens or len(q.prompt_token_ids) + n >= self.scheduler.max_model_len
+
+    def flush(self) -> List[RequestOutput]:
+        """Wait for the step in flight, if any, and record its tokens; returns the requests
+        that it finished."""
+        prev, self._inflight = self._inflight, None
+        if prev is None:
+            return []
+        self.scheduler.advance_counts(prev.out)
+        return self._outputs(self._resolve(prev))
+
+    def _resolve(self, prev: "_InFlight") -> List[Request]:
+        """Bring the tokens of a launched step to the host and let the scheduler decide who is
+        done.  Rows of requests that had ended before the step ran were not sampled: the
+        scheduler is given a filler for them, which it ignores."""
+        tokens = self.sampler.fetch(prev.pending) if prev.pending is not None else []
+        by_request = {id(q): t for q, t in zip(prev.live, tokens)}
+        full = [by_request.get(id(q), 0) for q in prev.sampling]
+        finished = self.scheduler.resolve(prev.out, full)
         self.stats["tokens_generated"] += len(tokens)
-        outs = []
+        if self._inflight is prev:
+            self._inflight = None
         for req in finished:
             self.runner.finish(req.request_id)
-            outs.append(RequestOutput(req.request_id, req.prompt_token_ids, list(req.output_token_ids),
-                                      req.finish_reason.value, req.num_preemptions))
-        return outs
+        return finished
+
+    @staticmethod
+    def _outputs(finished: List[Request]) -> List[RequestOutput]:
+        return [RequestOutput(req.request_id, req.prompt_token_ids, list(req.output_token_ids),
+                              req.finish_reason.value, req.num_preemptions) for req in finished]
 
     # ---- batch API ----------------------------------------------------------
     def generate(self, prompt_token_ids: Union[Sequence[int], Sequence[Sequence[int]]],

@@ -31,7 +31,7 @@ from __future__ import annotations
 
 import enum
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional
+from typing import Dict, Hashable, List, Optional, Sequence
 
 import ctypes
 
@@ -66,6 +66,7 @@ class Request:
     status: RequestStatus = RequestStatus.WAITING
     finish_reason: Optional[FinishReason] = None
     num_preemptions: int = 0
+    num_pending: int = 0                  # tokens sampled on the device whose values are not here yet
 
     @property
     def all_token_ids(self) -> List[int]:
@@ -215,18 +216,40 @@ class Scheduler:
     def advance(self, output: SchedulerOutput, sampled: Dict[Hashable, int]) -> List[Request]:
         """Record the step: rows are now cached; sampled tokens are appended; requests that
         are done are taken out (their cache is the caller's to free).  Returns them."""
-        toks = [int(sampled[r.request.request_id]) for r in output.rows if r.samples]
+        self.advance_counts(output)
+        return self.resolve(output, [int(sampled[r.request.request_id]) for r in output.rows if r.samples])
+
+    def advance_counts(self, output: SchedulerOutput) -> None:
+        """First half of :meth:`advance`, for a caller that launches the next step before this
+        step's tokens have reached the host: the step has been launched, its rows count as
+        cached and every sampled row's request as one token longer (value still unknown)."""
+        rc = self._lib.aps_advance_counts(self._h)
+        if rc != 0:
+            raise RuntimeError(self._error())
+        for r in output.rows:
+            if r.request.status is not RequestStatus.FINISHED:
+                r.request.num_computed += r.count
+                if r.samples:
+                    r.request.num_pending += 1
+
+    def resolve(self, output: SchedulerOutput, tokens: Sequence[int]) -> List[Request]:
+        """Second half: the token values of the oldest step not yet resolved, one per sampled
+        row in order.  Appends them (except to requests a stop token ended a step earlier),
+        decides who is done and returns those; their cache is the caller's to free."""
+        toks = [int(t) for t in tokens]
         arr = (ctypes.c_int * max(len(toks), 1))(*toks)
         nfin = ctypes.c_int(0)
-        rc = self._lib.aps_advance(self._h, arr, len(toks), ctypes.byref(nfin))
+        rc = self._lib.aps_resolve(self._h, arr, len(toks), ctypes.byref(nfin))
         if rc != 0:
             raise RuntimeError(self._error())
         k = 0
         for r in output.rows:
-            r.request.num_computed += r.count
-            if r.samples:
+            if not r.samples:
+                continue
+            if r.request.status is not RequestStatus.FINISHED:
                 r.request.output_token_ids.append(toks[k])
-                k += 1
+                r.request.num_pending -= 1
+            k += 1
         finished: List[Request] = []
         if nfin.value:
             ids = (ctypes.c_int64 * nfin.value)()
@@ -239,6 +262,9 @@ class Scheduler:
                 self.cache.unpin(req.request_id)
                 finished.append(req)
         return finished
+
+    def unresolved_steps(self) -> int:
+        return int(self._lib.aps_unresolved_steps(self._h))
 
     def abort(self, request_id: Hashable) -> Optional[Request]:
         """Take a request out, running or waiting; its cache is the caller's to free."""

@@ -213,6 +213,7 @@ def main() -> int:
         t = time.perf_counter()
         for _ in range(steps):
             llm.step()
+        llm.flush()                           # the last step's tokens are on the host too
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t
         # --- device-timed steps of the step function with GPU next-token choice ---

@@ -224,3 +224,41 @@ def test_tokens_handed_over_on_the_device_give_the_same_sequence(tmp_path, graph
         got.append(out.clone())
     got = torch.stack(got).T.tolist()
     assert got == want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_stop_token_found_one_step_late_changes_no_other_reply(tmp_path, dtype):
+    """The step after a stop token is already in flight when the token reaches the host: the
+    stopped request's row in it runs for nothing, the other requests go on undisturbed, and a
+    request added meanwhile joins them."""
+    from allpaca_b200 import LLM, SamplingParams
+    config, model, prompts, w = make(tmp_path, "B", dtype)
+    kw = dict(model=model, dtype=dtype, page_size=8, max_cache_tokens=1024, max_num_seqs=4,
+              max_num_batched_tokens=64, prefill_chunk=32)
+    free = LLM(**kw).generate(prompts[:3], SamplingParams.greedy_params(max_tokens=20))
+    stops = [free[0].token_ids[4], free[2].token_ids[11]]
+    params = [SamplingParams.greedy_params(max_tokens=20, stop_token_ids=[stops[0]]),
+              SamplingParams.greedy_params(max_tokens=20),
+              SamplingParams.greedy_params(max_tokens=20, stop_token_ids=[stops[1]])]
+    llm = LLM(**kw)
+    ids = [llm.add_request(p, sp) for p, sp in zip(prompts[:3], params)]
+    done = {}
+    steps = 0
+    late = None
+    while llm.has_unfinished():
+        for o in llm.step():
+            done[o.request_id] = o
+        steps += 1
+        if steps == 8:
+            late = llm.add_request(prompts[3], SamplingParams.greedy_params(max_tokens=6))
+    for o in llm.flush():
+        done[o.request_id] = o
+    cut0 = free[0].token_ids[:free[0].token_ids.index(stops[0]) + 1]
+    cut2 = free[2].token_ids[:free[2].token_ids.index(stops[1]) + 1]
+    assert done[ids[0]].token_ids == cut0 and done[ids[0]].finish_reason == "stop"
+    assert done[ids[1]].token_ids == free[1].token_ids and done[ids[1]].finish_reason == "length"
+    assert done[ids[2]].token_ids == cut2 and done[ids[2]].finish_reason == "stop"
+    alone = LLM(**kw).generate([prompts[3]], SamplingParams.greedy_params(max_tokens=6))[0]
+    assert done[late].token_ids == alone.token_ids
+    assert llm.runner.cache.num_running() == 0
+    llm.runner.cache.check()

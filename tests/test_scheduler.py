@@ -193,3 +193,42 @@ def test_token_slice_equals_slicing_the_joined_list():
     for start in range(0, 9):
         for count in range(0, 9 - start):
             assert req.token_slice(start, count) == req.all_token_ids[start:start + count]
+
+
+def test_two_halves_of_advance_with_a_step_in_flight():
+    """The next step is planned before the tokens of the step before are known: a request at its
+    length limit is planned no more, a stop token is found one step late, the row planned in
+    between runs for nothing and its token is dropped."""
+    cache, s = make(budget=16, chunk=8)
+    a, b = req("a", 3, max_tokens=5, stop=[99]), req("b", 3, max_tokens=2)
+    s.add(a), s.add(b)
+
+    def run(out):
+        for r in out.rows:
+            if r.request.status.value == "finished":
+                continue                                  # its cache is gone: the caller drops the row
+            if not cache.has(r.request.request_id):
+                cache.begin(r.request.request_id)
+            cache.append(r.request.request_id, r.count)
+
+    out0 = s.schedule()
+    run(out0)
+    s.advance_counts(out0)
+    out1 = s.schedule()                                   # planned without the tokens of step 0
+    assert [(r.request.request_id, r.start, r.count) for r in out1.rows] == [("a", 3, 1), ("b", 3, 1)]
+    assert s.resolve(out0, [7, 7]) == []
+    run(out1)
+    s.advance_counts(out1)                                # b now holds max_tokens tokens
+    out2 = s.schedule()
+    assert [r.request.request_id for r in out2.rows] == ["a"]
+    done = s.resolve(out1, [99, 8])
+    assert {d.request_id: d.finish_reason for d in done} == {"a": FinishReason.STOP, "b": FinishReason.LENGTH}
+    for d in done:
+        cache.free(d.request_id)
+    run(out2)
+    s.advance_counts(out2)
+    assert s.has_unfinished()                             # step 2 is still to be resolved
+    assert s.resolve(out2, [5]) == [] and not s.has_unfinished()
+    assert a.output_token_ids == [7, 99] and b.output_token_ids == [7, 8]
+    assert cache.num_running() == 0 and cache.num_free_pages() == 64
+    assert s.schedule().rows == []
