@@ -10,7 +10,8 @@
 //   MMA 1    S[128 x 128] = Q K^T        tcgen05.mma, accumulator in tensor memory
 //   softmax  two groups of four warps, one row per thread and 64 of the tile's 128 keys per
 //            group: read S from tensor memory, scale, mask, running maximum and sum in
-//            32-bit, write P in bfloat16 to shared memory in the operand layout.  The two
+//            32-bit, write P in bfloat16 back into tensor memory (two to a column, over the
+//            part of S just read), where the second product takes its A operand.  The two
 //            groups keep separate running maxima, like two key slices, and are combined at
 //            the end; eight warps give every scheduler two streams of this latency-bound work.
 //   MMA 2    O_g[128 x HD] += P_g V_g for each group's 64 keys, accumulated in tensor memory
@@ -52,7 +53,6 @@
 #define SUB_BYTES (128 * 128)              // a [128 rows x 64 bf16] sub-tile
 #define Q_BYTES (NHALF * SUB_BYTES)
 #define KV_BYTES (NHALF * SUB_BYTES)       // K (or V) of one tile
-#define P_BYTES (2 * SUB_BYTES)
 #define T5_THREADS 320                     // producer warp, MMA warp, 2 x 4 softmax warps
 #define T5_TMEM_COLS 512                   // S twice: 2 x 128 columns, then two O_tiles of HD columns
 #define T5_O_COL 256
@@ -61,6 +61,12 @@
 #define T5_ERR_WAIT 4
 
 static __device__ int g_t5_status;
+
+__device__ __forceinline__ float t5_max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 
 // 2^x by the special-function unit; exactly 0 for x = -inf
 __device__ __forceinline__ float t5_exp2(float x) {
@@ -82,8 +88,7 @@ struct T5Smem {
     static constexpr int kQ = 0;
     static constexpr int kK = kQ + Q_BYTES;                 // two stages
     static constexpr int kV = kK + 2 * KV_BYTES;            // two stages
-    static constexpr int kP = kV + 2 * KV_BYTES;
-    static constexpr int kBars = kP + 2 * P_BYTES;          // P twice
+    static constexpr int kBars = kV + 2 * KV_BYTES;
     static constexpr int kTotal = kBars + 256 + 1024;       // + alignment slack
 };
 
@@ -259,11 +264,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     ok = tc::mbar_wait(&p_ready[g * 2 + s], (it >> 1) & 1);
                     if (!ok) break;
                     tc::fence_after_sync();
-                    const uint64_t pd = tc::smem_desc_k_major_sw128(smem + T5Smem::kP + s * P_BYTES + g * SUB_BYTES);
+                    // P_g lies in tensor memory, over the first columns of the half of S it came from
+                    const uint32_t pt = tmem_base + (uint32_t)(s * BKV + g * 64);
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks)
-                        tc::mma_bf16(tmem_o + g * HD, pd + 2 * ks, vd + (uint64_t)((g * 4 + ks) * (16 * 128 / 16)),
-                                     idesc_o, (it > 0 || ks > 0) ? 1u : 0u);
+                        tc::mma_bf16_a_tmem(tmem_o + g * HD, pt + (uint32_t)(ks * 8),
+                                            vd + (uint64_t)((g * 4 + ks) * (16 * 128 / 16)), idesc_o,
+                                            (it > 0 || ks > 0) ? 1u : 0u);
                     tc::mma_commit(&o_full[g]);
                 }
                 if (!ok) break;
@@ -291,7 +298,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             const int k0 = (t_lo + it) * BKV + grp * 64;       // first key of this group's half tile
             const int buf = it & 1;
             const uint32_t s_cols = lane_base + (uint32_t)(buf * BKV + grp * 64);
-            uint8_t* prow = smem + T5Smem::kP + buf * P_BYTES + grp * SUB_BYTES + r * 128;
             // tcgen05.ld and .st are warp-wide instructions: whatever decides whether one runs is a vote
             if (!__all_sync(0xffffffffu, tc::mbar_wait(&s_full[buf], (it >> 1) & 1))) { ok = false; break; }
             tc::fence_after_sync();
@@ -318,9 +324,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                         v[j] = vis ? v[j] : 0xff800000u;
                     }
                 }
+                // (three-input maximum and two-wide multiply-add and add: half the instructions)
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int j = 0; j < 64; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[j]));
+                for (int j = 0; j < 64; j += 2)
+                    mx4[(j >> 1) & 3] = t5_max3(mx4[(j >> 1) & 3], __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
                 // the scale is positive: the maximum of the scaled scores is the scaled maximum
                 const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
                 const bool grow = mx > mref + 8.0f;            // also the row's first visible key
@@ -346,25 +354,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     tc::tmem_st_wait();
                 }
                 const float muse = mref == -INFINITY ? 0.f : mref;
-                float l4[4] = {0.f, 0.f, 0.f, 0.f};
+                float2 l2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+                const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-muse, -muse);
 #pragma unroll
                 for (int j = 0; j < 64; j += 2) {
-                    const float x0 = t5_exp2(fmaf(__uint_as_float(v[j]), p.scale_log2, -muse));
-                    const float x1 = t5_exp2(fmaf(__uint_as_float(v[j + 1]), p.scale_log2, -muse));
-                    l4[j & 3] += x0;
-                    l4[(j + 1) & 3] += x1;
-                    __nv_bfloat162 b2 = __floats2bfloat162_rn(x0, x1);
+                    const float2 a = __ffma2_rn(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), scale2, shift2);
+                    const float2 x = make_float2(t5_exp2(a.x), t5_exp2(a.y));
+                    l2[(j >> 1) & 1] = __fadd2_rn(l2[(j >> 1) & 1], x);
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(x.x, x.y);
                     packed[j >> 1] = *reinterpret_cast<uint32_t*>(&b2);
                 }
-                lsum = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                lsum = (l2[0].x + l2[0].y) + (l2[1].x + l2[1].y);
             }
             l += lsum;
-            // the half tile's 64 keys = eight 16-byte chunks of the row, in the operand's swizzle
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) =
-                    make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-            tc::fence_proxy_async();            // the tensor core reads P through the async proxy
+            // P goes back into tensor memory, two bfloat16 to a column, over the part of S this
+            // thread has just read: the second product takes it from there
+            tc::tmem_st_x32(s_cols, packed);
+            tc::tmem_st_wait();
             tc::fence_before_sync();
             tc::mbar_arrive(&p_ready[grp * 2 + buf]);
         }

@@ -138,6 +138,17 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16_f32(int M, int N) {
 }
 
 // ---- MMA ------------------------------------------------------------------------
+// The same with the A operand in tensor memory (M lanes x K/2 columns, two bf16 per column).
+__device__ __forceinline__ void mma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // D[tmem] (+)= A[smem] * B[smem]^T for one K=16 slice; issued by one thread.
 __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                          uint32_t accumulate) {
