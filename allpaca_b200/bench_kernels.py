@@ -85,11 +85,14 @@ def bench_gemm(args) -> dict:
             "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
-def _paged(batch, context, nkv, hd, P):
+def _paged(batch, context, nkv, hd, P, scattered=False):
+    """A cache and block tables: pages in rising order, as a fresh pool hands them out, or
+    scattered over the pool (the worst case: one load per page)."""
     pages_per = -(-context // P)
     cache = torch.randn(batch * pages_per, 2, nkv, P, hd, device="cuda", dtype=torch.bfloat16)
-    table = torch.randperm(batch * pages_per, device="cuda").to(torch.int32).view(batch, pages_per)
-    return cache, table
+    order = torch.randperm(batch * pages_per, device="cuda") if scattered else \
+        torch.arange(batch * pages_per, device="cuda")
+    return cache, order.to(torch.int32).view(batch, pages_per)
 
 
 def bench_attention(args) -> dict:
@@ -100,7 +103,7 @@ def bench_attention(args) -> dict:
     B, C, nh, nkv, hd, P = args.batch, args.context, args.heads, args.kv_heads, args.head_dim, args.page_size
     per = B * C * 2 * nkv * hd * 2
     copies = max(2, int(math.ceil(300e6 / per)))
-    caches = [_paged(B, C, nkv, hd, P) for _ in range(copies)]
+    caches = [_paged(B, C, nkv, hd, P, args.scattered_pages) for _ in range(copies)]
     q = torch.randn(B, nh * hd, device="cuda", dtype=torch.bfloat16)
     out = torch.empty_like(q)
     seq = torch.arange(B, device="cuda", dtype=torch.int32)
@@ -138,7 +141,7 @@ def bench_attention(args) -> dict:
 def bench_prefill_attention(args) -> dict:
     from allpaca_b200 import ops
     T, nh, nkv, hd, P = args.tokens, args.heads, args.kv_heads, args.head_dim, args.page_size
-    cache, table = _paged(1, T, nkv, hd, P)
+    cache, table = _paged(1, T, nkv, hd, P, args.scattered_pages)
     q = torch.randn(T, nh * hd, device="cuda", dtype=torch.bfloat16)
     out = torch.empty_like(q)
     seq = torch.zeros(T, device="cuda", dtype=torch.int32)
@@ -187,6 +190,8 @@ def main(argv=None) -> int:
             s.add_argument("--cp-async", action="store_true", help="decode: the cp.async kernel instead of the TMA one")
             s.add_argument("--splits", type=int, default=0, help="key slices (0: the kernel's own plan)")
             s.add_argument("--mma-sync", action="store_true", help="prompt attention with the mma.sync tile kernel")
+            s.add_argument("--scattered-pages", action="store_true",
+                           help="block tables in random order instead of rising page numbers")
     args = p.parse_args(argv)
     fn = {"gemm": bench_gemm, "attention": bench_attention, "prefill-attention": bench_prefill_attention}[args.what]
     print(json.dumps(fn(args)))

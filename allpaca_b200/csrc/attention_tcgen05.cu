@@ -94,6 +94,7 @@ struct T5Smem {
 
 __global__ void __launch_bounds__(T5_THREADS)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
+                         const __grid_constant__ CUtensorMap tmap_run,
                          const AttnT5Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -140,6 +141,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&tmap_q);
         tc::prefetch_tensormap(&tmap_kv);
+        tc::prefetch_tensormap(&tmap_run);
     }
     // V stages start as zeros: what a skipped page leaves in them must be finite, because a
     // probability of zero times a NaN would poison the row
@@ -209,7 +211,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     if (fine) tc::mbar_expect_tx(&full[s], (uint32_t)(valid * page_bytes * NHALF));
                 }
                 fine = __shfl_sync(0xffffffffu, fine, 0);
-                if (fine && page >= 0) {
+                // The pages of a tile often follow one another in memory (a sequence's pages are
+                // handed out in rising order): then one box per half fetches them all.  Loads are
+                // issued at a limited rate, so few large ones keep the tensor cores fed where
+                // many small ones do not.
+                const int page0 = __shfl_sync(0xffffffffu, page, 0);
+                const bool run = page0 >= 0 &&
+                                 __all_sync(0xffffffffu, lane >= pages_per_tile || page == page0 + lane);
+                if (fine && run) {
+                    if (lane == 0) {
+                        for (int h = 0; h < NHALF; ++h)
+                            tc::tma_load_3d(smem + base + s * KV_BYTES + h * SUB_BYTES, &tmap_run, h * 64,
+                                            (which * p.nkv + kvh) * p.P, page0, &full[s]);
+                    }
+                } else if (fine && page >= 0) {
                     const int row = ((page * 2 + which) * p.nkv + kvh) * p.P;
                     for (int h = 0; h < NHALF; ++h)
                         tc::tma_load_2d(smem + base + s * KV_BYTES + h * SUB_BYTES + lane * page_bytes, &tmap_kv,
@@ -505,6 +520,18 @@ AP_EXPORT int ap_attention_tcgen05(const void* q, void* out, const void* cache, 
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
                    "attention (tcgen05): cannot encode the cache tensor map");
     }
+    CUtensorMap mrun;
+    {
+        // the same cache as [page][row within the page][column]: a box spans the pages of a key tile
+        cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)(2 * nkv * P), (cuuint64_t)num_pages};
+        cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)page_stride * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)P, (cuuint32_t)(BKV / P)};
+        cuuint32_t es[3] = {1, 1, 1};
+        AP_REQUIRE(enc(&mrun, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(cache), dims, strides, box, es,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
+                   "attention (tcgen05): cannot encode the tensor map of page runs");
+    }
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -521,7 +548,7 @@ AP_EXPORT int ap_attention_tcgen05(const void* q, void* out, const void* cache, 
     AP_REQUIRE(nkv <= 65535, "attention (tcgen05): too many KV heads for the grid");
     dim3 grid(total_tiles, nkv);
     AP_CHECK_PDL_LAUNCH("attention_tcgen05", ap_launch_pdl(attention_tcgen05_kernel, grid, dim3(T5_THREADS),
-                                                           (size_t)T5Smem::kTotal, stream, mq, mkv, p));
+                                                           (size_t)T5Smem::kTotal, stream, mq, mkv, mrun, p));
     return AP_OK;
 }
 

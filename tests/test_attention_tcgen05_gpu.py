@@ -28,9 +28,12 @@ def ops():
 
 @pytest.mark.parametrize("nh,nkv,hd,P", SHAPES)
 @pytest.mark.parametrize("window", [0, 37, 300])
-def test_against_plain_and_tile_kernel(ops, nh, nkv, hd, P, window):
+@pytest.mark.parametrize("sequential", [False, True])
+def test_against_plain_and_tile_kernel(ops, nh, nkv, hd, P, window, sequential):
+    """Pages scattered over the pool (one load per page) and in rising order (one load per
+    run of pages that fills a key tile)."""
     assert supported(ops, nh, nkv, hd, P)
-    case = paged_case(SEQS, nh, nkv, hd, P, torch.bfloat16, seed=hd + P + window)
+    case = paged_case(SEQS, nh, nkv, hd, P, torch.bfloat16, seed=hd + P + window, sequential=sequential)
     scale = 0.9 / math.sqrt(hd)
     got = run_attention(ops, case, nh, nkv, hd, scale, window, tensor_cores=True)
     ops.check_kernel_status()
@@ -81,11 +84,12 @@ def test_finds_one_far_key(ops, far):
         assert float((got[h * 2].double() - ref[h * 2]).abs().max()) < 0.05
 
 
-def test_pages_given_back_are_not_read(ops):
+@pytest.mark.parametrize("sequential", [False, True])
+def test_pages_given_back_are_not_read(ops, sequential):
     nh, nkv, hd, P, window = 8, 2, 128, 16, 150
     seqs = [(900, 80), (500, 200)]
     freed = [900 - 80 - window + 1, 500 - 200 - window + 1]
-    case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=9, freed_before=freed)
+    case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=9, freed_before=freed, sequential=sequential)
     got = run_attention(ops, case, nh, nkv, hd, 0.08, window, tensor_cores=True)
     ops.check_kernel_status()
     assert rel_err(got, reference_attention(case, seqs, nh, hd, window, scale=0.08)) < 1.5e-2

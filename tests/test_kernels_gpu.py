@@ -292,14 +292,17 @@ def test_sample_distribution(ops):
 
 
 # ---------------------------------------------------------------- attention over pages
-def paged_case(seqs, nh, nkv, hd, P, dtype, seed, freed_before=None):
+def paged_case(seqs, nh, nkv, hd, P, dtype, seed, freed_before=None, sequential=False):
     """Random queries and a paged cache for sequences given as (context length, query rows).
     Pages are handed out in a shuffled order so that neighbours in a sequence are far apart
-    in memory.  `freed_before[s]`: pages wholly before that position are marked given back."""
+    in memory (`sequential`: in rising order, as a fresh pool hands them out).
+    `freed_before[s]`: pages wholly before that position are marked given back."""
     g = torch.Generator().manual_seed(seed)
     max_pages = max(-(-c // P) for c, _ in seqs)
     total_pages = sum(-(-c // P) for c, _ in seqs) + 3
     perm = torch.randperm(total_pages, generator=g).tolist()
+    if sequential:
+        perm = list(range(total_pages - 1, -1, -1))          # pop() hands out 0, 1, 2, ...
     cache = torch.randn(total_pages, 2, nkv, P, hd, generator=g).to(dtype)   # junk in unused slots
     table = torch.full((len(seqs), max_pages), -1, dtype=torch.int32)
     ks, vs, rows_q, token_seq, positions, seq_start = [], [], [], [], [], [0]
