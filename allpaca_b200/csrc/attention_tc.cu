@@ -654,7 +654,8 @@ struct DtSmem {
 
 template <bool CLUSTER>
 __global__ void __launch_bounds__(DT_THREADS)
-attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcParams p) {
+attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid_constant__ CUtensorMap tmap_run,
+                           const AttnTcParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(smem + DtSmem::kBars);
@@ -671,6 +672,7 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const At
         *abort_flag = 0;
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&tmap_kv);
+        tc::prefetch_tensormap(&tmap_run);
     }
     // V starts as zeros: what a skipped page leaves in a stage must be finite, because a
     // probability of zero times a NaN would poison the row
@@ -745,7 +747,21 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const At
             }
             fine = __shfl_sync(0xffffffffu, fine, 0);
             if (!fine) break;
-            if (page >= 0) {
+            // pages of a tile that follow one another in memory (a sequence's pages are handed out
+            // in rising order) come with one box per half: loads are issued at a limited rate
+            const int page0 = __shfl_sync(0xffffffffu, page, 0);
+            const bool run = page0 >= 0 && __all_sync(0xffffffffu, lane >= pages_per_tile || page == page0 + lane);
+            if (run) {
+                if (lane == 0) {
+                    uint8_t* dst = smem + s * DT_STAGE_BYTES;
+#pragma unroll
+                    for (int h = 0; h < DT_NHALF; ++h) {
+                        tc::tma_load_3d(dst + h * SWZ_HALF_BYTES, &tmap_run, h * 64, kvh * p.P, page0, &full[s]);
+                        tc::tma_load_3d(dst + DT_KV_BYTES + h * SWZ_HALF_BYTES, &tmap_run, h * 64,
+                                        (p.nkv + kvh) * p.P, page0, &full[s]);
+                    }
+                }
+            } else if (page >= 0) {
                 uint8_t* dst = smem + s * DT_STAGE_BYTES + lane * page_bytes;
                 const int krow = ((page * 2 + 0) * p.nkv + kvh) * p.P;
                 const int vrow = ((page * 2 + 1) * p.nkv + kvh) * p.P;
@@ -944,6 +960,18 @@ AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cach
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
                    "attention (decode, TMA): cannot encode the cache tensor map");
     }
+    CUtensorMap mrun;
+    {
+        // the same cache as [page][row within the page][column]: a box spans the pages of a key tile
+        cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)(2 * nkv * P), (cuuint64_t)num_pages};
+        cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)page_stride * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)P, (cuuint32_t)(BKV / P)};
+        cuuint32_t es[3] = {1, 1, 1};
+        AP_REQUIRE(dt_encode_fn()(&mrun, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(cache), dims, strides,
+                                  box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
+                   "attention (decode, TMA): cannot encode the tensor map of page runs");
+    }
     static bool configured = false;
     if (!configured) {
         int rc = configure_smem((const void*)attention_split_tma_kernel<false>, DtSmem::kTotal);
@@ -980,11 +1008,11 @@ AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cach
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = ap_pdl_enabled() ? 2 : 1;
-        AP_CHECK_PDL_LAUNCH("attention_split_tma", cudaLaunchKernelEx(&cfg, attention_split_tma_kernel<true>, mkv, p));
+        AP_CHECK_PDL_LAUNCH("attention_split_tma", cudaLaunchKernelEx(&cfg, attention_split_tma_kernel<true>, mkv, mrun, p));
         return AP_OK;
     }
     AP_CHECK_PDL_LAUNCH("attention_split_tma", ap_launch_pdl(attention_split_tma_kernel<false>, grid, dim3(DT_THREADS),
-                                                             (size_t)DtSmem::kTotal, stream, mkv, p));
+                                                             (size_t)DtSmem::kTotal, stream, mkv, mrun, p));
     if (nsplit > 1) {
         dim3 mgrid(T, nh);
         AP_CHECK_PDL_LAUNCH("attention_merge",

@@ -50,8 +50,11 @@ def test_shapes_are_taken_or_left(ops):
 
 @pytest.mark.parametrize("nh,nkv,hd,P", SHAPES)
 @pytest.mark.parametrize("window", [0, 37, 300])
-def test_against_plain_and_cp_async(ops, nh, nkv, hd, P, window):
-    case = paged_case(DECODE, nh, nkv, hd, P, torch.bfloat16, seed=hd + P + window)
+@pytest.mark.parametrize("sequential", [False, True])
+def test_against_plain_and_cp_async(ops, nh, nkv, hd, P, window, sequential):
+    """Pages scattered over the pool (one load per page) and in rising order (one load per
+    run of pages that fills a key tile)."""
+    case = paged_case(DECODE, nh, nkv, hd, P, torch.bfloat16, seed=hd + P + window, sequential=sequential)
     scale = 0.9 / math.sqrt(hd)
     got = run(ops, case, nh, nkv, hd, scale, window, use_tma=True)
     ref = reference_attention(case, DECODE, nh, hd, window or None, scale=scale)
@@ -96,10 +99,11 @@ def test_finds_one_far_key(ops, far):
         assert float((got[h * 2].double() - ref[h * 2]).abs().max()) < 0.05
 
 
-def test_pages_given_back_are_not_read(ops):
+@pytest.mark.parametrize("sequential", [False, True])
+def test_pages_given_back_are_not_read(ops, sequential):
     nh, nkv, hd, P, window = 8, 2, 128, 16, 150
     seqs = [(900, 1), (500, 1), (149, 1)]
     freed = [900 - 1 - window + 1, 500 - 1 - window + 1, 0]
-    case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=9, freed_before=freed)
+    case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=9, freed_before=freed, sequential=sequential)
     got = run(ops, case, nh, nkv, hd, 0.08, window, use_tma=True)
     assert rel_err(got, reference_attention(case, seqs, nh, hd, window, scale=0.08)) < 1.5e-2
