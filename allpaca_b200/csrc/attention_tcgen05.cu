@@ -59,6 +59,7 @@
 #define LOG2E_F 1.4426950408889634f
 
 #define T5_ERR_WAIT 4
+#define T5_KV_STAGES 2                     // K and V tiles in flight: a load takes longer than a tile's products
 
 static __device__ int g_t5_status;
 
@@ -87,8 +88,8 @@ struct AttnT5Params {
 struct T5Smem {
     static constexpr int kQ = 0;
     static constexpr int kK = kQ + Q_BYTES;                 // two stages
-    static constexpr int kV = kK + 2 * KV_BYTES;            // two stages
-    static constexpr int kBars = kV + 2 * KV_BYTES;
+    static constexpr int kV = kK + T5_KV_STAGES * KV_BYTES;
+    static constexpr int kBars = kV + T5_KV_STAGES * KV_BYTES;
     static constexpr int kTotal = kBars + 256 + 1024;       // + alignment slack
 };
 
@@ -100,14 +101,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + T5Smem::kBars);
     uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;       // [stage]
-    uint64_t* k_empty = bars + 3;      // [stage]
-    uint64_t* v_full = bars + 5;       // [stage]
-    uint64_t* v_empty = bars + 7;      // [stage]
-    uint64_t* s_full = bars + 9;       // [S buffer]
-    uint64_t* p_ready = bars + 11;     // [softmax group][P buffer]
-    uint64_t* o_full = bars + 15;      // [softmax group]
-    uint32_t* tmem_slot = (uint32_t*)(bars + 20);
+    uint64_t* k_full = bars + 1;                          // [stage]
+    uint64_t* k_empty = k_full + T5_KV_STAGES;            // [stage]
+    uint64_t* v_full = k_empty + T5_KV_STAGES;            // [stage]
+    uint64_t* v_empty = v_full + T5_KV_STAGES;            // [stage]
+    uint64_t* s_full = v_empty + T5_KV_STAGES;            // [S buffer]
+    uint64_t* p_ready = s_full + 2;                       // [softmax group][P buffer]
+    uint64_t* o_full = p_ready + 4;                       // [softmax group]
+    uint32_t* tmem_slot = (uint32_t*)(o_full + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     volatile int* s_seq = (volatile int*)(tmem_slot + 2);
     volatile int* s_tile = (volatile int*)(tmem_slot + 3);
@@ -127,14 +128,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         *s_seq = found;
         *s_tile = t;
         tc::mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < T5_KV_STAGES; ++s) {
             tc::mbar_init(&k_full[s], 1);
             tc::mbar_init(&k_empty[s], 1);
             tc::mbar_init(&v_full[s], 1);
             tc::mbar_init(&v_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
             tc::mbar_init(&s_full[s], 1);
-            tc::mbar_init(&p_ready[s], 128);
-            tc::mbar_init(&p_ready[2 + s], 128);
+            tc::mbar_init(&p_ready[s], 4);          // one arrival per warp of the group
+            tc::mbar_init(&p_ready[2 + s], 4);
             tc::mbar_init(&o_full[s], 1);
         }
         *abort_flag = 0;
@@ -145,7 +148,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     }
     // V stages start as zeros: what a skipped page leaves in them must be finite, because a
     // probability of zero times a NaN would poison the row
-    for (int i = threadIdx.x; i < 2 * KV_BYTES / 16; i += T5_THREADS)
+    for (int i = threadIdx.x; i < T5_KV_STAGES * KV_BYTES / 16; i += T5_THREADS)
         reinterpret_cast<uint4*>(smem + T5Smem::kV)[i] = make_uint4(0, 0, 0, 0);
     tc::fence_proxy_async();
     if (warp == 1) tc::tmem_alloc(tmem_slot, T5_TMEM_COLS);
@@ -197,8 +200,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             // K runs one tile ahead of V: K of tile i+1 feeds S of tile i+1, which the tensor cores
             // compute while the softmax warps are still on tile i; V of tile i is wanted last.
             auto load = [&](int it, int page, int which, uint64_t* full, uint64_t* empty, int base) -> int {
-                const int s = it & 1;
-                const uint32_t ph = (it >> 1) & 1;
+                const int s = it % T5_KV_STAGES;
+                const uint32_t ph = (uint32_t)((it / T5_KV_STAGES) & 1);
                 const int valid = __popc(__ballot_sync(0xffffffffu, page >= 0));
                 int fine = 1;
                 if (lane == 0) {
@@ -232,10 +235,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                 }
                 return fine;
             };
+            // The block table is read four tiles ahead of its use: a lookup is a round trip to L2,
+            // and one per tile on the loads' critical path would be most of a tile's time.
             int page_v = page_of(0);
+            int q0 = page_of(1), q1 = page_of(2), q2 = page_of(3), q3 = page_of(4);
             int fine = load(0, page_v, 0, k_full, k_empty, T5Smem::kK);
             for (int it = 0; it < ntiles && fine; ++it) {
-                const int page_k = page_of(it + 1);
+                const int page_k = q0;                              // pages of tile it + 1
+                q0 = q1; q1 = q2; q2 = q3;
+                q3 = page_of(it + 5);
                 if (it + 1 < ntiles) fine = load(it + 1, page_k, 0, k_full, k_empty, T5Smem::kK);
                 if (fine) fine = load(it, page_v, 1, v_full, v_empty, T5Smem::kV);
                 page_v = page_k;
@@ -248,8 +256,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             const uint32_t tmem_o = tmem_base + T5_O_COL;
             // S[buffer it & 1] = Q K^T of tile `it`; K's stage is free as soon as this product is done
             auto scores = [&](int it) -> bool {
-                const int s = it & 1;
-                if (!tc::mbar_wait(&k_full[s], (it >> 1) & 1)) return false;
+                const int s = it % T5_KV_STAGES, sb = it & 1;          // K stage, S buffer
+                if (!tc::mbar_wait(&k_full[s], (uint32_t)((it / T5_KV_STAGES) & 1))) return false;
                 tc::fence_after_sync();
 #pragma unroll
                 for (int h = 0; h < NHALF; ++h) {
@@ -257,24 +265,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     const uint64_t kd = tc::smem_desc_k_major_sw128(smem + T5Smem::kK + s * KV_BYTES + h * SUB_BYTES);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        tc::mma_bf16(tmem_base + (uint32_t)(s * BKV), qd + 2 * k, kd + 2 * k, idesc_s,
+                        tc::mma_bf16(tmem_base + (uint32_t)(sb * BKV), qd + 2 * k, kd + 2 * k, idesc_s,
                                      (h > 0 || k > 0) ? 1u : 0u);
                 }
                 tc::mma_commit(&k_empty[s]);
-                tc::mma_commit(&s_full[s]);
+                tc::mma_commit(&s_full[sb]);
                 return true;
             };
             bool ok = tc::mbar_wait(q_full, 0);
             if (ok) ok = scores(0);
             for (int it = 0; it < ntiles && ok && !*abort_flag; ++it) {
-                const int s = it & 1;
+                const int s = it & 1, sv = it % T5_KV_STAGES;          // S/P buffer, V stage
                 // S of tile it+1 goes into the buffer that tile it-1 used; the softmax groups have
                 // handed over P of tile it-1 (waited for below, one iteration ago), so they have read it
                 if (it + 1 < ntiles) ok = scores(it + 1);
-                if (ok) ok = tc::mbar_wait(&v_full[s], (it >> 1) & 1);
+                if (ok) ok = tc::mbar_wait(&v_full[sv], (uint32_t)((it / T5_KV_STAGES) & 1));
                 // O_g += P_g V_g, one product per softmax group as soon as its P is written (by then
                 // the group has also scaled O_g down where a row's reference maximum moved)
-                const uint64_t vd = tc::smem_desc_mn_major_sw128(smem + T5Smem::kV + s * KV_BYTES, SUB_BYTES);
+                const uint64_t vd = tc::smem_desc_mn_major_sw128(smem + T5Smem::kV + sv * KV_BYTES, SUB_BYTES);
                 for (int g = 0; g < 2 && ok; ++g) {
                     ok = tc::mbar_wait(&p_ready[g * 2 + s], (it >> 1) & 1);
                     if (!ok) break;
@@ -289,7 +297,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     tc::mma_commit(&o_full[g]);
                 }
                 if (!ok) break;
-                tc::mma_commit(&v_empty[s]);
+                tc::mma_commit(&v_empty[sv]);
             }
             if (!ok && !*abort_flag) {
                 *abort_flag = 1;
@@ -387,7 +395,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             tc::tmem_st_x32(s_cols, packed);
             tc::tmem_st_wait();
             tc::fence_before_sync();
-            tc::mbar_arrive(&p_ready[grp * 2 + buf]);
+            __syncwarp();                       // every lane's part of P is written: one arrival for the warp
+            if (lane == 0) tc::mbar_arrive(&p_ready[grp * 2 + buf]);
         }
         // the last product into O_g
         if (ok && !__all_sync(0xffffffffu, tc::mbar_wait(&o_full[grp], (ntiles - 1) & 1))) ok = false;
