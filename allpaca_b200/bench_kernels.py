@@ -150,10 +150,11 @@ def bench_prefill_attention(args) -> dict:
 
     def fn(i):
         ops.attention(q, out, cache, table, seq, pos, nh, nkv, hd, 1.0 / math.sqrt(hd), 0, seq_start=start,
-                      query_lens=[T], max_context=T, use_tcgen05=not args.mma_sync)
+                      query_lens=[T], max_context=T, use_tcgen05=not args.mma_sync,
+                      wide={"auto": None, "one": False, "two": True}[args.query_tiles])
     us = _time(fn, args.iters, args.warmup, not args.no_graph)
     flops = 4.0 * nh * hd * T * (T + 1) / 2
-    return {"kernel": "attention_tile" if args.mma_sync else "attention_tcgen05", "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
+    return {"kernel": "attention_tile" if args.mma_sync else "attention_tcgen05", "query_tiles": args.query_tiles, "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
             "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
@@ -190,6 +191,8 @@ def main(argv=None) -> int:
             s.add_argument("--cp-async", action="store_true", help="decode: the cp.async kernel instead of the TMA one")
             s.add_argument("--splits", type=int, default=0, help="key slices (0: the kernel's own plan)")
             s.add_argument("--mma-sync", action="store_true", help="prompt attention with the mma.sync tile kernel")
+            s.add_argument("--query-tiles", choices=["auto", "one", "two"], default="auto",
+                           help="prompt attention on tcgen05: query tiles to a CTA (auto: by the number of CTAs)")
             s.add_argument("--scattered-pages", action="store_true",
                            help="block tables in random order instead of rising page numbers")
     args = p.parse_args(argv)

@@ -118,7 +118,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 
     if (threadIdx.x == 0) {
         // late tiles of a sequence have the most keys to walk: hand them out first
-        int t = gridDim.x - 1 - blockIdx.x, found = -1;
+        // (the KV head is the fast index of the grid: all heads of the longest portions start first)
+        int t = (int)((gridDim.x - 1 - blockIdx.x) / (unsigned)p.nkv), found = -1;
         for (int s = 0; s < p.nseq; ++s) {
             const int n = p.seq_start[s + 1] - p.seq_start[s];
             const int nt = (n + p.tokens_per_tile - 1) / p.tokens_per_tile;
@@ -165,7 +166,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     if (active) {
         row0 = p.seq_start[seq] + *s_tile * p.tokens_per_tile;
         ntok = min(p.tokens_per_tile, p.seq_start[seq + 1] - row0);
-        kvh = blockIdx.y;
+        kvh = (int)(blockIdx.x % (unsigned)p.nkv);
         head0 = kvh * G;
         // positions are read after the kernels before this one have finished
     }
@@ -554,8 +555,8 @@ AP_EXPORT int ap_attention_tcgen05(const void* q, void* out, const void* cache, 
     p.max_blocks = max_blocks; p.nseq = nseq; p.nh = nh; p.nkv = nkv; p.P = P; p.window = window; p.group = G;
     p.tokens_per_tile = 128 / G;
     p.scale_log2 = scale * LOG2E_F;
-    AP_REQUIRE(nkv <= 65535, "attention (tcgen05): too many KV heads for the grid");
-    dim3 grid(total_tiles, nkv);
+    AP_REQUIRE((long long)total_tiles * nkv < (1LL << 31), "attention (tcgen05): too many CTAs for the grid");
+    dim3 grid((unsigned)(total_tiles * nkv));
     AP_CHECK_PDL_LAUNCH("attention_tcgen05", ap_launch_pdl(attention_tcgen05_kernel, grid, dim3(T5_THREADS),
                                                            (size_t)T5Smem::kTotal, stream, mq, mkv, mrun, p));
     return AP_OK;

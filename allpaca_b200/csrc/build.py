@@ -39,7 +39,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
 
 CORE_SOURCES = ["errors.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu",
                 "sampling.cu"]
-ATTN_SOURCES = ["errors.cu", "attention.cu", "attention_tc.cu", "attention_tcgen05.cu"]
+ATTN_SOURCES = ["errors.cu", "attention.cu", "attention_tc.cu", "attention_tcgen05.cu",
+                "attention_tcgen05_wide.cu"]
 HEADERS = ["common.cuh", "tcgen05.cuh", "attention_noalloc.h"]
 
 

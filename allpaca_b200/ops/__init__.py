@@ -308,14 +308,32 @@ def _decode_attention(lib, q, out, cache_layer, block_table, positions, rows, nu
          int(window or 0), 1, 0, nsplit, po, pm, pc, stream_handle())
 
 
+# CTAs of the tcgen05 attention with two query tiles from which it is preferred to the kernel
+# with one: below, the narrow kernel's twice as many CTAs fill the SMs better
+WIDE_ATTENTION_MIN_CTAS = 148
+
+
 def _prompt_attention(lib, q, out, cache_layer, block_table, seq_start, positions, first_seq, query_lens, T,
-                      num_heads, num_kv_heads, head_dim, P, scale, window, use_tcgen05) -> None:
+                      num_heads, num_kv_heads, head_dim, P, scale, window, use_tcgen05, wide=None) -> None:
     """The sequences from ``first_seq`` on (their rows follow those of the sequences before):
-    the tcgen05 kernel for 64 rows or more of a shape it takes, else the mma.sync tile kernel.
+    the tcgen05 kernels for 64 rows or more of a shape they take, else the mma.sync tile kernel.
+    Of the two tcgen05 kernels the one with two query tiles to a CTA runs when ``wide`` says so,
+    or (``wide=None``) when the portions are long enough to fill the GPU with such CTAs.
     Rows are addressed through ``seq_start``, so only it and the block table are offset."""
     nseq = len(query_lens)
     table_ptr = block_table.data_ptr() + first_seq * block_table.shape[1] * 4
     start_ptr = seq_start.data_ptr() + first_seq * 4
+    if (use_tcgen05 and wide is not False and sum(query_lens) >= 64 and hasattr(lib, "ap_attention_tcgen05_wide")
+            and lib.ap_attention_tcgen05_wide_supports(num_heads, num_kv_heads, head_dim, P)
+            and cache_layer.stride(0) == 2 * num_kv_heads * P * head_dim):
+        per_cta = int(lib.ap_attention_tcgen05_wide_tokens_per_cta(num_heads, num_kv_heads))
+        ctas = sum(-(-n // per_cta) for n in query_lens)
+        if wide or ctas * num_kv_heads >= WIDE_ATTENTION_MIN_CTAS:
+            call(lib, "ap_attention_tcgen05_wide", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
+                 cache_layer.shape[0], table_ptr, block_table.shape[1], start_ptr,
+                 positions.data_ptr(), nseq, T, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0),
+                 float(scale), int(window or 0), ctas, stream_handle())
+            return
     if (use_tcgen05 and sum(query_lens) >= 64 and hasattr(lib, "ap_attention_tcgen05")
             and lib.ap_attention_tcgen05_supports(num_heads, num_kv_heads, head_dim, P)
             and cache_layer.stride(0) == 2 * num_kv_heads * P * head_dim):
@@ -339,13 +357,15 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: int = 0, seq_start: Optional[torch.Tensor] = None,
               query_lens: Optional[Sequence[int]] = None, max_context: int = 0,
-              scratch=None, zero_scratch=None, use_tcgen05: bool = True, use_tma: bool = True) -> None:
+              scratch=None, zero_scratch=None, use_tcgen05: bool = True, use_tma: bool = True,
+              wide: Optional[bool] = None) -> None:
     """Causal attention of every row of ``q [T, nh*hd]`` over its sequence's cached keys.
 
     float32 runs the general CUDA-core kernel (the true 32-bit path).  bfloat16 runs on the
     tensor cores when ``seq_start`` (device, ``[nseq+1]``) and ``query_lens`` (host) are
     given: the split kernel when every sequence brings one row; else, for 64 rows or more and
-    the shapes it takes, the tcgen05 kernel (``use_tcgen05``), and otherwise the tile kernel.
+    the shapes it takes, a tcgen05 kernel (``use_tcgen05``; ``wide`` picks the one with two query
+    tiles to a CTA, ``None`` by the number of CTAs), and otherwise the tile kernel.
     ``scratch(name, shape, dtype)`` supplies the partial-result buffers of the split kernel;
     ``zero_scratch`` (same signature) supplies buffers that are zero when first handed out
     and stay with the caller: with it the last key slice to arrive combines all slices,
@@ -382,7 +402,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
                               head_dim, P, scale, window, max_context, scratch, zero_scratch, use_tma)
         if nd < nseq:
             _prompt_attention(lib, q, out, cache_layer, block_table, seq_start, positions, nd, query_lens[nd:], T,
-                              num_heads, num_kv_heads, head_dim, P, scale, window, use_tcgen05)
+                              num_heads, num_kv_heads, head_dim, P, scale, window, use_tcgen05, wide)
         return
     call(lib, "ap_attention_rows", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
          dtype_code(q.dtype), block_table.data_ptr(), block_table.shape[1], token_seq.data_ptr(),
@@ -479,6 +499,9 @@ def gemm_tc_status() -> int:
 def check_kernel_status() -> None:
     """Raise if a kernel reported that it gave up (a bounded wait inside it expired)."""
     for hd, lib in list(library._attn.items()):
+        if hasattr(lib, "ap_attention_tcgen05_wide_status") and int(lib.ap_attention_tcgen05_wide_status()) > 0:
+            raise KernelError(f"the tcgen05 attention kernel with two query tiles (head size {hd}) gave up "
+                              "waiting on its pipeline; its results are not valid")
         if hasattr(lib, "ap_attention_tcgen05_status") and int(lib.ap_attention_tcgen05_status()) != 0:
             raise KernelError(f"the tcgen05 attention kernel (head size {hd}) gave up waiting on its pipeline; "
                               f"its results are void")

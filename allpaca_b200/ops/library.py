@@ -117,6 +117,10 @@ _OPTIONAL_ATTN_SIGNATURES: Dict[str, list] = {
     "ap_attention_tcgen05_supports": [_I, _I, _I, _I],
     "ap_attention_tcgen05_tokens_per_tile": [_I, _I],
     "ap_attention_tcgen05_status": [],
+    "ap_attention_tcgen05_wide": [_P, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _L, _F, _I, _I, _P],
+    "ap_attention_tcgen05_wide_supports": [_I, _I, _I, _I],
+    "ap_attention_tcgen05_wide_tokens_per_cta": [_I, _I],
+    "ap_attention_tcgen05_wide_status": [],
     # int ap_attention_decode_tma(q, out, cache, num_pages, block_table, max_blocks, positions, T, nh, nkv, hd, P,
     #                             page_stride, scale, window, nsplit, part_o, part_ml, stream)
     "ap_attention_decode_tma": [_P, _P, _P, _L, _P, _I, _P, _I, _I, _I, _I, _I, _L, _F, _I, _I, _P, _P, _P],

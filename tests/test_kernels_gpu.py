@@ -340,7 +340,7 @@ def reference_attention(case, seqs, nh, hd, window, scale=None):
     return torch.cat(outs).reshape(-1, nh * hd)
 
 
-def run_attention(ops, case, nh, nkv, hd, scale, window, tensor_cores):
+def run_attention(ops, case, nh, nkv, hd, scale, window, tensor_cores, **more):
     q = dev(case["q"])
     out = torch.empty_like(q)
     bufs = {}
@@ -353,7 +353,7 @@ def run_attention(ops, case, nh, nkv, hd, scale, window, tensor_cores):
         kw = dict(seq_start=dev(case["seq_start"]), query_lens=case["query_lens"],
                   max_context=int(case["positions"].max()) + 1, scratch=scratch)
     ops.attention(q, out, dev(case["cache"]), dev(case["table"]), dev(case["token_seq"]),
-                  dev(case["positions"]), nh, nkv, hd, scale, window, **kw)
+                  dev(case["positions"]), nh, nkv, hd, scale, window, **kw, **more)
     return out.cpu()
 
 
