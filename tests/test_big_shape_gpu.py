@@ -8,7 +8,13 @@ import plain_llama
 pytestmark = pytest.mark.gpu
 
 
-def test_two_layers_of_the_8b_shape(tmp_path):
+@pytest.mark.parametrize("two_query_tiles", [False, True])
+def test_two_layers_of_the_8b_shape(tmp_path, monkeypatch, two_query_tiles):
+    """``two_query_tiles``: the prompt attention with two query tiles to a CTA, which the engine
+    otherwise keeps for longer portions, takes every portion of 64 rows or more."""
+    from allpaca_b200 import ops
+    if two_query_tiles:
+        monkeypatch.setattr(ops, "WIDE_ATTENTION_MIN_CTAS", 1)
     from allpaca_b200.config import EngineConfig
     from allpaca_b200.config.presets import preset_config
     from allpaca_b200.engine.batch import BatchEntry
