@@ -20,7 +20,7 @@ recurrent state (crates/allpaca-core/src/anchors.rs:16-56).
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, c_int, c_int32, c_int64, c_void_p, c_char_p
+from ctypes import POINTER, c_int, c_int64, c_void_p, c_char_p
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 

@@ -8,8 +8,6 @@ The reference lays a page out as all K rows then all V rows of one layer
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
-
 import torch
 
 

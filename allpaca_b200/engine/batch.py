@@ -10,7 +10,7 @@ concatenated token list of ``forward_batch`` (crates/allpaca-core/src/model.rs:3
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, List, Optional, Sequence
+from typing import Hashable, List, Sequence
 
 import torch
 

@@ -12,8 +12,6 @@ import itertools
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Union
 
-import torch
-
 from ..config import EngineConfig
 from ..sampling import SamplingParams, uniform
 from .batch import BatchEntry

@@ -38,7 +38,6 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         print("trace_run: --max-tokens must be positive", file=sys.stderr)
         return 2
     os.makedirs(args.out, exist_ok=True)
-    import numpy as np
     import torch
     from ..config import EngineConfig
     from .batch import BatchEntry

@@ -12,19 +12,18 @@ Role in the reference: ``forward_batch`` over ``SeqRows``
 """
 from __future__ import annotations
 
-from typing import Dict, Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, Optional, Sequence
 
-import numpy as np
 import torch
 
-from ..cache import CacheManager, GroupLayout, GroupStorage, OutOfPages, StateStorage, FREED
+from ..cache import CacheManager, GroupLayout, GroupStorage, StateStorage
 from ..config import EngineConfig
 from ..models import DecoderModel, load_config
 from ..parts import BuildEnv, Workspace
 from ..weights import load_checkpoint
 from ..ops import library
 from .batch import BatchEntry, StepBatch
-from .step_builder import StepError, build_step
+from .step_builder import build_step
 
 
 class ModelRunner:

@@ -21,7 +21,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from .. import ops
-from .base import (BuildEnv, KVNeed, LayerCache, Mixer, PartSpec, WeightSpec, build, register)
+from .base import BuildEnv, KVNeed, LayerCache, Mixer, WeightSpec, build, register
 from .linear import Linear
 
 

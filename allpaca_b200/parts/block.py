@@ -7,11 +7,11 @@ block hands its last addition to whoever runs next.
 """
 from __future__ import annotations
 
-from typing import Dict, Mapping
+from typing import Dict
 
 import torch
 
-from .base import Block, BuildEnv, LayerCache, Part, PartSpec, build, register
+from .base import Block, BuildEnv, LayerCache, Part, build, register
 
 
 @register("block", "prenorm")

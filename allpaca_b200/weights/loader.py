@@ -16,7 +16,7 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from typing import Callable, Dict, List, Mapping, Optional, Tuple
+from typing import Dict, Mapping, Tuple
 
 import torch
 

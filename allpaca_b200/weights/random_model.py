@@ -7,7 +7,7 @@ each tensor drawn from a generator keyed by ``(seed, tensor name)``.  Role in th
 """
 from __future__ import annotations
 
-from typing import Mapping, Optional
+from typing import Mapping
 
 import torch
 

@@ -16,7 +16,7 @@ import json
 import mmap
 import os
 import struct
-from typing import Dict, Iterable, List, Mapping, Optional, Tuple
+from typing import Dict, List, Mapping, Optional, Tuple
 
 import torch
 

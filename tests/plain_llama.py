@@ -18,7 +18,7 @@ softmax, norms and rotation angles stay in the compute dtype everywhere.
 from __future__ import annotations
 
 import math
-from typing import Dict, Mapping, Optional, Sequence
+from typing import Mapping, Optional, Sequence
 
 import torch
 

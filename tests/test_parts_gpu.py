@@ -1,7 +1,6 @@
 """Each part of a layer alone (norm, rotary embedding, linear, attention mixer, feed-forward,
 block) against the plain function of the same part, at sizes of its own, in 32-bit and in
 bfloat16, with the rows cut into portions so that the mixer reads what earlier steps cached."""
-import math
 
 import pytest
 import torch

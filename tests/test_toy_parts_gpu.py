@@ -3,7 +3,6 @@ registered, built into a model beside the attention mixer, and stepped, without 
 the package.  The model's order runs a layer twice (each run with its own cache and state)
 and lets one run read the keys and values another run wrote.  Toy parts use torch
 operations; they exist to test the framework's seams, not to be a model of anything."""
-import math
 
 import pytest
 import torch
