@@ -95,6 +95,28 @@ def host_library() -> ctypes.CDLL:
         lib.aps_planned.restype = None
         lib.aps_finished.argtypes = [c_void_p, POINTER(c_int64), POINTER(c_int)]
         lib.aps_finished.restype = None
+        # safetensors files (weights/safetensors_io.py is their Python face)
+        lib.apst_open.argtypes = [c_char_p]
+        lib.apst_open.restype = c_void_p
+        lib.apst_close.argtypes = [c_void_p]
+        lib.apst_close.restype = None
+        for name in ("apst_num_tensors", "apst_num_metadata"):
+            getattr(lib, name).argtypes = [c_void_p]
+            getattr(lib, name).restype = c_int
+        for name in ("apst_name", "apst_dtype", "apst_metadata_key", "apst_metadata_value"):
+            getattr(lib, name).argtypes = [c_void_p, c_int]
+            getattr(lib, name).restype = c_char_p
+        lib.apst_ndim.argtypes = [c_void_p, c_int]
+        lib.apst_ndim.restype = c_int
+        lib.apst_shape.argtypes = [c_void_p, c_int, POINTER(c_int64), c_int]
+        lib.apst_shape.restype = c_int
+        for name in ("apst_begin", "apst_end"):
+            getattr(lib, name).argtypes = [c_void_p, c_int]
+            getattr(lib, name).restype = c_int64
+        lib.apst_data.argtypes = [c_void_p]
+        lib.apst_data.restype = c_void_p
+        lib.apst_data_len.argtypes = [c_void_p]
+        lib.apst_data_len.restype = c_int64
         _lib = lib
     return _lib
 

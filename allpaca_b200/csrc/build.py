@@ -164,8 +164,9 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
     return lib
 
 
-HOST_SOURCES = ["host/cache_manager.cpp", "host/step_builder.cpp", "host/scheduler.cpp", "host/c_api.cpp"]
-HOST_HEADERS = ["host/cache_manager.hpp", "host/step_builder.hpp", "host/scheduler.hpp"]
+HOST_SOURCES = ["host/cache_manager.cpp", "host/step_builder.cpp", "host/scheduler.cpp", "host/safetensors.cpp",
+                "host/c_api.cpp"]
+HOST_HEADERS = ["host/cache_manager.hpp", "host/step_builder.hpp", "host/scheduler.hpp", "host/safetensors.hpp"]
 
 
 def find_cxx() -> str:

@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "cache_manager.hpp"
+#include "safetensors.hpp"
 #include "scheduler.hpp"
 #include "step_builder.hpp"
 
@@ -175,4 +176,42 @@ APC_EXPORT int aps_list(void* s, int which, int64_t* out, int cap) {
     const std::vector<int64_t> v = ((Scheduler*)s)->list(which);
     for (int i = 0; i < (int)v.size() && i < cap; ++i) out[i] = v[i];
     return (int)v.size();
+}
+
+// ---- safetensors files ---------------------------------------------------------------------
+// apst_open gives a handle, or null with the reason in apc_last_error(); the pointers handed out
+// (names, types, the data) live as long as the handle.
+APC_EXPORT void* apst_open(const char* path) {
+    std::string why;
+    SafetensorsFile* f = SafetensorsFile::open(path ? path : "", &why);
+    if (!f) g_error = why;
+    return f;
+}
+APC_EXPORT void apst_close(void* h) { delete (SafetensorsFile*)h; }
+APC_EXPORT int apst_num_tensors(void* h) { return (int)((SafetensorsFile*)h)->tensors().size(); }
+static const TensorEntry* entry(void* h, int i) {
+    const auto& t = ((SafetensorsFile*)h)->tensors();
+    return i >= 0 && (size_t)i < t.size() ? &t[(size_t)i] : nullptr;
+}
+APC_EXPORT const char* apst_name(void* h, int i) { const TensorEntry* e = entry(h, i); return e ? e->name.c_str() : nullptr; }
+APC_EXPORT const char* apst_dtype(void* h, int i) { const TensorEntry* e = entry(h, i); return e ? e->dtype.c_str() : nullptr; }
+APC_EXPORT int apst_ndim(void* h, int i) { const TensorEntry* e = entry(h, i); return e ? (int)e->shape.size() : -1; }
+APC_EXPORT int apst_shape(void* h, int i, int64_t* out, int cap) {
+    const TensorEntry* e = entry(h, i);
+    if (!e || (int)e->shape.size() > cap) return -1;
+    std::copy(e->shape.begin(), e->shape.end(), out);
+    return (int)e->shape.size();
+}
+APC_EXPORT int64_t apst_begin(void* h, int i) { const TensorEntry* e = entry(h, i); return e ? e->begin : -1; }
+APC_EXPORT int64_t apst_end(void* h, int i) { const TensorEntry* e = entry(h, i); return e ? e->end : -1; }
+APC_EXPORT const void* apst_data(void* h) { return ((SafetensorsFile*)h)->data(); }
+APC_EXPORT int64_t apst_data_len(void* h) { return ((SafetensorsFile*)h)->data_len(); }
+APC_EXPORT int apst_num_metadata(void* h) { return (int)((SafetensorsFile*)h)->metadata().size(); }
+APC_EXPORT const char* apst_metadata_key(void* h, int i) {
+    const auto& m = ((SafetensorsFile*)h)->metadata();
+    return i >= 0 && (size_t)i < m.size() ? m[(size_t)i].first.c_str() : nullptr;
+}
+APC_EXPORT const char* apst_metadata_value(void* h, int i) {
+    const auto& m = ((SafetensorsFile*)h)->metadata();
+    return i >= 0 && (size_t)i < m.size() ? m[(size_t)i].second.c_str() : nullptr;
 }

@@ -7,20 +7,20 @@ and :181-188): an unsigned 64-bit little-endian header length, a JSON header
 the header.  Sharded checkpoints carry ``model.safetensors.index.json`` with a
 ``weight_map`` from tensor name to file (crates/allpaca-safetensors/src/catalog.rs:51-98).
 
-Tensors are memory-mapped and handed out as torch tensors in their stored
-dtype; nothing is converted here.
+Files are opened, checked and memory-mapped by the C++ host library
+(``csrc/host/safetensors.cpp``); tensors are handed out as torch tensors over the
+mapping in their stored dtype, nothing is converted here.  The writer (used by the
+random-weights mode) is Python.
 """
 from __future__ import annotations
 
+import ctypes
 import json
-import mmap
 import os
 import struct
 from typing import Dict, List, Mapping, Optional, Tuple
 
 import torch
-
-MAX_HEADER_BYTES = 100 * 1024 * 1024   # parser.rs:11
 
 _DTYPES = {
     "F64": torch.float64, "F32": torch.float32, "F16": torch.float16,
@@ -35,55 +35,36 @@ class SafetensorsError(ValueError):
 
 
 class SafetensorsFile:
-    """One memory-mapped safetensors file."""
+    """One memory-mapped safetensors file.  Opening, the header (length, UTF-8, JSON, every
+    entry's type, shape and byte range) and the mapping are the C++ host library's
+    (``csrc/host/safetensors.cpp``); this class hands the mapped bytes out as torch tensors."""
 
     def __init__(self, path: str):
+        from ..cache.manager import host_library
         self.path = path
-        try:
-            self._fh = open(path, "rb")
-        except OSError as e:
-            raise SafetensorsError(f"cannot open {path}: {e.strerror}") from None
-        size = os.fstat(self._fh.fileno()).st_size
-        if size < 8:
-            raise SafetensorsError(f"{path}: file of {size} bytes is too short for a header length")
-        (hlen,) = struct.unpack("<Q", self._fh.read(8))
-        if hlen == 0 or hlen > MAX_HEADER_BYTES:
-            raise SafetensorsError(f"{path}: header length {hlen} is outside 1..{MAX_HEADER_BYTES}")
-        if 8 + hlen > size:
-            raise SafetensorsError(f"{path}: header of {hlen} bytes overruns the file of {size} bytes")
-        raw = self._fh.read(hlen)
-        try:
-            header = json.loads(raw.decode("utf-8"))
-        except UnicodeDecodeError:
-            raise SafetensorsError(f"{path}: header is not UTF-8") from None
-        except json.JSONDecodeError as e:
-            raise SafetensorsError(f"{path}: header is not JSON: {e}") from None
-        if not isinstance(header, dict):
-            raise SafetensorsError(f"{path}: header is not a JSON object")
-        self.metadata = header.pop("__metadata__", None) or {}
-        self._data_start = 8 + hlen
-        self._data_len = size - self._data_start
+        self._lib = host_library()
+        self._h = self._lib.apst_open(os.fsencode(path))
+        if not self._h:
+            raise SafetensorsError(self._lib.apc_last_error().decode("utf-8", "replace"))
+        lib, h = self._lib, self._h
+        self.metadata = {lib.apst_metadata_key(h, i).decode(): lib.apst_metadata_value(h, i).decode()
+                         for i in range(lib.apst_num_metadata(h))}
+        self._data = lib.apst_data(h) or 0
         self.entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...], int, int]] = {}
-        for name, e in header.items():
-            try:
-                dt, shape, (b, en) = e["dtype"], tuple(int(x) for x in e["shape"]), e["data_offsets"]
-            except (KeyError, TypeError, ValueError):
-                raise SafetensorsError(f"{path}: malformed entry for tensor {name!r}") from None
-            if dt not in _DTYPES:
-                raise SafetensorsError(f"{path}: tensor {name!r} has unsupported dtype {dt!r}")
-            dtype = _DTYPES[dt]
-            n = 1
-            for s in shape:
-                n *= s
-            need = n * torch.empty((), dtype=dtype).element_size()
-            if not (0 <= b <= en <= self._data_len):
-                raise SafetensorsError(
-                    f"{path}: tensor {name!r} data [{b}, {en}) lies outside the {self._data_len} data bytes")
-            if en - b != need:
-                raise SafetensorsError(
-                    f"{path}: tensor {name!r} of shape {list(shape)} {dt} needs {need} bytes, has {en - b}")
-            self.entries[name] = (dtype, shape, int(b), int(en))
-        self._mm = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ) if size else None
+        for i in range(lib.apst_num_tensors(h)):
+            nd = lib.apst_ndim(h, i)
+            dims = (ctypes.c_int64 * max(nd, 1))()
+            lib.apst_shape(h, i, dims, max(nd, 1))
+            self.entries[lib.apst_name(h, i).decode()] = (
+                _DTYPES[lib.apst_dtype(h, i).decode()], tuple(int(d) for d in dims[:nd]),
+                int(lib.apst_begin(h, i)), int(lib.apst_end(h, i)))
+
+    def __del__(self):
+        # tensors handed out keep this object alive (see ``tensor``), so nothing reads the
+        # mapping any more when it goes
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.apst_close(h)
 
     def names(self) -> List[str]:
         return list(self.entries)
@@ -97,11 +78,9 @@ class SafetensorsFile:
         dtype, shape, b, e = self.entries[name]
         if e == b:
             return torch.empty(shape, dtype=dtype)
-        buf = memoryview(self._mm)[self._data_start + b:self._data_start + e]
-        import warnings
-        with warnings.catch_warnings():
-            warnings.simplefilter("ignore")   # torch warns that the buffer is not writable
-            t = torch.frombuffer(buf, dtype=dtype)
+        buf = (ctypes.c_char * (e - b)).from_address(self._data + b)
+        buf._file = self                      # the view holds the buffer, the buffer holds the mapping
+        t = torch.frombuffer(buf, dtype=dtype)
         return t.view(shape)
 
 

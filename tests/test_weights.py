@@ -130,3 +130,61 @@ def test_random_weights_are_seeded_and_shaped(tmp_path):
     assert torch.equal(cc.tensor("model.norm.weight"), torch.ones(96, dtype=torch.bfloat16))
     assert json.load(open(os.path.join(c, "config.json")))["torch_dtype"] == "bfloat16"
     check_names(cpu_model(TINY_B).weight_targets(), {n: ca.info(n)[1] for n in ca.names()})
+
+
+def _file_with_header(path, header_bytes, data=b""):
+    path.write_bytes(struct.pack("<Q", len(header_bytes)) + header_bytes + data)
+    return str(path)
+
+
+def test_native_reader_header_corner_cases(tmp_path):
+    """The C++ reader of the header: escapes and non-ASCII in names, metadata, whitespace,
+    tensors without elements, names written twice, bytes that are not UTF-8, entries that
+    are not what they should be."""
+    p = tmp_path / "h.safetensors"
+    data = struct.pack("<4f", 1.0, 2.0, 3.0, 4.0)
+    h = ('{ "__metadata__": {"format": "pt", "n\\u00e4me": "caf\\u00e9 \\ud83d\\ude00"},\n'
+         ' "layer\\u002e0.w\\/x": {"dtype":"F32","shape":[2,2],"data_offsets":[0,16]},\n'
+         ' "größe": {"dtype":"BF16","shape":[0,7],"data_offsets":[16,16]},\n'
+         ' "scalar": {"dtype":"F32","shape":[],"data_offsets":[12,16]} }   ').encode("utf-8")
+    f = SafetensorsFile(_file_with_header(p, h, data))
+    assert f.metadata == {"format": "pt", "näme": "café \U0001F600"}
+    assert f.names() == ["layer.0.w/x", "größe", "scalar"]
+    assert torch.equal(f.tensor("layer.0.w/x"), torch.tensor([[1.0, 2.0], [3.0, 4.0]]))
+    assert f.info("größe") == (torch.bfloat16, (0, 7)) and f.tensor("größe").shape == (0, 7)
+    assert f.tensor("scalar").shape == () and float(f.tensor("scalar")) == 4.0
+
+    twice = b'{"t":{"dtype":"U8","shape":[1],"data_offsets":[0,1]},"t":{"dtype":"U8","shape":[1],"data_offsets":[0,1]}}'
+    with pytest.raises(SafetensorsError, match="appears twice"):
+        SafetensorsFile(_file_with_header(p, twice, b"x"))
+    with pytest.raises(SafetensorsError, match="not UTF-8"):
+        SafetensorsFile(_file_with_header(p, b'{"t\xff": 1}'))
+    with pytest.raises(SafetensorsError, match="not a JSON object"):
+        SafetensorsFile(_file_with_header(p, b'[1, 2]'))
+    with pytest.raises(SafetensorsError, match="not JSON.*text after the value"):
+        SafetensorsFile(_file_with_header(p, b'{} {}'))
+    for bad in (b'{"t": 3}', b'{"t":{"dtype":"F32","shape":[1.5],"data_offsets":[0,4]}}',
+                b'{"t":{"dtype":"F32","shape":[-1],"data_offsets":[0,4]}}',
+                b'{"t":{"dtype":"F32","shape":[1],"data_offsets":[0]}}',
+                b'{"t":{"dtype":7,"shape":[1],"data_offsets":[0,4]}}'):
+        with pytest.raises(SafetensorsError, match="malformed entry for tensor 't'"):
+            SafetensorsFile(_file_with_header(p, bad, b"xxxx"))
+    huge = b'{"t":{"dtype":"F64","shape":[4294967296,4294967296],"data_offsets":[0,8]}}'
+    with pytest.raises(SafetensorsError, match="needs more than"):
+        SafetensorsFile(_file_with_header(p, huge, b"x" * 8))
+    with pytest.raises(SafetensorsError, match="header length 0"):
+        p.write_bytes(struct.pack("<Q", 0) + b"{}")
+        SafetensorsFile(str(p))
+    with pytest.raises(SafetensorsError, match="cannot open"):
+        SafetensorsFile(str(tmp_path / "missing.safetensors"))
+
+
+def test_a_tensor_keeps_its_mapping_alive(tmp_path):
+    import gc
+    p = str(tmp_path / "x.safetensors")
+    want = torch.arange(1000, dtype=torch.float32)
+    write_safetensors(p, {"w": want})
+    t = SafetensorsFile(p).tensor("w")          # the file object itself is dropped at once
+    gc.collect()
+    os.remove(p)
+    assert torch.equal(t, want) and torch.equal(t[10:20].clone(), want[10:20])
