@@ -1145,7 +1145,29 @@ AP_EXPORT int ap_gemm_tc_persistent(const void* a, const void* w, void* out, int
     // token tiles: as many as tiles of the full width (128 for up to 128 rows, else 256) would
     // take, but evenly filled: their width is the smallest multiple of 16 that covers the rows
     const int cap = M <= 128 ? 128 : 256;
-    const int tiles_m = (M + cap - 1) / cap;
+    int tiles_m = (M + cap - 1) / cap;
+    {
+        // One or two token tiles more, where that fills the SMs better: a tile's time is about that of
+        // 150 + width token columns (the weight tile's 128 x K bytes cost the same at any width), and
+        // the product takes as many of those as the busiest SM walks tiles.  Not where few tiles of a
+        // long K are shared between CTAs instead (launch_persistent), and only for a clear gain.
+        static int sms = 0;
+        if (sms == 0) {
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess ||
+                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+                sms = 148;
+        }
+        const long long tiles_n = (N + TILE_W - 1) / TILE_W;
+        const bool shared = scratch && tiles_n * tiles_m * 2 <= sms && (K + TILE_K - 1) / TILE_K >= 96;
+        auto cost = [&](int tm) {
+            const int width = ((M + tm - 1) / tm + 15) / 16 * 16;
+            return ((tiles_n * tm + sms - 1) / sms) * (150 + width);
+        };
+        const int base = tiles_m;
+        for (int tm = base + 1; tm <= base + 2 && !shared; ++tm)
+            if (cost(tm) * 100 < cost(tiles_m) * 95) tiles_m = tm;
+    }
     const int bn = ((M + tiles_m - 1) / tiles_m + 15) / 16 * 16;
     CUtensorMap mw, ma;
     AP_REQUIRE(make_map(&mw, w, N, K, ldw, TILE_W), "gemm_tc: cannot encode the weight's tensor map");
