@@ -133,7 +133,7 @@ def bench_attention(args) -> dict:
     us = _time(fn, args.iters, args.warmup, not args.no_graph)
     return {"kernel": "attention_split+merge" if args.cp_async else "attention_split_tma+merge", "batch": B, "context": C, "heads": nh, "kv_heads": nkv,
             "head_dim": hd, "splits": ops.decode_splits(B, nh, nkv, C, slots=444 if args.cp_async else 296,
-                                        cluster_sizes=() if args.cp_async else (2, 4, 8)),
+                                        cluster_sizes=() if args.cp_async else (2, 4, 8, 16)),
             "us": round(us, 2),
             "GBps": round(per / us / 1e3, 1)}
 

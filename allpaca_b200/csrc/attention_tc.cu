@@ -619,7 +619,7 @@ AP_EXPORT int ap_attention_tc_tokens_per_tile(int nh, int nkv) {
 // cp.async.bulk.tensor (128-byte swizzle), with no address arithmetic in the consumer warps
 // and no round trip to the block table inside the loop.  The four consumer warps take 16 keys
 // of every tile each, as in attention_split_kernel.  CLUSTER: the key slices of one row and KV
-// head form a thread-block cluster (2, 4 or 8 CTAs) and hand their results to its first CTA
+// head form a thread-block cluster (2, 4, 8 or 16 CTAs) and hand their results to its first CTA
 // through distributed shared memory, which combines them and writes the row: no partial
 // results in global memory and no second kernel.  Otherwise the slices are combined as for
 // attention_split_kernel.
@@ -930,7 +930,7 @@ AP_EXPORT int ap_attention_decode_tma_in_cluster(int nh, int nkv, int nsplit) {
     if (nkv <= 0 || nh % nkv) return 0;
     const int reps = nh / nkv;
     const int hc = reps < 16 ? reps : 16;
-    return (nsplit == 2 || nsplit == 4 || nsplit == 8) && DtSmem::exchange_fits(nsplit, hc);
+    return (nsplit == 2 || nsplit == 4 || nsplit == 8 || nsplit == 16) && DtSmem::exchange_fits(nsplit, hc);
 }
 
 // The split kernel with TMA loads: one row per sequence, `nsplit` key slices; part_o/part_ml
@@ -994,6 +994,13 @@ AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cach
     AP_REQUIRE(nkv * p.n_chunks <= 65535, "attention: too many KV heads for the grid");
     dim3 grid(T, nkv * p.n_chunks, nsplit);
     if (cluster) {
+        static bool wide_clusters = false;
+        if (nsplit > 8 && !wide_clusters) {
+            // clusters of more than 8 CTAs are an opt-in of the kernel
+            cudaError_t e = cudaFuncSetAttribute(attention_split_tma_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            AP_REQUIRE(e == cudaSuccess, "attention: clusters of %d CTAs are not available: %s", nsplit, cudaGetErrorString(e));
+            wide_clusters = true;
+        }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(DT_THREADS);

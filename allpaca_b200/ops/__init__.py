@@ -280,8 +280,12 @@ def _decode_attention(lib, q, out, cache_layer, block_table, positions, rows, nu
     tma = (use_tma and hasattr(lib, "ap_attention_decode_tma")
            and bool(lib.ap_attention_decode_tma_supports(num_heads, num_kv_heads, head_dim, P))
            and cache_layer.stride(0) == 2 * num_kv_heads * P * head_dim)
+    sizes = ()
+    if tma:
+        # 16 slices (a cluster size the kernel has to opt into) where the exchange buffer holds them
+        sizes = (2, 4, 8, 16) if lib.ap_attention_decode_tma_in_cluster(num_heads, num_kv_heads, 16) else (2, 4, 8)
     nsplit = decode_splits(rows, num_heads, num_kv_heads, max_context, window, slots=296 if tma else 444,
-                           cluster_sizes=(2, 4, 8) if tma else ())
+                           cluster_sizes=sizes)
     po = pm = pc = 0
     needs_scratch = nsplit > 1 and not (tma and lib.ap_attention_decode_tma_in_cluster(num_heads, num_kv_heads, nsplit))
     if needs_scratch:
@@ -290,7 +294,7 @@ def _decode_attention(lib, q, out, cache_layer, block_table, positions, rows, nu
         po = scratch("attn.part_o", (nsplit, rows, num_heads, head_dim), torch.float32).data_ptr()
         pm = scratch("attn.part_ml", (nsplit, rows, num_heads, 2), torch.float32).data_ptr()
     if tma:
-        # fed by TMA: a ring of tiles in flight, two CTAs per SM; 2, 4 or 8 slices are combined
+        # fed by TMA: a ring of tiles in flight, two CTAs per SM; 2, 4, 8 or 16 slices are combined
         # inside a thread-block cluster and need no scratch
         call(lib, "ap_attention_decode_tma", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
              cache_layer.shape[0], block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), rows,
@@ -427,7 +431,10 @@ def _decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: in
     four tiles, and every slice adds a little to the combining pass.  Slice counts in
     ``cluster_sizes`` are combined inside the kernel; the others pay for a second kernel and a
     round trip of the partial results, counted as ten tiles.  The count with the smallest
-    ``waves * (tiles per slice + 4) + 0.15 * slices (+ 10)`` is taken.
+    ``waves * (tiles per slice + 4) + 0.15 * slices (+ 10)`` is taken.  Clusters of 16 find room
+    only a few at a time (one or two to a GPC): they are considered for up to 8 of them, at the
+    price of three tiles (one sequence of 32768 keys: 48 -> 33 us; two such sequences are slower
+    with 16 slices than with 8).
     """
     reps = num_heads // num_kv_heads
     chunks = -(-reps // min(reps, 16))
@@ -440,6 +447,10 @@ def _decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: in
         cost = waves * (-(-tiles // ns) + 4) + 0.15 * ns
         if cluster_sizes and ns > 1 and ns not in cluster_sizes:
             cost += 10
+        elif ns > 8 and ns in cluster_sizes:
+            if ctas > 8:
+                continue
+            cost += 3
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = ns, cost
     return best

@@ -63,11 +63,11 @@ def test_against_plain_and_cp_async(ops, nh, nkv, hd, P, window, sequential):
     assert rel_err(got, other.double()) < 1.5e-2
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 4, 7, 8, 24, 47])
+@pytest.mark.parametrize("splits", [1, 2, 3, 4, 7, 8, 16, 24, 47])
 @pytest.mark.parametrize("nh,nkv,hd,P", [(8, 2, 128, 16), (16, 1, 128, 64), (40, 2, 64, 16)])
 def test_any_number_of_key_slices(ops, splits, nh, nkv, hd, P, monkeypatch):
-    """Slices that hold one tile, many tiles or none at all (more slices than tiles); 2, 4 and
-    8 slices are combined inside a thread-block cluster where their results fit, the other
+    """Slices that hold one tile, many tiles or none at all (more slices than tiles); 2, 4, 8
+    and 16 slices are combined inside a thread-block cluster where their results fit, the other
     counts by a second kernel."""
     case = paged_case(DECODE, nh, nkv, hd, P, torch.bfloat16, seed=splits)
     got = run(ops, case, nh, nkv, hd, 0.08, 0, use_tma=True, splits=splits, monkeypatch=monkeypatch)
