@@ -315,12 +315,18 @@ SafetensorsFile* SafetensorsFile::open(const std::string& path, std::string* err
     for (auto& item : header.object) {
         const std::string& name = item.first;
         const JValue& e = item.second;
+        // names and metadata leave this library as C strings
         if (name == "__metadata__") {
             if (e.kind == JValue::Object)
-                for (auto& kv : e.object)
-                    if (kv.second.kind == JValue::String) f->metadata_.emplace_back(kv.first, kv.second.string);
+                for (auto& kv : e.object) {
+                    if (kv.second.kind != JValue::String) continue;
+                    if (kv.first.find('\0') != std::string::npos || kv.second.string.find('\0') != std::string::npos)
+                        return give_up("metadata holds a NUL character");
+                    f->metadata_.emplace_back(kv.first, kv.second.string);
+                }
             continue;
         }
+        if (name.find('\0') != std::string::npos) return give_up("a tensor's name holds a NUL character");
         if (!seen.insert(name).second) return give_up("tensor " + quoted(name) + " appears twice in the header");
         const JValue *dtype = nullptr, *shape = nullptr, *offsets = nullptr;
         if (e.kind == JValue::Object)

@@ -188,3 +188,37 @@ def test_a_tensor_keeps_its_mapping_alive(tmp_path):
     gc.collect()
     os.remove(p)
     assert torch.equal(t, want) and torch.equal(t[10:20].clone(), want[10:20])
+
+
+def test_native_header_reader_agrees_with_json_on_random_headers(tmp_path):
+    """Names of any characters, written escaped or raw, with any spacing: the C++ reader and
+    Python's json module read the same entries, in the same order."""
+    from hypothesis import given, settings, strategies as st
+    p = tmp_path / "r.safetensors"
+    chars = st.characters(blacklist_categories=("Cs",), blacklist_characters="\0")
+    names = st.text(chars, min_size=1, max_size=12).filter(lambda n: n != "__metadata__")
+    shapes = st.lists(st.integers(0, 5), max_size=3)
+
+    @settings(max_examples=60, deadline=None)
+    @given(st.dictionaries(names, shapes, max_size=6), st.booleans(), st.sampled_from([None, 1, 3]),
+           st.dictionaries(st.text(chars, max_size=6), st.text(chars, max_size=6), max_size=3))
+    def check(tensors, ascii_only, indent, meta):
+        header, offset = {}, 0
+        if meta:
+            header["__metadata__"] = meta
+        for name, shape in tensors.items():
+            n = 2
+            for s in shape:
+                n *= s
+            header[name] = {"dtype": "BF16", "shape": shape, "data_offsets": [offset, offset + n]}
+            offset += n
+        raw = json.dumps(header, ensure_ascii=ascii_only, indent=indent).encode("utf-8")
+        f = SafetensorsFile(_file_with_header(p, raw, b"\0" * offset))
+        assert f.names() == list(tensors)
+        assert f.metadata == (meta or {})
+        for name, shape in tensors.items():
+            assert f.info(name) == (torch.bfloat16, tuple(shape))
+            assert f.tensor(name).shape == tuple(shape)
+    check()
+    with pytest.raises(SafetensorsError, match="NUL"):
+        SafetensorsFile(_file_with_header(p, b'{"a\\u0000b":{"dtype":"U8","shape":[0],"data_offsets":[0,0]}}'))
