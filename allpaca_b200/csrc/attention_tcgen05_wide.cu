@@ -12,8 +12,11 @@
 //   softmax a      ... (waits)      |                 | softmax of S_a -> P_a            ...
 //   softmax b      ... softmax of S_b -> P_b          | (waits)        |                 ...
 //
-// A softmax group is four warps, one row per thread over all 128 keys of the tile in two
-// passes over S (maximum, then probabilities; 64 scores in registers at a time).  P goes back
+// A softmax group is four warps, one row per thread, the row's 128 scores of the tile in
+// registers (one pass over tensor memory: maximum, then probabilities packed over the scores).
+// For that the block is three groups of four warps: `setmaxnreg` takes registers from the
+// last (the loading warp, the issuing warp, two idle ones: 56 each) and gives them to the two
+// softmax groups (224 each), which adds up to what the launch holds.  P goes back
 // into tensor memory over the S it came from (two bfloat16 to a column) and is the second
 // product's A operand there; O is accumulated in tensor memory over all key tiles and scaled
 // down only when a row's maximum has grown by more than 2^8 over its reference.  Loads,
