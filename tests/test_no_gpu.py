@@ -32,3 +32,24 @@ def test_command_line_parser():
     assert a.synthetic == "tiny-a" and a.seed == 3 and a.prompt_ids == ["1,2"]
     b = build_parser().parse_args(["init-random", "--preset", "tiny-b", "--out", "x"])
     assert b.preset == "tiny-b" and b.dtype == "bfloat16"
+
+
+def test_plan_of_key_slices_for_decoding():
+    """The number of key slices of the decode attention: one slice where the batch fills the
+    GPU by itself, more for few sequences, cluster sizes preferred to counts that need a second
+    kernel, and 16 (a cluster only few of which find room) for up to 8 clusters alone."""
+    from allpaca_b200.ops import decode_splits
+    tma = dict(slots=296, cluster_sizes=(2, 4, 8, 16))
+    assert decode_splits(64, 32, 8, 4096, **tma) == 1
+    assert decode_splits(8, 32, 8, 4096, **tma) == 4
+    assert decode_splits(1, 32, 8, 4096, **tma) == 8
+    assert decode_splits(1, 32, 8, 8192, **tma) == 16
+    assert decode_splits(2, 32, 8, 8192, **tma) == 8           # 16 clusters of 16 would not find room
+    assert decode_splits(1, 32, 8, 8192, slots=296, cluster_sizes=(2, 4, 8)) == 8
+    for rows in (1, 3, 8, 40):
+        for ctx in (1, 63, 64, 65, 1000, 20000, 131072):
+            for window in (0, 100):
+                n = decode_splits(rows, 32, 8, ctx, window, **tma)
+                keys = min(ctx, window) if window else ctx
+                assert 1 <= n <= max(1, -(-keys // 64))          # never more slices than tiles of 64 keys
+    assert decode_splits(1, 8, 8, 300, window=0, **tma) == decode_splits(1, 8, 8, 100000, window=300, **tma)
