@@ -52,7 +52,7 @@ class LLM:
                  max_cache_tokens: Optional[int] = None, max_num_seqs: int = 64,
                  max_num_batched_tokens: int = 2048, prefill_chunk: int = 512,
                  max_model_len: Optional[int] = None, gpu_memory_fraction: float = 0.85,
-                 device: str = "cuda:0", runner: Optional[ModelRunner] = None):
+                 device: str = "cuda:0", runner: Optional[ModelRunner] = None, sampler=None):
         if runner is None:
             if model is None:
                 raise ValueError("LLM needs a model folder (or a ready runner)")
@@ -70,8 +70,10 @@ class LLM:
         e = runner.engine
         self.scheduler = Scheduler(runner.cache, e.max_num_seqs, e.max_num_batched_tokens,
                                    e.prefill_chunk, runner.max_model_len)
-        from ..sampling.sampler import Sampler
-        self.sampler = Sampler(runner.device, e.max_num_seqs)
+        if sampler is None:
+            from ..sampling.sampler import Sampler
+            sampler = Sampler(runner.device, e.max_num_seqs)
+        self.sampler = sampler
         self._ids = itertools.count()
         self._inflight: Optional[_InFlight] = None
         self.stats = {"steps": 0, "prompt_tokens": 0, "tokens_generated": 0, "preemptions": 0,
@@ -174,7 +176,10 @@ class LLM:
         if self._inflight is prev:
             self._inflight = None
         for req in finished:
-            self.runner.finish(req.request_id)
+            # a request can end while it holds nothing: preempted (pages given back) while the
+            # step with its last row was still in flight, and that row's token was a stop token
+            if self.runner.has(req.request_id):
+                self.runner.finish(req.request_id)
         return finished
 
     @staticmethod
