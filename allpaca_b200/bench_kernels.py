@@ -3,6 +3,7 @@
     python -m allpaca_b200.bench_kernels gemm --m 8 --n 6144 --k 4096 [--splits S] [--partials] [--swiglu]
     python -m allpaca_b200.bench_kernels attention --batch 8 --context 4096
     python -m allpaca_b200.bench_kernels prefill-attention --tokens 2048
+    python -m allpaca_b200.bench_kernels versus-reference      # a table: ours against the reference's own kernels
 
 Each call works on the next of several copies of its large operand (together larger than
 the 126 MB L2), so every timed launch reads its bytes from HBM.  Times are CUDA events
@@ -117,19 +118,10 @@ def bench_attention(args) -> dict:
             bufs[key] = torch.empty(shape, device="cuda", dtype=dtype)
         return bufs[key]
 
-    zeroed = {}
-
-    def zero_scratch(name, shape, dtype):
-        key = (name, tuple(shape))
-        if key not in zeroed:
-            zeroed[key] = torch.zeros(shape, device="cuda", dtype=dtype)
-        return zeroed[key]
-
     def fn(i):
         cache, table = caches[i % copies]
         ops.attention(q, out, cache, table, seq, pos, nh, nkv, hd, 1.0 / math.sqrt(hd), 0, seq_start=start,
-                      query_lens=[1] * B, max_context=C, scratch=scratch,
-                      zero_scratch=zero_scratch if args.fused_merge else None, use_tma=not args.cp_async)
+                      query_lens=[1] * B, max_context=C, scratch=scratch, use_tma=not args.cp_async)
     us = _time(fn, args.iters, args.warmup, not args.no_graph)
     return {"kernel": "attention_split+merge" if args.cp_async else "attention_split_tma+merge", "batch": B, "context": C, "heads": nh, "kv_heads": nkv,
             "head_dim": hd, "splits": ops.decode_splits(B, nh, nkv, C, slots=444 if args.cp_async else 296,
@@ -156,6 +148,148 @@ def bench_prefill_attention(args) -> dict:
     flops = 4.0 * nh * hd * T * (T + 1) / 2
     return {"kernel": "attention_tile" if args.mma_sync else "attention_tcgen05", "query_tiles": args.query_tiles, "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
             "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
+
+
+def bench_versus_reference(args) -> dict:
+    """The operations of a decode step at the Llama-3.1-8B sizes (8 rows; 2048 keys), and the prompt
+    attention of 512 tokens: the reference's own CUDA kernels (32-bit float, its only precision;
+    ``baseline/reference_kernels.py``) against this engine's kernel of the same operation in 32-bit
+    and in bfloat16 (what serving runs).  Launched from the host one after the other, CUDA events
+    around ``--iters`` launches; large operands rotate over copies that together exceed L2."""
+    import os
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from allpaca_b200 import ops
+    from baseline import reference_kernels
+    ref = reference_kernels.load()
+    if ref is None:
+        return {"unavailable": "the reference's kernels are not built here"}
+    H, NH, NKV, HD, INTER, M, KEYS = 4096, 32, 8, 128, 14336, 8, 2048
+    rows = []
+
+    def timed(fn):
+        return round(_time(fn, args.iters, args.warmup, graph=False), 2)
+
+    def weights(n, k, dtype):
+        copies = max(2, int(math.ceil(300e6 / (n * k * torch.empty((), dtype=dtype).element_size()))))
+        return [(torch.randn(n, k, device="cuda") * 0.02).to(dtype) for _ in range(min(copies, 8))]
+
+    for name, n, k in (("QKV product", (NH + 2 * NKV) * HD, H), ("O product", H, NH * HD),
+                       ("gate and up products + SiLU*up", 2 * INTER, H), ("down product", H, INTER)):
+        w32 = weights(n, k, torch.float32)
+        a32 = torch.randn(M, k, device="cuda")
+        out32 = torch.empty(M, n, device="cuda")
+        if name.startswith("gate"):
+            act = torch.empty(M, INTER, device="cuda")
+
+            g32, u32 = torch.empty(M, INTER, device="cuda"), torch.empty(M, INTER, device="cuda")
+
+            def theirs(i):
+                w = w32[i % len(w32)]
+                ref.gemm_nt(a32, w[:INTER], g32)
+                ref.gemm_nt(a32, w[INTER:], u32)
+                ref.silu_mul(g32, u32, act)
+
+            def ours32(i):
+                ops.gemm_simt(a32, w32[i % len(w32)], out32)
+                ops.swiglu(out32, act)
+        else:
+            def theirs(i):
+                ref.gemm_nt(a32, w32[i % len(w32)], out32)
+
+            def ours32(i):
+                ops.gemm_simt(a32, w32[i % len(w32)], out32)
+        t_ref, t32 = timed(theirs), timed(ours32)
+        del w32
+        w16 = weights(n, k, torch.bfloat16)
+        a16 = a32.bfloat16()
+        S = ops.gemm_tc_splits(M, n, k)
+        if name.startswith("gate"):
+            out16 = torch.empty(M, INTER, device="cuda", dtype=torch.bfloat16)
+
+            def ours16(i):
+                ops.gemm_tc(a16, w16[i % len(w16)], out16, S, reduce=S > 1, pairs=True)
+        else:
+            out16 = torch.empty(M, n, device="cuda", dtype=torch.bfloat16)
+
+            def ours16(i):
+                ops.gemm_tc(a16, w16[i % len(w16)], out16, S, reduce=S > 1)
+        rows.append((f"{name}, {M} x {n} x {k}", t_ref, t32, timed(ours16)))
+        del w16
+    # norm
+    x, w = torch.randn(M, H, device="cuda"), torch.ones(H, device="cuda")
+    o32, o16 = torch.empty(M, H, device="cuda"), torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+    rows.append((f"RMSNorm, {M} x {H}", timed(lambda i: ref.rmsnorm_rows(x, w, o32, 1e-5)),
+                 timed(lambda i: ops.add_rmsnorm(x, w, 1e-5, o32)), timed(lambda i: ops.add_rmsnorm(x, w, 1e-5, o16))))
+    # rotation of 8 rows at one position each (the reference: one launch per row, as its decode does)
+    q, k = torch.randn(M, NH, HD, device="cuda"), torch.randn(M, NKV, HD, device="cuda")
+    qkv = torch.randn(M, (NH + 2 * NKV) * HD, device="cuda")
+    pos = torch.arange(100, 100 + M, device="cuda", dtype=torch.int32)
+    inv = torch.rand(HD // 2, device="cuda")
+    table = torch.empty(M, HD // 2, 2, device="cuda")
+    q_out32 = torch.empty(M, NH * HD, device="cuda")
+    q_out16 = torch.empty(M, NH * HD, device="cuda", dtype=torch.bfloat16)
+    qkv16 = qkv.bfloat16()
+
+    def their_rope(i):
+        for r in range(M):
+            ref.rope_adjacent(q[r:r + 1], k[r:r + 1], 100 + r, 500000.0)
+
+    def our_rope(out, src):
+        def fn(i):
+            ops.rope_table(pos, inv, table)
+            ops.rope_kv_store(src, out, None, pos, None, None, table, 0, NH, NKV, HD)
+        return fn
+    rows.append((f"rotation of Q and K, {M} rows", timed(their_rope), timed(our_rope(q_out32, qkv)),
+                 timed(our_rope(q_out16, qkv16))))
+    # decode attention: 8 sequences of 2048 keys (the reference: one call per sequence)
+    kk, vv = torch.randn(M, KEYS, NKV, HD, device="cuda"), torch.randn(M, KEYS, NKV, HD, device="cuda")
+    qd = torch.randn(M, 1, NH, HD, device="cuda")
+    od = torch.empty_like(qd)
+
+    def their_decode(i):
+        for b in range(M):
+            ref.attention(qd[b], kk[b], vv[b], od[b], causal=True)
+    P = 16
+    seq = torch.arange(M, device="cuda", dtype=torch.int32)
+    start = torch.arange(M + 1, device="cuda", dtype=torch.int32)
+    last = torch.full((M,), KEYS - 1, device="cuda", dtype=torch.int32)
+    bufs = {}
+
+    def scratch(name, shape, dtype):
+        return bufs.setdefault((name, tuple(shape)), torch.empty(shape, device="cuda", dtype=dtype))
+
+    def our_decode(dtype):
+        cache, tbl = _paged(M, KEYS, NKV, HD, P)
+        cache = cache.to(dtype)
+        qq = torch.randn(M, NH * HD, device="cuda").to(dtype)
+        oo = torch.empty_like(qq)
+        return lambda i: ops.attention(qq, oo, cache, tbl, seq, last, NH, NKV, HD, HD ** -0.5, 0, seq_start=start,
+                                       query_lens=[1] * M, max_context=KEYS, scratch=scratch)
+    rows.append((f"decode attention, {M} sequences x {KEYS} keys", timed(their_decode),
+                 timed(our_decode(torch.float32)), timed(our_decode(torch.bfloat16))))
+    # prompt attention of 512 tokens
+    T = 512
+    qp, kp, vp = (torch.randn(T, n, HD, device="cuda") for n in (NH, NKV, NKV))
+    op = torch.empty_like(qp)
+
+    def our_prompt(dtype):
+        cache, tbl = _paged(1, T, NKV, HD, P)
+        cache = cache.to(dtype)
+        qq = torch.randn(T, NH * HD, device="cuda").to(dtype)
+        oo = torch.empty_like(qq)
+        ts = torch.zeros(T, device="cuda", dtype=torch.int32)
+        st = torch.tensor([0, T], device="cuda", dtype=torch.int32)
+        ps = torch.arange(T, device="cuda", dtype=torch.int32)
+        return lambda i: ops.attention(qq, oo, cache, tbl, ts, ps, NH, NKV, HD, HD ** -0.5, 0, seq_start=st,
+                                       query_lens=[T], max_context=T)
+    rows.append((f"prompt attention, {T} tokens, causal", timed(lambda i: ref.attention(qp, kp, vp, op, causal=True)),
+                 timed(our_prompt(torch.float32)), timed(our_prompt(torch.bfloat16))))
+    ops.check_kernel_status()
+    print("| operation | reference kernel (32-bit), us | ours 32-bit, us | ours bfloat16, us | reference / ours bfloat16 |")
+    print("|---|---|---|---|---|")
+    for name, a, b, c in rows:
+        print(f"| {name} | {a} | {b} | {c} | {a / c:.1f}x |")
+    return {"rows": [{"operation": n, "reference_us": a, "ours_float32_us": b, "ours_bfloat16_us": c} for n, a, b, c in rows]}
 
 
 def main(argv=None) -> int:
@@ -186,8 +320,6 @@ def main(argv=None) -> int:
             s.add_argument("--batch", type=int, default=8)
             s.add_argument("--context", type=int, default=4096)
             s.add_argument("--tokens", type=int, default=2048)
-            s.add_argument("--fused-merge", action="store_true",
-                           help="cp.async kernel: the last slice to arrive combines them all")
             s.add_argument("--cp-async", action="store_true", help="decode: the cp.async kernel instead of the TMA one")
             s.add_argument("--splits", type=int, default=0, help="key slices (0: the kernel's own plan)")
             s.add_argument("--mma-sync", action="store_true", help="prompt attention with the mma.sync tile kernel")
@@ -195,8 +327,12 @@ def main(argv=None) -> int:
                            help="prompt attention on tcgen05: query tiles to a CTA (auto: by the number of CTAs)")
             s.add_argument("--scattered-pages", action="store_true",
                            help="block tables in random order instead of rising page numbers")
+    s = sub.add_parser("versus-reference")
+    s.add_argument("--iters", type=int, default=20)
+    s.add_argument("--warmup", type=int, default=3)
     args = p.parse_args(argv)
-    fn = {"gemm": bench_gemm, "attention": bench_attention, "prefill-attention": bench_prefill_attention}[args.what]
+    fn = {"gemm": bench_gemm, "attention": bench_attention, "prefill-attention": bench_prefill_attention,
+          "versus-reference": bench_versus_reference}[args.what]
     print(json.dumps(fn(args)))
     return 0
 

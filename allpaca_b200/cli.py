@@ -50,7 +50,11 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--top-k", type=int)
     g.add_argument("--top-p", type=float)
     g.add_argument("--stop-token-ids", default="", help="token ids that end a reply")
-    g.add_argument("--dtype", choices=["bfloat16", "float32"], default=None)
+    g.add_argument("--dtype", choices=["bfloat16", "float32", "auto"], default=None,
+                   help="default: what the model folder's config.json names as torch_dtype")
+    g.add_argument("--float32-weights", choices=["keep", "round", "refuse"], default="keep",
+                   help="matrices stored in 32-bit under --dtype bfloat16: keep them (slow, announced), "
+                        "round them to bfloat16 at load, or refuse the checkpoint")
     g.add_argument("--page-tokens", "--page-size", dest="page_tokens", type=int, help="tokens per cache page")
     g.add_argument("--chunk-tokens", "--prefill-chunk", dest="chunk_tokens", type=int,
                    help="largest portion of one prompt per step")
@@ -118,7 +122,7 @@ def cmd_generate(args) -> int:
         model_path = tmp.name
     if not model_path:
         raise SystemExit("allpaca generate: give --model DIR or --synthetic [PRESET]")
-    llm = LLM(model=model_path, dtype=args.dtype or "bfloat16", seed=seed,
+    llm = LLM(model=model_path, dtype=args.dtype or "auto", seed=seed, float32_weights=args.float32_weights,
               page_size=pick(args.page_tokens, sec("kv").get("page_tokens", 16)),
               prefill_chunk=pick(args.chunk_tokens, sec("prefill").get("chunk_tokens", 512)),
               max_num_seqs=pick(args.max_active_requests, sec("engine").get("max_active_requests", 64)),

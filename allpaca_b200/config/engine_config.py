@@ -43,6 +43,7 @@ class EngineConfig:
     seed: int = 0xA110ACA                   # crates/allpaca-core/src/sampling.rs:6
     use_cuda_graphs: bool = True
     device: str = "cuda:0"
+    float32_weights: str = "keep"           # matrices stored in 32-bit under a bfloat16 engine: keep | round | refuse
 
     def validate(self) -> None:
         self.dtype = parse_dtype(self.dtype)
@@ -53,6 +54,8 @@ class EngineConfig:
             raise ConfigError("num_pages must be positive")
         if not (0.0 < self.gpu_memory_fraction <= 1.0):
             raise ConfigError("gpu_memory_fraction must be in (0, 1]")
+        if self.float32_weights not in ("keep", "round", "refuse"):
+            raise ConfigError(f"float32_weights must be keep, round or refuse, not {self.float32_weights!r}")
         if self.max_num_batched_tokens < self.max_num_seqs:
             raise ConfigError("max_num_batched_tokens must allow one row per running request "
                               f"({self.max_num_batched_tokens} < {self.max_num_seqs})")

@@ -49,8 +49,6 @@ struct AttnTcParams {
     const int* positions;
     float* part_o;       // [nsplit][T][nh][HD]
     float* part_ml;      // [nsplit][T][nh][2]
-    int* counters;       // [T][gridDim.y] arrival counts of the slices, all zero between launches;
-                         // nullptr: a separate kernel combines the slices
     size_t page_stride;
     int max_blocks, nseq, T, nh, nkv, P, window;
     int tokens_per_tile, heads_per_chunk, n_chunks, nsplit;
@@ -471,38 +469,6 @@ attention_split_kernel(const AttnTcParams p) {
             }
         }
     }
-    if (p.nsplit == 1 || p.counters == nullptr) return;
-    // The slice that arrives last combines them all: no CTA waits for another.
-    __shared__ int s_last;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int* c = p.counters + (size_t)row * gridDim.y + blockIdx.y;
-        const int arrived = atomicAdd(c, 1);
-        s_last = arrived == p.nsplit - 1;
-        if (s_last) *c = 0;                  // every slice has arrived: ready for the next launch
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    for (int idx = threadIdx.x; idx < nheads * HD; idx += ATC_THREADS) {
-        const int r = idx / HD, d = idx - r * HD;
-        const size_t orow = (size_t)row * p.nh + head0 + r;
-        float M = -INFINITY;
-        for (int z = 0; z < p.nsplit; ++z) M = fmaxf(M, __ldcg(p.part_ml + ((size_t)z * p.T * p.nh + orow) * 2));
-        float L = 0.f, O = 0.f;
-        if (M != -INFINITY) {
-            for (int z = 0; z < p.nsplit; ++z) {
-                const size_t prow = (size_t)z * p.T * p.nh + orow;
-                const float lz = __ldcg(p.part_ml + prow * 2 + 1);
-                if (lz <= 0.f) continue;
-                const float f = lz * exp2f(__ldcg(p.part_ml + prow * 2) - M);
-                L += f;
-                O += __ldcg(p.part_o + prow * HD + d) * f;
-            }
-        }
-        p.out[orow * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
-    }
 }
 
 // combine the slices of the split kernel: grid (rows, heads)
@@ -542,14 +508,13 @@ static int configure_smem(const void* kern, int bytes) {
 
 // mode 0: tile kernel over `total_tiles` query tiles (prompt portions, mixed batches);
 // mode 1: split kernel, one row per sequence, `nsplit` key slices; part_o/part_ml are
-//         scratch of nsplit*T*nh*HD and nsplit*T*nh*2 floats (unused for nsplit == 1);
-//         counters: T * nkv * ceil(group/16) ints that are zero on entry and zero again on
-//         exit, or nullptr to combine the slices with a second kernel.
+//         scratch of nsplit*T*nh*HD and nsplit*T*nh*2 floats (unused for nsplit == 1), which
+//         a second kernel combines.
 AP_EXPORT int ap_attention_tc(const void* q, void* out, const void* cache, const int* block_table,
                               int max_blocks, const int* seq_start, const int* positions, int nseq, int T,
                               int nh, int nkv, int hd, int P, long long page_stride, float scale, int window,
                               int mode, int total_tiles, int nsplit, float* part_o, float* part_ml,
-                              int* counters, cudaStream_t stream) {
+                              cudaStream_t stream) {
     AP_REQUIRE(hd == HD, "attention: this library was compiled for head size %d, not %d", HD, hd);
     AP_REQUIRE(T >= 0 && nseq >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0 && P > 0 && max_blocks > 0,
                "attention: bad sizes T=%d heads=%d kv_heads=%d page=%d", T, nh, nkv, P);
@@ -557,7 +522,7 @@ AP_EXPORT int ap_attention_tc(const void* q, void* out, const void* cache, const
     AttnTcParams p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.cache = (const bf16*)cache;
     p.block_table = block_table; p.seq_start = seq_start; p.positions = positions;
-    p.part_o = part_o; p.part_ml = part_ml; p.counters = counters; p.page_stride = (size_t)page_stride;
+    p.part_o = part_o; p.part_ml = part_ml; p.page_stride = (size_t)page_stride;
     p.max_blocks = max_blocks; p.nseq = nseq; p.T = T; p.nh = nh; p.nkv = nkv; p.P = P; p.window = window;
     p.scale_log2 = scale * LOG2E;
     const int reps = nh / nkv;
@@ -595,7 +560,7 @@ AP_EXPORT int ap_attention_tc(const void* q, void* out, const void* cache, const
     dim3 grid(T, nkv * p.n_chunks, nsplit);
     AP_CHECK_PDL_LAUNCH("attention_split",
                         ap_launch_pdl(attention_split_kernel, grid, dim3(ATC_THREADS), smem_bytes, stream, p));
-    if (nsplit > 1 && counters == nullptr) {
+    if (nsplit > 1) {
         dim3 mgrid(T, nh);
         AP_CHECK_PDL_LAUNCH("attention_merge",
                             ap_launch_pdl(attention_merge_kernel, mgrid, dim3(HD < 128 ? 64 : 128), 0, stream,
@@ -983,7 +948,7 @@ AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cach
     AttnTcParams p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.cache = (const bf16*)cache;
     p.block_table = block_table; p.seq_start = nullptr; p.positions = positions;
-    p.part_o = part_o; p.part_ml = part_ml; p.counters = nullptr; p.page_stride = (size_t)page_stride;
+    p.part_o = part_o; p.part_ml = part_ml; p.page_stride = (size_t)page_stride;
     p.max_blocks = max_blocks; p.nseq = T; p.T = T; p.nh = nh; p.nkv = nkv; p.P = P; p.window = window;
     p.scale_log2 = scale * LOG2E;
     const int reps = nh / nkv;
@@ -1089,7 +1054,6 @@ AP_EXPORT int ap_attention_decode_static(const void* q, void* out, const void* c
     p.block_table = block_table; p.seq_start = nullptr; p.positions = positions;
     p.part_o = scratch;
     p.part_ml = scratch + (size_t)nsplit * T * num_heads * HD;
-    p.counters = nullptr;
     p.page_stride = (size_t)page_stride;
     p.max_blocks = max_blocks; p.nseq = T; p.T = T; p.nh = num_heads; p.nkv = num_kv_heads; p.P = page_size;
     p.window = window; p.scale_log2 = scale * LOG2E;

@@ -14,7 +14,7 @@
 // ---------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                                    float* __restrict__ x, int H, int V) {
+                                    float* __restrict__ x, int H, int V, float scale) {
     const int t = blockIdx.x;
     ap_pdl_trigger();
     ap_pdl_wait();
@@ -24,11 +24,11 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const TW* __
     tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
     const TW* src = table + (size_t)tok * H;
     float* dst = x + (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ap_to_float(src[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ap_to_float(src[i]) * scale;
 }
 
 AP_EXPORT int ap_embed_gather(const int* tokens, const void* table, int table_dtype, float* x,
-                              int T, int H, int V, cudaStream_t stream) {
+                              int T, int H, int V, float scale, cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && H > 0 && V > 0, "embed_gather: bad sizes T=%d H=%d V=%d", T, H, V);
     if (T == 0) return AP_OK;
     const int threads = H >= 1024 ? 256 : 128;
@@ -36,9 +36,9 @@ AP_EXPORT int ap_embed_gather(const int* tokens, const void* table, int table_dt
     // before it on the stream has finished.  Kernels later in the step may therefore read what
     // earlier steps wrote (the cache) ahead of their own dependency wait.
     if (table_dtype == AP_F32)
-        embed_gather_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, x, H, V);
+        embed_gather_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, x, H, V, scale);
     else if (table_dtype == AP_BF16)
-        embed_gather_kernel<bf16><<<T, threads, 0, stream>>>(tokens, (const bf16*)table, x, H, V);
+        embed_gather_kernel<bf16><<<T, threads, 0, stream>>>(tokens, (const bf16*)table, x, H, V, scale);
     else
         AP_REQUIRE(false, "embed_gather: unknown table dtype %d", table_dtype);
     AP_CHECK_LAUNCH("embed_gather");
@@ -178,6 +178,74 @@ AP_EXPORT int ap_residual_add(float* x, const float* delta, int S, long long del
 }
 
 // ---------------------------------------------------------------------------
+// bias and logit transforms, for decoders that have them (none on the plain Llama path):
+//   bias_add:        out[t, n] += bias[n]                       (out in 32-bit or bfloat16)
+//   logit_transform: z = (logit + bias[n]) * scale;  z = cap * tanh(z / cap) when cap > 0
+// ---------------------------------------------------------------------------
+template <typename TO, typename TB>
+__global__ void bias_add_kernel(TO* __restrict__ out, const TB* __restrict__ bias, size_t n, int N) {
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = ap_from_float<TO>(ap_to_float(out[i]) + ap_to_float(bias[i % N]));
+}
+
+AP_EXPORT int ap_bias_add(void* out, int out_dtype, const void* bias, int bias_dtype, int T, int N,
+                          cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && N > 0 && out && bias, "bias_add: bad arguments T=%d N=%d", T, N);
+    if (T == 0) return AP_OK;
+    const size_t n = (size_t)T * N;
+    const int threads = 256;
+    size_t blocks = (n + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+#define LAUNCH(TO, TB)                                                                                    \
+    AP_CHECK_PDL_LAUNCH("bias_add", ap_launch_pdl(bias_add_kernel<TO, TB>, dim3((unsigned)blocks), dim3(threads), 0, \
+                                                  stream, (TO*)out, (const TB*)bias, n, N))
+    if (out_dtype == AP_F32 && bias_dtype == AP_F32) LAUNCH(float, float);
+    else if (out_dtype == AP_F32 && bias_dtype == AP_BF16) LAUNCH(float, bf16);
+    else if (out_dtype == AP_BF16 && bias_dtype == AP_F32) LAUNCH(bf16, float);
+    else if (out_dtype == AP_BF16 && bias_dtype == AP_BF16) LAUNCH(bf16, bf16);
+    else AP_REQUIRE(false, "bias_add: unknown dtypes out=%d bias=%d", out_dtype, bias_dtype);
+#undef LAUNCH
+    return AP_OK;
+}
+
+template <typename TB>
+__global__ void logit_transform_kernel(float* __restrict__ logits, const TB* __restrict__ bias, size_t n, int V,
+                                       float scale, float cap) {
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float z = logits[i];
+        if (bias) z += ap_to_float(bias[i % V]);
+        z *= scale;
+        if (cap > 0.f) z = cap * tanhf(z / cap);
+        logits[i] = z;
+    }
+}
+
+AP_EXPORT int ap_logit_transform(float* logits, const void* bias, int bias_dtype, int R, int V, float scale,
+                                 float softcap, cudaStream_t stream) {
+    AP_REQUIRE(R >= 0 && V > 0 && logits, "logit_transform: bad arguments R=%d V=%d", R, V);
+    if (R == 0) return AP_OK;
+    const size_t n = (size_t)R * V;
+    const int threads = 256;
+    size_t blocks = (n + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (bias == nullptr || bias_dtype == AP_F32)
+        AP_CHECK_PDL_LAUNCH("logit_transform", ap_launch_pdl(logit_transform_kernel<float>, dim3((unsigned)blocks),
+                                                             dim3(threads), 0, stream, logits, (const float*)bias, n,
+                                                             V, scale, softcap));
+    else if (bias_dtype == AP_BF16)
+        AP_CHECK_PDL_LAUNCH("logit_transform", ap_launch_pdl(logit_transform_kernel<bf16>, dim3((unsigned)blocks),
+                                                             dim3(threads), 0, stream, logits, (const bf16*)bias, n,
+                                                             V, scale, softcap));
+    else
+        AP_REQUIRE(false, "logit_transform: unknown bias dtype %d", bias_dtype);
+    return AP_OK;
+}
+
+// ---------------------------------------------------------------------------
 // rotary embedding of Q and K + write of K and V into cache pages.
 //   in:  [S, T, (nh + 2*nkv) * hd]  (S partial sums in 32-bit, or S == 1 in TI)
 //   q_out: [T, nh*hd]
@@ -220,6 +288,32 @@ AP_EXPORT int ap_rope_table(const int* positions, const float* inv_freq, float* 
     return AP_OK;
 }
 
+// A page is first written at its slot 0 (a request's positions are contiguous).  The threads
+// that store the token of slot 0 also clear the slots of the page behind the last one this step
+// writes (`last_slot`, counted from slot 0; the slots up to it belong to other rows of this
+// launch): the attention kernels load whole pages and weigh what lies behind a row's position
+// with a probability of exactly zero, which only gives zero if it is finite, and a page that
+// was given back keeps its last owner's values, whatever they were.
+template <typename TO>
+__device__ __forceinline__ void clear_page_tail(TO* __restrict__ page, int last_slot, int nkv, int hd, int P,
+                                                int worker, int workers) {
+    const int first = last_slot + 1;
+    if (first >= P) return;
+    const int per_plane = (P - first) * hd;               // the cleared slots of one head are contiguous
+    const int total = 2 * nkv * per_plane;
+    if (sizeof(TO) == 2 && hd % 8 == 0 && (((uintptr_t)page) & 15) == 0) {
+        for (int i = worker; i < total / 8; i += workers) {
+            const int plane = (i * 8) / per_plane, e = i * 8 - plane * per_plane;
+            *reinterpret_cast<uint4*>(page + ((size_t)plane * P + first) * hd + e) = make_uint4(0, 0, 0, 0);
+        }
+    } else {
+        for (int i = worker; i < total; i += workers) {
+            const int plane = i / per_plane, e = i - plane * per_plane;
+            page[((size_t)plane * P + first) * hd + e] = ap_from_float<TO>(0.f);
+        }
+    }
+}
+
 // One thread per pair of elements: (nh + nkv) * half rotated pairs, then nkv * half pairs of V.
 #define ROPE_THREADS 256
 template <typename TI, typename TO>
@@ -230,7 +324,8 @@ rope_kv_store_kernel(const TI* __restrict__ in, int S, size_t in_stride,
                      const int* __restrict__ token_seq,
                      const int* __restrict__ block_table, int max_blocks,
                      const float2* __restrict__ cos_sin, int pairing,
-                     int nh, int nkv, int hd, int P, size_t page_stride) {
+                     int nh, int nkv, int hd, int P, size_t page_stride,
+                     const int* __restrict__ context_lens) {
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int item = blockIdx.y * ROPE_THREADS + threadIdx.x;
@@ -238,14 +333,18 @@ rope_kv_store_kernel(const TI* __restrict__ in, int S, size_t in_stride,
     ap_pdl_wait();
     const int rot_pairs = (nh + nkv) * half;
     const int v_pairs = cache ? nkv * half : 0;
-    if (item >= rot_pairs + v_pairs) return;
     const size_t row = (size_t)t * (nh + 2 * nkv) * hd;
     int page = -1, off = 0;
     if (cache) {
         const int ipos = positions[t];
-        page = block_table[(size_t)token_seq[t] * max_blocks + ipos / P];
+        const int seq = token_seq[t];
+        page = block_table[(size_t)seq * max_blocks + ipos / P];
         off = ipos % P;
+        if (context_lens && off == 0 && page >= 0)
+            clear_page_tail(cache + (size_t)page * page_stride, context_lens[seq] - 1 - ipos, nkv, hd, P,
+                            blockIdx.y * ROPE_THREADS + threadIdx.x, gridDim.y * ROPE_THREADS);
     }
+    if (item >= rot_pairs + v_pairs) return;
     if (item < rot_pairs) {
         const int head = item / half, i = item - head * half;
         if (head >= nh && page < 0) return;
@@ -282,7 +381,7 @@ rope_kv_store_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ q_ou
                             const int* __restrict__ positions, const int* __restrict__ token_seq,
                             const int* __restrict__ block_table, int max_blocks,
                             const float2* __restrict__ cos_sin, int nh, int nkv, int hd, int P,
-                            size_t page_stride) {
+                            size_t page_stride, const int* __restrict__ context_lens) {
     const int t = blockIdx.x;
     const int half = hd >> 1, h8 = half >> 3;             // groups of 8 pairs per head
     const int item = blockIdx.y * ROPE_THREADS + threadIdx.x;
@@ -290,14 +389,18 @@ rope_kv_store_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ q_ou
     ap_pdl_wait();
     const int rot_items = (nh + nkv) * h8;
     const int v_items = cache ? nkv * (hd >> 3) : 0;
-    if (item >= rot_items + v_items) return;
     const size_t row = (size_t)t * (nh + 2 * nkv) * hd;
     int page = -1, off = 0;
     if (cache) {
         const int ipos = positions[t];
-        page = block_table[(size_t)token_seq[t] * max_blocks + ipos / P];
+        const int seq = token_seq[t];
+        page = block_table[(size_t)seq * max_blocks + ipos / P];
         off = ipos % P;
+        if (context_lens && off == 0 && page >= 0)
+            clear_page_tail(cache + (size_t)page * page_stride, context_lens[seq] - 1 - ipos, nkv, hd, P,
+                            blockIdx.y * ROPE_THREADS + threadIdx.x, gridDim.y * ROPE_THREADS);
     }
+    if (item >= rot_items + v_items) return;
     if (item < rot_items) {
         const int head = item / h8, i = (item - head * h8) * 8;
         if (head >= nh && page < 0) return;
@@ -336,7 +439,7 @@ AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in
                                void* cache, int act_dtype, const int* positions, const int* token_seq,
                                const int* block_table, int max_blocks, const float* cos_sin, int pairing,
                                int T, int nh, int nkv, int hd, int P, long long page_stride,
-                               cudaStream_t stream) {
+                               const int* context_lens, cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && nh > 0 && nkv >= 0 && hd > 0 && (hd % 2) == 0 && S >= 1,
                "rope_kv_store: bad sizes T=%d heads=%d kv_heads=%d head_dim=%d S=%d", T, nh, nkv, hd, S);
     AP_REQUIRE(pairing == 0 || pairing == 1, "rope_kv_store: unknown pairing %d", pairing);
@@ -354,7 +457,7 @@ AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in
         AP_CHECK_PDL_LAUNCH("rope_kv_store", ap_launch_pdl(
             rope_kv_store_bf16x8_kernel, grid8, dim3(ROPE_THREADS), 0, stream, (const bf16*)in, (bf16*)q_out,
             (bf16*)cache, positions, token_seq, block_table, max_blocks, (const float2*)cos_sin, nh, nkv, hd, P,
-            (size_t)page_stride));
+            (size_t)page_stride, context_lens));
         return AP_OK;
     }
     const int items = (nh + nkv) * (hd / 2) + (cache ? nkv * (hd / 2) : 0);
@@ -364,7 +467,8 @@ AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in
     AP_CHECK_PDL_LAUNCH("rope_kv_store", ap_launch_pdl(                                             \
         rope_kv_store_kernel<TI, TO>, grid, dim3(ROPE_THREADS), 0, stream,                          \
         (const TI*)in, S, (size_t)in_stride, (TO*)q_out, (TO*)cache, positions, token_seq,         \
-        block_table, max_blocks, (const float2*)cos_sin, pairing, nh, nkv, hd, P, (size_t)page_stride))
+        block_table, max_blocks, (const float2*)cos_sin, pairing, nh, nkv, hd, P, (size_t)page_stride, \
+        context_lens))
     if (in_dtype == AP_F32 && act_dtype == AP_F32) LAUNCH(float, float);
     else if (in_dtype == AP_F32 && act_dtype == AP_BF16) LAUNCH(float, bf16);
     else if (in_dtype == AP_BF16 && act_dtype == AP_BF16) {

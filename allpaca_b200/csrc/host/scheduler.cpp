@@ -81,6 +81,22 @@ void Scheduler::reserve(const SchedRequest& r, int64_t count) {
     for (int g = 0; g < cache_->num_groups(); ++g) reserved_[g] += missing[g];
 }
 
+// Whether a request that has not begun may be admitted with `left` tokens still to run: a group
+// that keeps every key must have room for all of them now (else the request would be admitted
+// only to be preempted); a group with a window needs room for the most it ever holds at once,
+// the same bound add() checks, since pages the window has passed come back after every step.
+bool Scheduler::admission_fits(int64_t left) const {
+    for (int g = 0; g < cache_->num_groups(); ++g) {
+        const GroupLayout& layout = cache_->group(g);
+        int64_t tokens = left;
+        if (layout.window > 0)
+            tokens = std::min(left, (int64_t)layout.window + std::min(prefill_chunk_, token_budget_) + layout.page_size);
+        const int64_t pages = (tokens + layout.page_size - 1) / layout.page_size;
+        if (pages > cache_->num_free_pages(g) - reserved_[g]) return false;
+    }
+    return true;
+}
+
 // The most tokens up to `want` whose pages are free (0 if not even one).
 int64_t Scheduler::largest_fit(const SchedRequest& r, int64_t want) const {
     if (want <= 0) return 0;
@@ -182,7 +198,7 @@ int Scheduler::schedule() {
         const int64_t id = waiting_.front();
         SchedRequest& r = reqs_[id];
         const int64_t left = r.num_tokens() - r.num_computed;
-        if (!cache_->can_append(-1, left, reserved_.data())) break;
+        if (!admission_fits(left)) break;
         const int64_t count = std::min(std::min(left, budget), prefill_chunk_);
         waiting_.pop_front();
         running_.push_back(id);

@@ -100,6 +100,7 @@ public:
 
 private:
     bool fits(const SchedRequest& r, int64_t count) const;
+    bool admission_fits(int64_t left) const;
     void reserve(const SchedRequest& r, int64_t count);
     int64_t largest_fit(const SchedRequest& r, int64_t want) const;
     void preempt(int64_t id);

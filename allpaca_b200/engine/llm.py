@@ -47,12 +47,16 @@ class _InFlight:
 class LLM:
     """One model on one GPU with a continuous-batching scheduler above the step function."""
 
-    def __init__(self, model: Optional[str] = None, dtype="bfloat16", seed: Optional[int] = None,
+    def __init__(self, model: Optional[str] = None, dtype="auto", seed: Optional[int] = None,
                  page_size: int = 16, num_pages: Optional[int] = None,
                  max_cache_tokens: Optional[int] = None, max_num_seqs: int = 64,
                  max_num_batched_tokens: int = 2048, prefill_chunk: int = 512,
                  max_model_len: Optional[int] = None, gpu_memory_fraction: float = 0.85,
-                 device: str = "cuda:0", runner: Optional[ModelRunner] = None, sampler=None):
+                 device: str = "cuda:0", float32_weights: str = "keep",
+                 runner: Optional[ModelRunner] = None, sampler=None):
+        """``dtype``: ``"bfloat16"``, ``"float32"`` or ``"auto"`` (what the model folder's
+        config.json names as ``torch_dtype``).  ``float32_weights``: what a bfloat16 engine does
+        with matrices stored in 32-bit (``"keep"`` and say so, ``"round"``, ``"refuse"``)."""
         if runner is None:
             if model is None:
                 raise ValueError("LLM needs a model folder (or a ready runner)")
@@ -60,7 +64,8 @@ class LLM:
                                max_cache_tokens=max_cache_tokens, max_num_seqs=max_num_seqs,
                                max_num_batched_tokens=max_num_batched_tokens,
                                prefill_chunk=prefill_chunk, max_model_len=max_model_len,
-                               gpu_memory_fraction=gpu_memory_fraction, device=device)
+                               gpu_memory_fraction=gpu_memory_fraction, device=device,
+                               float32_weights=float32_weights)
             if seed is not None:
                 cfg.seed = seed
             runner = ModelRunner(model, cfg)

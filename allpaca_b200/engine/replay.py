@@ -29,6 +29,9 @@ def parse_args(argv: Optional[Sequence[str]] = None) -> argparse.Namespace:
                    help="most tokens live requests hold at any time (each rounded up to 64)")
     p.add_argument("--page-size", type=int, default=PAGE_SIZE)
     p.add_argument("--max-live", type=int, default=MAX_LIVE, help="requests live at a time")
+    p.add_argument("--no-graphs", action="store_true",
+                   help="launch every kernel from the host (as generation does, steps of one row per request "
+                        "are otherwise replayed as CUDA graphs from their third use on)")
     return p.parse_args(argv)
 
 
@@ -50,7 +53,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     cfg = EngineConfig(dtype=args.dtype, page_size=args.page_size,
                        num_pages=rounded // args.page_size, max_num_seqs=args.max_live,
                        max_num_batched_tokens=max(rounded, args.max_live), prefill_chunk=rounded,
-                       use_cuda_graphs=False)
+                       use_cuda_graphs=not args.no_graphs)
     runner = ModelRunner(args.model, cfg)
     for line in sys.stdin:
         line = line.strip()

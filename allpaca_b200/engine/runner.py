@@ -31,6 +31,9 @@ class ModelRunner:
                  model_config=None):
         """Load the model folder at ``model_path`` (or take a ready ``model`` whose weights
         are loaded) and set up caches for it."""
+        if engine.dtype in (None, "auto"):
+            # the type the checkpoint says it was saved in (config.json's torch_dtype)
+            engine.dtype = load_config(model_path)[1].torch_dtype if model_path else "bfloat16"
         engine.validate()
         self.engine = engine
         if not torch.cuda.is_available():
@@ -43,7 +46,7 @@ class ModelRunner:
         if model is None:
             arch, cfg = load_config(model_path)
             model = DecoderModel(arch.spec_builder(cfg), self.env)
-            load_checkpoint(model, model_path, engine.dtype, self.device)
+            load_checkpoint(model, model_path, engine.dtype, self.device, engine.float32_weights)
             model_config = cfg
         self.model = model
         self.workspace = model.env.workspace      # the buffers the model's parts use
@@ -55,14 +58,15 @@ class ModelRunner:
         self._host = None
         self._dev = None
         self._graphs: Dict[tuple, "_DecodeGraph"] = {}
+        # a part that decides on the host what to launch for a step cannot be replayed
+        self._host_control = model.host_control()
+        self.graph_replays = 0
 
     # ---- caches ---------------------------------------------------------
     def _setup_caches(self) -> None:
         e = self.engine
         self.cache_plan = self.model.cache_plan()
-        elt = torch.empty((), dtype=e.dtype).element_size()
-        page_bytes = [len(g.runs) * 2 * g.need.num_kv_heads * e.page_size * g.need.head_dim * elt
-                      for g in self.cache_plan]
+        page_bytes = [len(g.runs) * g.need.page_bytes(e.page_size, e.dtype) for g in self.cache_plan]
         if e.num_pages is not None:
             num_pages = e.num_pages
         elif e.max_cache_tokens is not None:
@@ -76,8 +80,8 @@ class ModelRunner:
         self.num_pages = int(num_pages)
         layouts = [GroupLayout(e.page_size, self.num_pages, g.need.window) for g in self.cache_plan]
         self.cache = CacheManager(layouts, e.max_num_seqs)
-        self.storages = [GroupStorage(len(g.runs), self.num_pages, g.need.num_kv_heads, e.page_size,
-                                      g.need.head_dim, e.dtype, self.device) for g in self.cache_plan]
+        self.storages = [GroupStorage(len(g.runs), self.num_pages, g.need.page_shape(e.page_size),
+                                      g.need.dtype or e.dtype, self.device) for g in self.cache_plan]
         self.states = [StateStorage(e.max_num_seqs, b, self.device) if b > 0 else None
                        for b in self.model.state_bytes()]
         self.model.bind_caches(self.cache_plan, self.storages, self.states)
@@ -129,7 +133,8 @@ class ModelRunner:
     def _graphable(self, entries: Sequence[BatchEntry]) -> bool:
         """A pure decode step (one row per request, every row's logits wanted) of a size
         graphs are kept for."""
-        return (self.engine.use_cuda_graphs and 0 < len(entries) <= self.engine.max_num_seqs
+        return (self.engine.use_cuda_graphs and not self._host_control
+                and 0 < len(entries) <= self.engine.max_num_seqs
                 and all(len(en.tokens) == 1 and list(en.want) == [0] for en in entries))
 
     def _graph_step(self, entries: Sequence[BatchEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -155,6 +160,7 @@ class ModelRunner:
         batch.max_context_len = bound
         if gs.graph is not None and gs.generation == self.workspace.generation:
             gs.graph.replay()
+            self.graph_replays += 1
             library.add_launches(gs.num_kernels)
             return gs.logits
         # A batch size that shows up once or twice (requests finishing one after another) is

@@ -18,7 +18,7 @@ from typing import Dict, List, Mapping, Optional, Tuple
 import torch
 
 from .. import ops
-from ..parts import (Block, BuildEnv, KVNeed, LayerCache, ModelSpec, Part, WeightSpec, build)
+from ..parts import (Block, BuildEnv, CacheNeed, LayerCache, ModelSpec, Part, WeightSpec, build)
 from ..parts.linear import Linear
 
 
@@ -26,7 +26,7 @@ from ..parts.linear import Linear
 class CacheGroupPlan:
     """Runs of the order that share a page pool, and what a page of theirs holds."""
 
-    need: KVNeed
+    need: CacheNeed
     runs: List[int]
 
 
@@ -38,6 +38,7 @@ class DecoderModel:
         self.final_norm = build("norm", spec.final_norm, env)
         self.embedding: Optional[torch.Tensor] = None
         self.head = Linear(env, spec.vocab_size, spec.hidden_size)
+        self.head_bias: Optional[torch.Tensor] = None
         self._validate_order()
         self.caches: List[LayerCache] = [LayerCache() for _ in spec.order]
 
@@ -58,6 +59,8 @@ class DecoderModel:
             s.head_name: (WeightSpec((s.vocab_size, s.hidden_size), "linear",
                                      optional=True), None, "head"),
         }
+        if s.head_bias_name:
+            out[s.head_bias_name] = (WeightSpec((s.vocab_size,), "bias"), None, "head_bias")
         for name, ws in self.final_norm.weights().items():
             out[s.final_norm_prefix + name] = (ws, self.final_norm, name)
         for block, prefix in zip(self.blocks, s.layer_prefixes):
@@ -84,6 +87,7 @@ class DecoderModel:
             self.head.load(self.embedding)
         else:
             self.head.load(tensors[s.head_name])
+        self.head_bias = tensors[s.head_bias_name].contiguous() if s.head_bias_name else None
 
     # ---- caches ---------------------------------------------------------
     def cache_plan(self) -> List[CacheGroupPlan]:
@@ -92,7 +96,7 @@ class DecoderModel:
         for r, run in enumerate(self.spec.order):
             if run.cache_from is not None:
                 continue
-            need = self.blocks[run.layer].mixer.kv_need()
+            need = self.blocks[run.layer].mixer.cache_need()
             if need is None:
                 continue
             for g in groups:
@@ -102,6 +106,12 @@ class DecoderModel:
             else:
                 groups.append(CacheGroupPlan(need, [r]))
         return groups
+
+    def host_control(self) -> bool:
+        """Whether any part decides on the host, step by step, what it launches (such a model's
+        steps are not recorded as CUDA graphs)."""
+        every = [p for b in self.blocks for p in b.parts()] + list(self.final_norm.parts())
+        return any(p.host_control for p in every)
 
     def state_bytes(self) -> List[int]:
         """Fixed-size state bytes per request, for each run of the order."""
@@ -120,7 +130,7 @@ class DecoderModel:
                                state=states[r].rows if states[r] is not None else None)
             if src in where:
                 g, i = where[src]
-                cache.kv = storages[g].run_view(i)
+                cache.pages = storages[g].run_view(i)
                 cache.group = g
             self.caches[r] = cache
 
@@ -131,7 +141,8 @@ class DecoderModel:
         s = self.spec
         step.shared.clear()
         x = ws.get("model.residual", (T, s.hidden_size), torch.float32)
-        ops.embed_gather(step.token_ids, self.embedding, x)
+        ops.embed_gather(step.token_ids, self.embedding, x,
+                         s.embedding_scale if s.embedding_scale is not None else 1.0)
         delta = None
         for r, run in enumerate(s.order):
             delta = self.blocks[run.layer].forward(x, delta, step, self.caches[r])
@@ -142,4 +153,7 @@ class DecoderModel:
         h = ws.get("model.final_normed", (R, s.hidden_size), self.env.dtype)
         self.final_norm.forward(x, h, delta=delta, rows=step.logit_rows)
         out = self.head.forward(h, "model.logits", "float32")
+        if self.head_bias is not None or s.logit_scale is not None or s.logit_softcap:
+            ops.logit_transform(out, self.head_bias, s.logit_scale if s.logit_scale is not None else 1.0,
+                                s.logit_softcap or 0.0)
         return out

@@ -8,12 +8,17 @@ architecture; tensor names: crates/allpaca-safetensors/src/names.rs:26-102).
 """
 from __future__ import annotations
 
-from ..config.model_config import LlamaConfig
+from ..config.model_config import ConfigError, LlamaConfig
 from ..parts import LayerRun, ModelSpec, PartSpec
 from .registry import register_architecture
 
 
 def llama_spec(cfg: LlamaConfig) -> ModelSpec:
+    if cfg.head_dim % 16 != 0 or cfg.head_dim > 256:
+        # what the attention kernels are built for: said when the model is described, before
+        # any weight is read or any kernel is compiled
+        raise ConfigError(f"head_dim {cfg.head_dim} is not one the attention kernels take "
+                          f"(multiples of 16 up to 256)")
     norm = PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps})
     rope = PartSpec("rope", {
         "head_dim": cfg.head_dim, "theta": cfg.rope_theta, "pairing": "half",

@@ -7,6 +7,7 @@ consumer a 32-bit tensor ``[S, T, N]``; consumers add the S slices in order.
 from __future__ import annotations
 
 import functools
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -48,8 +49,8 @@ def _partials(t: torch.Tensor, name: str):
     raise KernelError(f"{name} must be [T,N] or [S,T,N], has shape {tuple(t.shape)}")
 
 
-def embed_gather(tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor) -> None:
-    """``x[t] = table[tokens[t]]`` into the 32-bit residual stream ``x [T,H]``."""
+def embed_gather(tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0) -> None:
+    """``x[t] = table[tokens[t]] * scale`` into the 32-bit residual stream ``x [T,H]``."""
     _check(tokens, "tokens", torch.int32, 1)
     _check(table, "table", dims=2)
     _check(x, "x", torch.float32, 2)
@@ -58,7 +59,33 @@ def embed_gather(tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor) -> 
         raise KernelError(f"embed_gather: shapes disagree: tokens {tuple(tokens.shape)}, "
                           f"table {tuple(table.shape)}, x {tuple(x.shape)}")
     call(core(), "ap_embed_gather", tokens.data_ptr(), table.data_ptr(), dtype_code(table.dtype),
-         x.data_ptr(), T, H, table.shape[0], stream_handle())
+         x.data_ptr(), T, H, table.shape[0], float(scale), stream_handle())
+
+
+def bias_add(out: torch.Tensor, bias: torch.Tensor) -> None:
+    """``out[t, n] += bias[n]`` for ``out [T, N]`` (or ``[1, T, N]``) in float32 or bfloat16."""
+    _check(out, "out")
+    _check(bias, "bias", dims=1)
+    N = bias.shape[0]
+    if out.dim() not in (2, 3) or out.shape[-1] != N or (out.dim() == 3 and out.shape[0] != 1):
+        raise KernelError(f"bias_add: out {tuple(out.shape)} does not end in the bias's {N} columns")
+    call(core(), "ap_bias_add", out.data_ptr(), dtype_code(out.dtype), bias.data_ptr(), dtype_code(bias.dtype),
+         out.numel() // N, N, stream_handle())
+
+
+def logit_transform(logits: torch.Tensor, bias: Optional[torch.Tensor] = None, scale: float = 1.0,
+                    softcap: float = 0.0) -> None:
+    """In place on 32-bit ``logits [R, V]``: ``z = (logit + bias) * scale``, then
+    ``cap * tanh(z / cap)`` when ``softcap`` is positive."""
+    _check(logits, "logits", torch.float32, 2)
+    R, V = logits.shape
+    if bias is not None:
+        _check(bias, "bias", dims=1)
+        if bias.shape[0] != V:
+            raise KernelError("logit_transform: the bias must have one entry per column")
+    call(core(), "ap_logit_transform", logits.data_ptr(), bias.data_ptr() if bias is not None else 0,
+         dtype_code(bias.dtype) if bias is not None else AP_F32, R, V, float(scale), float(softcap or 0.0),
+         stream_handle())
 
 
 def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -103,8 +130,14 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
 def rope_kv_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[torch.Tensor],
                   positions: torch.Tensor, token_seq: Optional[torch.Tensor],
                   block_table: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
-                  pairing: int, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+                  pairing: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                  context_lens: Optional[torch.Tensor] = None) -> None:
     """Rotate Q and K of ``qkv [T, (nh+2nkv)*hd]`` and store K, V into cache pages.
+
+    ``context_lens`` (int32 per sequence: the tokens it holds after this step): a page that
+    gets its first token in this step has the slots behind the sequence's last token cleared,
+    so that a page taken over from another request holds nothing of it that a kernel could
+    read.  The engine always gives it.
 
     ``cache_layer`` is one layer's pages ``[pages, 2, nkv, P, hd]``; a row's page is
     ``block_table[token_seq[t], pos // P]`` and its slot ``pos % P``.  ``cos_sin`` is the
@@ -135,10 +168,13 @@ def rope_kv_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[
         _check(cos_sin, "cos_sin", torch.float32, 3)
         if cos_sin.shape[0] < T or tuple(cos_sin.shape[1:]) != (head_dim // 2, 2):
             raise KernelError("rope_kv_store: cos_sin must be [T, head_dim/2, 2]")
+    if context_lens is not None:
+        _check(context_lens, "context_lens", torch.int32, 1)
     call(core(), "ap_rope_kv_store", ptr, code, S, stride, q_out.data_ptr(), cptr,
          dtype_code(q_out.dtype), positions.data_ptr(), tsptr, btptr, maxb,
          cos_sin.data_ptr() if cos_sin is not None else 0, int(pairing), T, num_heads,
-         num_kv_heads, head_dim, P, page_stride, stream_handle())
+         num_kv_heads, head_dim, P, page_stride,
+         context_lens.data_ptr() if context_lens is not None and cache_layer is not None else 0, stream_handle())
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor) -> None:
@@ -275,7 +311,7 @@ def gemm_tc_persistent(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pair
 
 
 def _decode_attention(lib, q, out, cache_layer, block_table, positions, rows, num_heads, num_kv_heads, head_dim, P,
-                      scale, window, max_context, scratch, zero_scratch, use_tma) -> None:
+                      scale, window, max_context, scratch, use_tma) -> None:
     """The first ``rows`` rows of the batch, one per sequence: the split kernels."""
     tma = (use_tma and hasattr(lib, "ap_attention_decode_tma")
            and bool(lib.ap_attention_decode_tma_supports(num_heads, num_kv_heads, head_dim, P))
@@ -286,7 +322,7 @@ def _decode_attention(lib, q, out, cache_layer, block_table, positions, rows, nu
         sizes = (2, 4, 8, 16) if lib.ap_attention_decode_tma_in_cluster(num_heads, num_kv_heads, 16) else (2, 4, 8)
     nsplit = decode_splits(rows, num_heads, num_kv_heads, max_context, window, slots=296 if tma else 444,
                            cluster_sizes=sizes)
-    po = pm = pc = 0
+    po = pm = 0
     needs_scratch = nsplit > 1 and not (tma and lib.ap_attention_decode_tma_in_cluster(num_heads, num_kv_heads, nsplit))
     if needs_scratch:
         if scratch is None:
@@ -301,20 +337,15 @@ def _decode_attention(lib, q, out, cache_layer, block_table, positions, rows, nu
              num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0), float(scale), int(window or 0),
              nsplit, po, pm, stream_handle())
         return
-    if needs_scratch and zero_scratch is not None:
-        # arrival counters of the slices: zero now, and left zero by every launch
-        reps = num_heads // num_kv_heads
-        chunks = -(-reps // min(reps, 16))
-        pc = zero_scratch("attn.counters", (rows * num_kv_heads * chunks,), torch.int32).data_ptr()
     call(lib, "ap_attention_tc", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
          block_table.data_ptr(), block_table.shape[1], 0, positions.data_ptr(),
          rows, rows, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0), float(scale),
-         int(window or 0), 1, 0, nsplit, po, pm, pc, stream_handle())
+         int(window or 0), 1, 0, nsplit, po, pm, stream_handle())
 
 
 # CTAs of the tcgen05 attention with two query tiles from which it is preferred to the kernel
 # with one: below, the narrow kernel's twice as many CTAs fill the SMs better
-WIDE_ATTENTION_MIN_CTAS = 148
+WIDE_ATTENTION_MIN_CTAS = int(os.environ.get("ALLPACA_WIDE_ATTENTION_MIN_CTAS", "148"))
 
 
 def _prompt_attention(lib, q, out, cache_layer, block_table, seq_start, positions, first_seq, query_lens, T,
@@ -353,7 +384,7 @@ def _prompt_attention(lib, q, out, cache_layer, block_table, seq_start, position
     call(lib, "ap_attention_tc", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(),
          table_ptr, block_table.shape[1], start_ptr, positions.data_ptr(),
          nseq, T, num_heads, num_kv_heads, head_dim, P, cache_layer.stride(0), float(scale),
-         int(window or 0), 0, tiles, 1, 0, 0, 0, stream_handle())
+         int(window or 0), 0, tiles, 1, 0, 0, stream_handle())
 
 
 def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
@@ -361,7 +392,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: int = 0, seq_start: Optional[torch.Tensor] = None,
               query_lens: Optional[Sequence[int]] = None, max_context: int = 0,
-              scratch=None, zero_scratch=None, use_tcgen05: bool = True, use_tma: bool = True,
+              scratch=None, use_tcgen05: bool = True, use_tma: bool = True,
               wide: Optional[bool] = None) -> None:
     """Causal attention of every row of ``q [T, nh*hd]`` over its sequence's cached keys.
 
@@ -370,10 +401,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
     given: the split kernel when every sequence brings one row; else, for 64 rows or more and
     the shapes it takes, a tcgen05 kernel (``use_tcgen05``; ``wide`` picks the one with two query
     tiles to a CTA, ``None`` by the number of CTAs), and otherwise the tile kernel.
-    ``scratch(name, shape, dtype)`` supplies the partial-result buffers of the split kernel;
-    ``zero_scratch`` (same signature) supplies buffers that are zero when first handed out
-    and stay with the caller: with it the last key slice to arrive combines all slices,
-    without it a second kernel does.
+    ``scratch(name, shape, dtype)`` supplies the partial-result buffers of the split kernel
+    where its key slices are not combined inside a thread-block cluster.
     """
     _check(q, "q", dims=2)
     _check(out, "out", q.dtype, 2)
@@ -403,7 +432,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
             nd += 1
         if nd > 0:
             _decode_attention(lib, q, out, cache_layer, block_table, positions, nd, num_heads, num_kv_heads,
-                              head_dim, P, scale, window, max_context, scratch, zero_scratch, use_tma)
+                              head_dim, P, scale, window, max_context, scratch, use_tma)
         if nd < nseq:
             _prompt_attention(lib, q, out, cache_layer, block_table, seq_start, positions, nd, query_lens[nd:], T,
                               num_heads, num_kv_heads, head_dim, P, scale, window, use_tcgen05, wide)

@@ -22,10 +22,12 @@ class KernelError(RuntimeError):
 _P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
 
 _CORE_SIGNATURES = {
-    "ap_embed_gather": [_P, _P, _I, _P, _I, _I, _I, _P],
+    "ap_embed_gather": [_P, _P, _I, _P, _I, _I, _I, _F, _P],
+    "ap_bias_add": [_P, _I, _P, _I, _I, _I, _P],
+    "ap_logit_transform": [_P, _P, _I, _I, _I, _F, _F, _P],
     "ap_add_rmsnorm": [_P, _P, _I, _L, _P, _I, _F, _P, _I, _P, _I, _I, _P],
     "ap_residual_add": [_P, _P, _I, _L, _L, _P],
-    "ap_rope_kv_store": [_P, _I, _I, _L, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _L, _P],
+    "ap_rope_kv_store": [_P, _I, _I, _L, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _L, _P, _P],
     "ap_rope_table": [_P, _P, _P, _I, _I, _P],
     "ap_swiglu": [_P, _I, _I, _L, _P, _I, _I, _I, _I, _P],
     "ap_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _L, _L, _L, _P],
@@ -111,7 +113,7 @@ def attention(head_dim: int) -> ctypes.CDLL:
 
 
 _OPTIONAL_ATTN_SIGNATURES: Dict[str, list] = {
-    "ap_attention_tc": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _L, _F, _I, _I, _I, _I, _P, _P, _P, _P],
+    "ap_attention_tc": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _L, _F, _I, _I, _I, _I, _P, _P, _P],
     "ap_attention_tc_tokens_per_tile": [_I, _I],
     "ap_attention_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _L, _F, _I, _I, _P],
     "ap_attention_tcgen05_supports": [_I, _I, _I, _I],

@@ -21,7 +21,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from .. import ops
-from .base import BuildEnv, KVNeed, LayerCache, Mixer, WeightSpec, build, register
+from .base import BuildEnv, CacheNeed, KVNeed, LayerCache, Mixer, PartError, WeightSpec, build, register
 from .linear import Linear
 
 
@@ -29,7 +29,8 @@ from .linear import Linear
 class GroupedQueryAttention(Mixer):
     """Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``,
     ``position`` (a :class:`PartSpec` of kind ``position`` or None), ``window`` (None or
-    tokens), ``scale`` (None: ``1/sqrt(head_dim)``), ``shares_kv`` (False)."""
+    tokens), ``scale`` (None: ``1/sqrt(head_dim)``), ``shares_kv`` (False), ``qkv_bias`` and
+    ``o_bias`` (False: the projections have no bias, as on the Llama path)."""
 
     def __init__(self, params, env: BuildEnv):
         super().__init__(params, env)
@@ -41,9 +42,13 @@ class GroupedQueryAttention(Mixer):
         self.hd = int(p["head_dim"])
         if self.nh % self.nkv:
             raise ValueError(f"{self.nh} heads are not a multiple of {self.nkv} KV heads")
+        if self.hd <= 0 or self.hd % 16 or self.hd > 256:
+            raise PartError(f"head_dim {self.hd} is not one the attention kernels take (multiples of 16 up to 256)")
         self.window = p.get("window") or None
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
         self.shares_kv = bool(p.get("shares_kv", False))
+        self.qkv_bias = bool(p.get("qkv_bias", False))
+        self.o_bias = bool(p.get("o_bias", False))
         pos = p.get("position")
         self.position = build("position", pos, env) if pos is not None else None
         self.q_size = self.nh * self.hd
@@ -58,18 +63,32 @@ class GroupedQueryAttention(Mixer):
         if not self.shares_kv:
             w["k_proj.weight"] = WeightSpec((self.kv_size, self.hidden))
             w["v_proj.weight"] = WeightSpec((self.kv_size, self.hidden))
+        if self.qkv_bias:
+            w["q_proj.bias"] = WeightSpec((self.q_size,), "bias")
+            if not self.shares_kv:
+                w["k_proj.bias"] = WeightSpec((self.kv_size,), "bias")
+                w["v_proj.bias"] = WeightSpec((self.kv_size,), "bias")
+        if self.o_bias:
+            w["o_proj.bias"] = WeightSpec((self.hidden,), "bias")
         return w
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         parts = [tensors["q_proj.weight"]]
         if not self.shares_kv:
             parts += [tensors["k_proj.weight"], tensors["v_proj.weight"]]
-        self.qkv.load(torch.cat(parts, dim=0) if len(parts) > 1 else parts[0])
-        self.o.load(tensors["o_proj.weight"])
+        names = ["q_proj"] + ([] if self.shares_kv else ["k_proj", "v_proj"])
+        bias = torch.cat([tensors[n + ".bias"] for n in names], dim=0) if self.qkv_bias else None
+        self.qkv.load(torch.cat(parts, dim=0) if len(parts) > 1 else parts[0], bias)
+        self.o.load(tensors["o_proj.weight"], tensors["o_proj.bias"] if self.o_bias else None)
 
     # ---- cache ----------------------------------------------------------
-    def kv_need(self) -> Optional[KVNeed]:
+    def cache_need(self) -> Optional[CacheNeed]:
         return KVNeed(self.nkv, self.hd, self.window)
+
+    def parts(self):
+        yield self
+        if self.position is not None:
+            yield from self.position.parts()
 
     # ---- one step -------------------------------------------------------
     def forward(self, h: torch.Tensor, step, cache: LayerCache) -> torch.Tensor:
@@ -88,11 +107,11 @@ class GroupedQueryAttention(Mixer):
             self.position.apply(qv, kv, step.positions)
         cos_sin, pairing = table if table is not None else (None, 0)
         ops.rope_kv_store(
-            qkv, q, cache.kv if writes else None, step.positions, step.token_seq,
+            qkv, q, cache.pages if writes else None, step.positions, step.token_seq,
             step.block_tables[cache.group] if writes else None, cos_sin, pairing,
-            self.nh, self.nkv if not self.shares_kv else 0, self.hd)
+            self.nh, self.nkv if not self.shares_kv else 0, self.hd, context_lens=step.context_lens)
         attn = ws.get("attn.out", (T, self.q_size), self.env.dtype)
-        ops.attention(q, attn, cache.kv, step.block_tables[cache.group], step.token_seq,
+        ops.attention(q, attn, cache.pages, step.block_tables[cache.group], step.token_seq,
                       step.positions, self.nh, self.nkv, self.hd, self.scale,
                       self.window or 0, seq_start=step.seq_start, query_lens=step.host_query_lens,
                       max_context=step.max_context_len, scratch=ws.get)

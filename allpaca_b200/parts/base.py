@@ -111,21 +111,6 @@ class Workspace:
         self._views[vkey] = view
         return view
 
-    def get_zeroed(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
-        """Like :meth:`get`, but the memory is zero when it is first handed out (and after
-        growing); users that leave it zero find it zero again."""
-        n = 1
-        for s in shape:
-            n *= int(s)
-        key = f"{name}:{dtype}"
-        buf = self._buffers.get(key)
-        if buf is None or buf.numel() < n:
-            buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
-            self._buffers[key] = buf
-            self.generation += 1
-            self._views = {k: v for k, v in self._views.items() if not (k[0] == name and k[2] == dtype)}
-        return buf[:n].view(*shape)
-
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
 
@@ -135,30 +120,54 @@ class WeightSpec:
     """One tensor a part needs: its shape and what it is (decides type and random init)."""
 
     shape: Tuple[int, ...]
-    role: str = "linear"      # "linear" | "embedding" | "norm" | "table"
+    role: str = "linear"      # "linear" | "embedding" | "norm" | "bias" | "table"
     optional: bool = False
 
 
 @dataclass(frozen=True)
-class KVNeed:
-    """Keys and values a mixer keeps per token: all of them, or a trailing window."""
+class CacheNeed:
+    """What a mixer keeps per token, in pages.
 
-    num_kv_heads: int
-    head_dim: int
-    window: Optional[int] = None       # None: every earlier token stays readable
+    One page of one run of the order is a tensor ``[*outer, page_size, *inner]`` of ``dtype``
+    (None: the engine's activation type): ``inner`` is what one token stores contiguously,
+    ``outer`` counts separate planes of such rows inside a page (keys and values of several
+    heads: ``(2, kv_heads)`` with ``inner = (head_dim,)``; one latent vector per token:
+    ``()`` with ``inner = (width,)``).  ``window`` (None: every earlier token stays readable)
+    lets the cache manager take back the pages a trailing window has passed.  Runs whose
+    needs are equal share a page pool and a block table."""
+
+    outer: Tuple[int, ...] = ()
+    inner: Tuple[int, ...] = ()
+    dtype: Optional[torch.dtype] = None
+    window: Optional[int] = None
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        return (*self.outer, int(page_size), *self.inner)
+
+    def page_bytes(self, page_size: int, engine_dtype: torch.dtype) -> int:
+        n = int(page_size)
+        for d in (*self.outer, *self.inner):
+            n *= int(d)
+        return n * torch.empty((), dtype=self.dtype or engine_dtype).element_size()
+
+
+def KVNeed(num_kv_heads: int, head_dim: int, window: Optional[int] = None) -> CacheNeed:
+    """Keys and values of ``num_kv_heads`` heads per token: pages ``[2, kv_heads, page, head_dim]``."""
+    return CacheNeed(outer=(2, int(num_kv_heads)), inner=(int(head_dim),), window=window)
 
 
 @dataclass
 class LayerCache:
     """What one run of a layer sees of the caches.
 
-    ``kv``: pages of this run ``[pages, 2, kv_heads, page, head_dim]`` or None;
-    ``group``: index into the step's per-group block tables and slots;
+    ``pages``: pages of this run ``[num_pages, *outer, page_size, *inner]`` (see
+    :class:`CacheNeed`) or None;
+    ``group``: index into the step's per-group block tables;
     ``writes``: False when the run reads the pages another run wrote;
     ``state``: ``[max_seqs, state_bytes]`` uint8 rows of fixed-size state, or None.
     """
 
-    kv: Optional[torch.Tensor] = None
+    pages: Optional[torch.Tensor] = None
     group: int = -1
     writes: bool = True
     state: Optional[torch.Tensor] = None
@@ -167,9 +176,21 @@ class LayerCache:
 class Part:
     """Common face of every part."""
 
+    #: True when ``forward`` reads the step's host-side lists (``step.host_*``) or otherwise
+    #: decides on the host what to launch for a given step.  Steps of a model with such a
+    #: part are never recorded as CUDA graphs: a replay would repeat the decisions of the
+    #: recorded step.  A part that reads only the step's device tensors (``state_slots``,
+    #: ``seq_start``, ``positions`` ...; a sequence's first portion is the one whose first row
+    #: has position 0) leaves it False.
+    host_control: bool = False
+
     def __init__(self, params: Dict[str, Any], env: BuildEnv):
         self.params = params
         self.env = env
+
+    def parts(self):
+        """This part and the parts built inside it."""
+        yield self
 
     def weights(self) -> Dict[str, WeightSpec]:
         """Local tensor names -> what they are."""
@@ -213,7 +234,8 @@ class Mixer(Part):
     """``forward(h, step, cache) -> delta``: ``h [T, hidden]`` normalised rows in the activation
     type; returns 32-bit ``[S, T, hidden]`` partial sums to be added to the residual."""
 
-    def kv_need(self) -> Optional[KVNeed]:
+    def cache_need(self) -> Optional[CacheNeed]:
+        """What the mixer keeps per token in pages (None: nothing)."""
         return None
 
     def state_bytes(self) -> int:
@@ -244,6 +266,11 @@ class Block(Part):
     def sub_parts(self) -> Dict[str, Part]:
         """Weight-name prefix -> part, for loading."""
         raise NotImplementedError
+
+    def parts(self):
+        yield self
+        for part in self.sub_parts().values():
+            yield from part.parts()
 
     def forward(self, x, delta, step, cache: LayerCache):
         raise NotImplementedError
@@ -276,3 +303,8 @@ class ModelSpec:
     head_name: str = "lm_head.weight"
     tie_word_embeddings: bool = False
     max_position_embeddings: int = 2048
+    # Ends of the stack that some decoders alter; all default to "as it is".
+    embedding_scale: Optional[float] = None      # the gathered embedding row is multiplied by it
+    head_bias_name: Optional[str] = None         # a [vocab] tensor added to the logits
+    logit_scale: Optional[float] = None          # logits are multiplied by it ...
+    logit_softcap: Optional[float] = None        # ... and then become cap * tanh(logit / cap)

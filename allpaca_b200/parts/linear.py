@@ -26,12 +26,18 @@ class Linear:
         self.out_features = int(out_features)
         self.in_features = int(in_features)
         self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
 
-    def load(self, weight: torch.Tensor) -> None:
+    def load(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+        """``bias`` (``[out]``, optional) is added to the finished sums by a kernel of its own, after
+        they were rounded to the output type; nothing on the Llama path has one."""
         if tuple(weight.shape) != (self.out_features, self.in_features):
             raise ValueError(f"weight {tuple(weight.shape)} is not "
                              f"[{self.out_features}, {self.in_features}]")
         self.weight = weight.contiguous()
+        if bias is not None and tuple(bias.shape) != (self.out_features,):
+            raise ValueError(f"bias {tuple(bias.shape)} is not [{self.out_features}]")
+        self.bias = bias.contiguous() if bias is not None else None
 
     def uses_tensor_cores(self) -> bool:
         return (self.weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
@@ -69,6 +75,8 @@ class Linear:
             ops.gemm_tc(a, self.weight, target, nsplit, reduce=nsplit > 1)
         else:
             ops.gemm_simt(a, self.weight, target)
+        if self.bias is not None:
+            ops.bias_add(target, self.bias)
         return out
 
     def forward_gated(self, a: torch.Tensor, buffer_name: str) -> Optional[torch.Tensor]:
@@ -76,7 +84,7 @@ class Linear:
         kernel, ``[T, out/2]`` in the activation type; None when the shape is not one the fused
         kernel is used for (the caller then multiplies and activates separately)."""
         T = a.shape[0]
-        if not self.uses_tensor_cores() or self.out_features % 2:
+        if not self.uses_tensor_cores() or self.out_features % 2 or self.bias is not None:
             return None
         out = self.env.workspace.get(buffer_name, (T, self.out_features // 2), self.env.dtype)
         nsplit = ops.gemm_tc_splits(T, self.out_features, self.in_features)

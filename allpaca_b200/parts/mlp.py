@@ -20,25 +20,34 @@ from .linear import Linear
 
 @register("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
-    """Parameters: ``hidden_size``, ``intermediate_size``."""
+    """Parameters: ``hidden_size``, ``intermediate_size``, ``bias`` (False: no biases, as on the
+    Llama path)."""
 
     def __init__(self, params, env: BuildEnv):
         super().__init__(params, env)
         self.require("hidden_size", "intermediate_size")
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
+        self.bias = bool(params.get("bias", False))
         self.gate_up = Linear(env, 2 * self.inter, self.hidden)
         self.down = Linear(env, self.hidden, self.inter)
 
     def weights(self) -> Dict[str, WeightSpec]:
-        return {"gate_proj.weight": WeightSpec((self.inter, self.hidden)),
-                "up_proj.weight": WeightSpec((self.inter, self.hidden)),
-                "down_proj.weight": WeightSpec((self.hidden, self.inter))}
+        w = {"gate_proj.weight": WeightSpec((self.inter, self.hidden)),
+             "up_proj.weight": WeightSpec((self.inter, self.hidden)),
+             "down_proj.weight": WeightSpec((self.hidden, self.inter))}
+        if self.bias:
+            w.update({"gate_proj.bias": WeightSpec((self.inter,), "bias"),
+                      "up_proj.bias": WeightSpec((self.inter,), "bias"),
+                      "down_proj.bias": WeightSpec((self.hidden,), "bias")})
+        return w
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
-        self.gate_up.load(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden))
-        self.down.load(tensors["down_proj.weight"])
+        gu_bias = torch.stack([tensors["gate_proj.bias"], tensors["up_proj.bias"]], dim=1).reshape(-1) \
+            if self.bias else None
+        self.gate_up.load(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden), gu_bias)
+        self.down.load(tensors["down_proj.weight"], tensors["down_proj.bias"] if self.bias else None)
 
     def forward(self, h: torch.Tensor, step) -> torch.Tensor:
         T = h.shape[0]

@@ -2,6 +2,10 @@
 
 Stored types are kept: floating tensors go to the engine's type (bfloat16, or float32 for
 the 32-bit path; a tensor stored in 32-bit stays 32-bit), integer tables become int32.
+A matrix that stays 32-bit in a bfloat16 engine runs on the slow CUDA-core product: that is
+said aloud once per load, and ``float32_weights`` chooses otherwise (``"round"`` them to
+bfloat16 at load, or ``"refuse"`` the checkpoint); vectors (norm weights, biases) cost nothing
+in 32-bit and always stay.
 Every problem of a checkpoint is reported in one error that lists the missing tensors,
 the unexpected ones and those of the wrong shape.
 
@@ -16,6 +20,7 @@ from __future__ import annotations
 import hashlib
 import json
 import os
+import sys
 from typing import Dict, Mapping, Tuple
 
 import torch
@@ -57,10 +62,21 @@ def check_names(targets: Mapping[str, Tuple[WeightSpec, object, str]],
         raise WeightError("\n".join(lines))
 
 
-def load_checkpoint(model, path: str, engine_dtype: torch.dtype, device: torch.device) -> None:
-    """Read every tensor the model names from a model folder and hand them to the parts."""
+FLOAT32_WEIGHT_POLICIES = ("keep", "round", "refuse")
+
+
+def load_checkpoint(model, path: str, engine_dtype: torch.dtype, device: torch.device,
+                    float32_weights: str = "keep") -> None:
+    """Read every tensor the model names from a model folder and hand them to the parts.
+
+    ``float32_weights`` says what happens to matrices stored in 32-bit when the engine runs in
+    bfloat16: ``"keep"`` them (slow CUDA-core products, announced on standard error),
+    ``"round"`` them to bfloat16, or ``"refuse"`` the checkpoint."""
+    if float32_weights not in FLOAT32_WEIGHT_POLICIES:
+        raise WeightError(f"float32_weights must be one of {FLOAT32_WEIGHT_POLICIES}, not {float32_weights!r}")
     ckpt = Checkpoint(path)
     targets = model.weight_targets()
+    wide = []
     # buffers some exporters save beside the weights; they are recomputed from the configuration
     derived = (".rotary_emb.inv_freq",)
     check_names(targets, {n: ckpt.info(n)[1] for n in ckpt.names() if not n.endswith(derived)})
@@ -72,7 +88,19 @@ def load_checkpoint(model, path: str, engine_dtype: torch.dtype, device: torch.d
         want = storage_dtype(t.dtype, engine_dtype)
         if engine_dtype == torch.float32 and t.dtype.is_floating_point:
             want = torch.float32          # the 32-bit path widens 16-bit checkpoints
+        elif want == torch.float32 and targets[name][0].role in ("linear", "embedding"):
+            wide.append(name)
+            if float32_weights == "round":
+                want = engine_dtype
         tensors[name] = t.to(device=device, dtype=want, non_blocking=False).contiguous()
+    if wide and float32_weights == "refuse":
+        raise WeightError(f"{len(wide)} matrices of {path} are stored in 32-bit (first: {wide[0]}) and the engine "
+                          f"runs in bfloat16: run it with dtype float32, or let float32_weights round or keep them")
+    if wide and float32_weights == "keep":
+        print(f"[allpaca_b200] warning: {len(wide)} matrices of {path} are stored in 32-bit (first: {wide[0]}); "
+              f"in a bfloat16 engine they stay 32-bit and their products run on the CUDA cores, far slower "
+              f"than the tensor cores.  Use dtype float32 for the true 32-bit path, or float32_weights='round' "
+              f"to round them to bfloat16 at load.", file=sys.stderr, flush=True)
     model.load_weights(tensors)
 
 

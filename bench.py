@@ -65,7 +65,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
@@ -114,102 +114,79 @@ def model_numbers(cfg, layers: int):
     return per_layer, linear, kv_per_token
 
 
-def main() -> int:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--preset", default="llama-3.1-8b")
-    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the preset (named in config)")
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--prefill-tokens", type=int, default=2048)
-    ap.add_argument("--page-size", type=int, default=16)
-    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
-    ap.add_argument("--prefill-only", action="store_true", help="time only the prefill (for profilers)")
-    ap.add_argument("--seed", type=int, default=2)
-    ap.add_argument("--l2-prefetch-mb", type=int, default=0, help="weight bytes a GEMM may prefetch into L2 early")
-    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profilers)")
-    args = ap.parse_args()
+class Workbench:
+    """One model shape with random weights on the device, its runner, and the timed runs."""
 
-    if args.impl == "reference":
-        return reference_arm()
-    if args.gpus != 1:
-        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
-        return 2
-    if args.warmup < 3:
-        args.warmup = 3
+    def __init__(self, preset: str, layers, args, max_batch: int):
+        import torch
+        from allpaca_b200.config import EngineConfig
+        from allpaca_b200.config.presets import preset_config
+        from allpaca_b200.engine.runner import ModelRunner
+        from allpaca_b200.parts import BuildEnv, Workspace
+        from allpaca_b200.weights.random_model import random_model_on_device
+        self.torch, self.args, self.preset = torch, args, preset
+        raw = preset_config(preset)
+        self.full_layers = raw["num_hidden_layers"]
+        self.layers = layers or self.full_layers
+        raw["num_hidden_layers"] = self.layers
+        max_len = max(args.context, args.prefill_tokens) + 16
+        raw["max_position_embeddings"] = max(raw.get("max_position_embeddings", 0), max_len)
+        self.device = torch.device("cuda:0")
+        torch.cuda.set_device(self.device)
+        engine = EngineConfig(dtype="bfloat16", page_size=args.page_size,
+                              max_cache_tokens=max_batch * (args.context + args.page_size) + args.prefill_tokens + 64,
+                              max_num_seqs=max_batch, max_num_batched_tokens=max(args.prefill_tokens, max_batch),
+                              prefill_chunk=args.prefill_tokens, max_model_len=max_len, seed=args.seed,
+                              use_cuda_graphs=not args.no_graphs)
+        engine.validate()
+        env = BuildEnv(dtype=engine.dtype, device=self.device, workspace=Workspace(self.device),
+                       page_size=engine.page_size, max_seqs=engine.max_num_seqs)
+        t0 = time.time()
+        self.cfg, model = random_model_on_device(raw, args.seed, env)
+        self.runner = ModelRunner(None, engine, model=model, model_config=self.cfg)
+        self.runner.workspace = env.workspace
+        torch.cuda.synchronize()
+        print(f"[bench] {preset} ready in {time.time() - t0:.1f} s: {self.layers}/{self.full_layers} layers, "
+              f"cache {self.runner.memory_report()['cache_bytes'] / 2**30:.1f} GiB", file=sys.stderr, flush=True)
+        self.per_layer, self.linear_elems, self.kv_per_token = model_numbers(self.cfg, self.layers)
+        self.gen = torch.Generator().manual_seed(args.seed)
 
-    import torch
-    from allpaca_b200 import LLM, SamplingParams, ops
-    from allpaca_b200.config import EngineConfig
-    from allpaca_b200.config.presets import preset_config
-    from allpaca_b200.engine.batch import BatchEntry
-    from allpaca_b200.engine.runner import ModelRunner
-    from allpaca_b200.engine.scheduler import Request
-    from allpaca_b200.ops import library
-    from allpaca_b200.parts import BuildEnv, Workspace
-    from allpaca_b200.weights.random_model import random_model_on_device
+    def close(self):
+        self.runner = None
+        import gc
+        gc.collect()
+        self.torch.cuda.empty_cache()
 
-    pk = peaks()
-    library.core().ap_gemm_tc_set_l2_prefetch(args.l2_prefetch_mb << 20)
-    raw = preset_config(args.preset)
-    full_layers = raw["num_hidden_layers"]
-    layers = args.layers or full_layers
-    raw["num_hidden_layers"] = layers
-    max_batch = args.batch if args.no_points else max(args.batch, 64)
-    total_steps = args.warmup + args.steps + 8
-    max_len = max(args.context, args.prefill_tokens) + 16
-    raw["max_position_embeddings"] = max(raw.get("max_position_embeddings", 0), max_len)
-
-    device = torch.device("cuda:0")
-    torch.cuda.set_device(device)
-    engine = EngineConfig(dtype="bfloat16", page_size=args.page_size,
-                          max_cache_tokens=max_batch * (args.context + args.page_size) + args.prefill_tokens + 64,
-                          max_num_seqs=max_batch, max_num_batched_tokens=max(args.prefill_tokens, max_batch),
-                          prefill_chunk=args.prefill_tokens, max_model_len=max_len, seed=args.seed,
-                          use_cuda_graphs=not args.no_graphs)
-    engine.validate()
-    env = BuildEnv(dtype=engine.dtype, device=device, workspace=Workspace(device),
-                   page_size=engine.page_size, max_seqs=engine.max_num_seqs)
-    t0 = time.time()
-    cfg, model = random_model_on_device(raw, args.seed, env)
-    runner = ModelRunner(None, engine, model=model, model_config=cfg)
-    runner.workspace = env.workspace
-    torch.cuda.synchronize()
-    print(f"[bench] model ready in {time.time() - t0:.1f} s: {layers}/{full_layers} layers, "
-          f"cache {runner.memory_report()['cache_bytes'] / 2**30:.1f} GiB", file=sys.stderr, flush=True)
-    per_layer, linear_elems, kv_per_token = model_numbers(cfg, layers)
-    gen = torch.Generator().manual_seed(args.seed)
-
-    def fast_forward(llm, batch, start_len):
+    def _fast_forward(self, llm, batch, start_len):
         """Requests that already hold `start_len - 1` tokens of (synthetic, zero) cache: the
         next step runs their last prompt token and decoding goes on from there."""
-        ids = []
+        from allpaca_b200 import SamplingParams
+        from allpaca_b200.engine.scheduler import Request
         for i in range(batch):
-            prompt = torch.randint(0, cfg.vocab_size, (start_len,), generator=gen).tolist()
+            prompt = self.torch.randint(0, self.cfg.vocab_size, (start_len,), generator=self.gen).tolist()
             req = Request(("bench", i), prompt, SamplingParams.greedy_params(max_tokens=10 ** 6))
             llm.scheduler.adopt_running(req, start_len - 1)
-            runner.cache.begin(req.request_id)
-            runner.cache.append(req.request_id, start_len - 1)
-            ids.append(req.request_id)
-        return ids
+            self.runner.cache.begin(req.request_id)
+            self.runner.cache.append(req.request_id, start_len - 1)
 
-    def drain(llm):
-        for req in list(llm.scheduler.running):
-            llm.scheduler.abort(req.request_id)
-            runner.finish(req.request_id)
-
-    def decode_run(batch, steps, warmup, sample_clocks=False):
+    def decode_run(self, batch, steps, warmup, sample_clocks=False):
         """(device tok/s, ms/step, e2e tok/s, launches, h2d bytes, d2h bytes, clocks)."""
+        torch, runner, args = self.torch, self.runner, self.args
+        from allpaca_b200 import LLM, ops
+        from allpaca_b200.engine.batch import BatchEntry
+        from allpaca_b200.ops import library
         llm = LLM(runner=runner)
         start_len = args.context - (2 * (warmup + steps) + 2)
-        fast_forward(llm, batch, start_len)
+        self._fast_forward(llm, batch, start_len)
+        # the clocks are sampled over both timed regions (the same K steps twice: through the
+        # entry point, then device-timed)
+        sampler = ClockSampler()
         # --- end to end through the entry point, host clock ---
         for _ in range(warmup):
             llm.step()
         torch.cuda.synchronize()
+        if sample_clocks:
+            sampler.start()
         t = time.perf_counter()
         for _ in range(steps):
             llm.step()
@@ -223,7 +200,7 @@ def main() -> int:
             llm.scheduler.abort(r.request_id)
         # the next tokens are chosen on the GPU and handed to the next step on the GPU: no step
         # waits for the host (the end-to-end figure above is the one with host tokens in and out)
-        out = torch.tensor(tokens, dtype=torch.int32).to(device)
+        out = torch.tensor(tokens, dtype=torch.int32).to(self.device)
         entries = [BatchEntry(r.request_id, [0], [0]) for r in reqs]
 
         def one_step():
@@ -231,9 +208,6 @@ def main() -> int:
             ops.argmax(logits, out)
         for _ in range(warmup):
             one_step()
-        sampler = ClockSampler()
-        if sample_clocks:
-            sampler.start()
         calls0 = library.launch_count()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -251,11 +225,19 @@ def main() -> int:
         h2d = 4 * (3 * batch + (batch + 1) + 3 * batch + batch * -(-args.context // args.page_size))
         return batch / (ms / 1e3), ms, batch * steps / e2e_s, launches, h2d, 4 * batch, clocks
 
-    def prefill_run(tokens_n):
-        best = None
+    def step_bytes(self, batch, steps):
+        """What a decode step has to read: every weight once, and the cache of the live requests
+        at the middle of the timed region."""
+        ctx_mid = self.args.context - (steps + 2) // 2
+        return 2.0 * self.linear_elems + batch * ctx_mid * self.kv_per_token
+
+    def prefill_run(self, tokens_n):
+        """(best ms, median ms, flops) of five prompts of ``tokens_n`` tokens, after one that warms up."""
+        torch, runner, cfg = self.torch, self.runner, self.cfg
+        from allpaca_b200.engine.batch import BatchEntry
         times = []
-        for i in range(5):
-            prompt = torch.randint(0, cfg.vocab_size, (tokens_n,), generator=gen).tolist()
+        for i in range(6):
+            prompt = torch.randint(0, cfg.vocab_size, (tokens_n,), generator=self.gen).tolist()
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             start.record()
@@ -263,23 +245,57 @@ def main() -> int:
             stop.record()
             torch.cuda.synchronize()
             runner.finish(("prefill", i))
-            ms = start.elapsed_time(stop)
-            times.append(round(ms, 3))
-            best = ms if best is None or (i > 0 and ms < best) else best
+            times.append(round(start.elapsed_time(stop), 3))
         print(f"[bench] prefill of {tokens_n} tokens, ms per run (the first warms up): {times}", file=sys.stderr, flush=True)
-        flops = 2.0 * tokens_n * layers * per_layer + 2.0 * cfg.vocab_size * cfg.hidden_size \
-            + layers * 4.0 * cfg.q_size * tokens_n * (tokens_n + 1) / 2
-        return best, flops
+        flops = 2.0 * tokens_n * self.layers * self.per_layer + 2.0 * cfg.vocab_size * cfg.hidden_size \
+            + self.layers * 4.0 * cfg.q_size * tokens_n * (tokens_n + 1) / 2
+        return min(times[1:]), statistics.median(times[1:]), flops
 
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--preset", default="llama-3.1-8b")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the preset (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
+    ap.add_argument("--no-presets", action="store_true",
+                    help="skip the decode points of the other benchmark shapes (Llama-3.2-1B, Llama-2-13B)")
+    ap.add_argument("--prefill-only", action="store_true", help="time only the prefill (for profilers)")
+    ap.add_argument("--seed", type=int, default=2)
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profilers)")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    if 2 * (args.warmup + args.steps) + 66 > args.context:
+        print(f"bench.py: --steps {args.steps} does not fit a context of {args.context} tokens twice over "
+              f"(the steps run once through the entry point and once device-timed)", file=sys.stderr)
+        return 2
+
+    from allpaca_b200 import ops
+    pk = peaks()
+    max_batch = args.batch if args.no_points else max(args.batch, 64)
+    bench = Workbench(args.preset, args.layers, args, max_batch)
+    cfg, layers = bench.cfg, bench.layers
     if args.prefill_only:
-        pms, flops = prefill_run(args.prefill_tokens)
-        print(json.dumps({"prefill_ms": round(pms, 3), "tokens": args.prefill_tokens, "layers": layers,
-                          "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}))
+        pms, pmed, flops = bench.prefill_run(args.prefill_tokens)
+        print(json.dumps({"prefill_ms": round(pms, 3), "median_ms": round(pmed, 3), "tokens": args.prefill_tokens,
+                          "layers": layers, "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}))
         return 0
-    value, ms, e2e, launches, h2d, d2h, clocks = decode_run(args.batch, args.steps, args.warmup, True)
-    ctx_mid = args.context - (args.steps + 2) // 2
-    step_bytes = 2.0 * linear_elems + args.batch * ctx_mid * kv_per_token
-    achieved = step_bytes / (ms / 1e3) / 1e9
+    value, ms, e2e, launches, h2d, d2h, clocks = bench.decode_run(args.batch, args.steps, args.warmup, True)
+    achieved = bench.step_bytes(args.batch, args.steps) / (ms / 1e3) / 1e9
     result = {
         "metric": f"decode tok/s ({'8B shape' if args.preset == 'llama-3.1-8b' else args.preset}, bf16)", "value": round(value, 2), "unit": "tok/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
@@ -287,13 +303,13 @@ def main() -> int:
         "data": "synthetic", "impl": "ours",
         "config": {
             "model": args.preset, "global_batch": args.batch, "seq_len": args.context,
-            "parallelism": "single-gpu", "layers": layers, "layers_in_shape": full_layers,
+            "parallelism": "single-gpu", "layers": layers, "layers_in_shape": bench.full_layers,
             "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
             "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
             "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
             "page_size": args.page_size, "weights": "random N(0,0.02) seed %d" % args.seed,
             "cache_fill": "synthetic (zeros), prefill timed separately",
-            "l2": "inputs larger than L2 (weights %.1f GB per step)" % (2.0 * linear_elems / 1e9),
+            "l2": "inputs larger than L2 (weights %.1f GB per step)" % (2.0 * bench.linear_elems / 1e9),
             "peaks": pk["source"],
         },
         "clocks": clocks,
@@ -303,15 +319,29 @@ def main() -> int:
                      "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"]},
     }
     if not args.no_points:
-        pms, flops = prefill_run(args.prefill_tokens)
+        pms, pmed, flops = bench.prefill_run(args.prefill_tokens)
         result["prefill"] = {"value": round(args.prefill_tokens / (pms / 1e3), 1), "tokens": args.prefill_tokens,
-                             "ms": round(pms, 3),
+                             "ms": round(pms, 3), "median_ms": round(pmed, 3),
                              "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                             "frac_median": round(flops / (pmed / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
                              "of": pk["source"]}
         points = {}
+        side_steps = max(8, min(args.steps // 4, 64))
         for b in (1, 64):
-            v, _, _, _, _, _, _ = decode_run(b, max(8, args.steps // 4), 3)
+            v, bms, _, _, _, _, _ = bench.decode_run(b, side_steps, 3)
             points[f"decode_b{b}"] = round(v, 2)
+            points[f"decode_b{b}_hbm_frac"] = round(bench.step_bytes(b, side_steps) / (bms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+        if not args.no_presets and args.preset == "llama-3.1-8b" and args.layers is None:
+            # the other benchmark shapes, full size, the same batch and context
+            ops.check_kernel_status()
+            bench.close()
+            for other in ("llama-3.2-1b", "llama-2-13b"):
+                wb = Workbench(other, None, args, args.batch)
+                v, bms, _, _, _, _, _ = wb.decode_run(args.batch, side_steps, 3)
+                points[f"decode_b{args.batch}_{other}"] = round(v, 2)
+                points[f"decode_b{args.batch}_{other}_hbm_frac"] = round(
+                    wb.step_bytes(args.batch, side_steps) / (bms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+                wb.close()
         result["points"] = points
     ops.check_kernel_status()
     print(json.dumps(result))

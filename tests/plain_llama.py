@@ -183,8 +183,10 @@ def attention_mixer(x: torch.Tensor, positions: torch.Tensor, w: Mapping[str, to
 
 def llama_forward(cfg: Mapping, weights: Mapping[str, torch.Tensor],
                   tokens: Sequence[int], dtype: torch.dtype = torch.float32,
-                  round_to: Optional[torch.dtype] = None) -> torch.Tensor:
-    """Logits ``[T, vocab]`` of one whole sequence starting at position 0.
+                  round_to: Optional[torch.dtype] = None,
+                  rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Logits ``[T, vocab]`` of one whole sequence starting at position 0 (with ``rows``: only of
+    those positions, ``[len(rows), vocab]``; everything before the head still runs whole).
 
     Block order ``x -> norm -> attention -> +x -> norm -> ffn -> +x``
     (crates/allpaca-core/src/model.rs:8447-8696), final norm and head
@@ -210,6 +212,8 @@ def llama_forward(cfg: Mapping, weights: Mapping[str, torch.Tensor],
         x = x + swiglu_feed_forward(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                                     w[p + "mlp.down_proj.weight"], round_to)
     h = _round(rmsnorm(x, w["model.norm.weight"], s["eps"]), round_to)
+    if rows is not None:
+        h = h[torch.as_tensor(list(rows), dtype=torch.long)]
     head = w["model.embed_tokens.weight"] if (s["tied"] or "lm_head.weight" not in w) \
         else w["lm_head.weight"]
     return h @ head.T

@@ -81,3 +81,65 @@ def test_two_layers_of_the_8b_shape(tmp_path, monkeypatch, two_query_tiles):
         assert err < tol, (dtype, "portions", err)
         del runner, model
         torch.cuda.empty_cache()
+
+
+# ---------------------------------------------------------------------------
+# the same shape through bin/trace_run, in all four ways of cutting and batching
+# ---------------------------------------------------------------------------
+BIG_LENGTHS = [72, 150, 320]
+
+
+@pytest.fixture(scope="module")
+def big_model(tmp_path_factory):
+    """Two layers of the Llama-3.1-8B shape as model folders (float32, and its bfloat16
+    rounding), with the requests and what the plain implementation says about them."""
+    import helpers
+    from allpaca_b200.config.presets import preset_config
+    from allpaca_b200.weights.loader import write_model_folder
+    raw = preset_config("llama-3.1-8b")
+    raw["num_hidden_layers"] = 2
+    raw["max_position_embeddings"] = 512
+    root = tmp_path_factory.mktemp("big")
+    d32 = helpers.make_model_folder(str(root / "f32"), raw, 2, "float32")
+    w = helpers.load_weights(d32)
+    d16 = str(root / "bf16")
+    write_model_folder(d16, dict(helpers.load_config(d32), torch_dtype="bfloat16"),
+                       {k: v.to(torch.bfloat16) for k, v in w.items()})
+    requests = {str(i): helpers.random_tokens(n, raw["vocab_size"], 500 + i) for i, n in enumerate(BIG_LENGTHS)}
+    return {"config": raw, "float32": d32, "bfloat16": d16, "weights": w, "requests": requests}
+
+
+@pytest.mark.parametrize("dtype,two_query_tiles", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+def test_two_layers_of_the_8b_shape_replayed_in_every_mode(tmp_path, big_model, dtype, two_query_tiles):
+    """Whole; the last 32 tokens one by one; portions of changing size down to two tokens; mixed
+    with up to four live requests on a pool so small that pages are used again.  At this shape
+    the bfloat16 run is the one place where the tcgen05 products and the tcgen05 attention
+    (with ``two_query_tiles`` the kernel with two query tiles to a CTA for every portion of 64
+    rows or more) are compared with the plain implementation end to end."""
+    import os
+    import numpy as np
+    import helpers
+    from test_replay_gpu import build_trace
+    tb, alias, peak = build_trace(big_model["requests"], dense=False)
+    env = dict(os.environ)
+    if two_query_tiles:
+        env["ALLPACA_WIDE_ATTENTION_MIN_CTAS"] = "1"
+    outputs = helpers.run_trace(big_model[dtype], dtype, str(tmp_path / "out"), tb.steps, peak, env=env,
+                                timeout=1500)
+    # the plain logits of the rows the trace asks for, per request
+    wanted = {}
+    for k, rows in tb.rows.items():
+        for rid, pos in rows:
+            wanted.setdefault(alias[rid], set()).add(pos)
+    w = big_model["weights"]
+    if dtype == "bfloat16":
+        w = {k: v.to(torch.bfloat16) for k, v in w.items()}
+    reference = {}
+    for r, toks in big_model["requests"].items():
+        rows = sorted(wanted[r])
+        out = plain_llama.llama_forward(big_model["config"], w, toks, torch.float32,
+                                        round_to=torch.bfloat16 if dtype == "bfloat16" else None, rows=rows)
+        full = {pos: out[i].double().numpy() for i, pos in enumerate(rows)}
+        reference[r] = full
+    helpers.compare(outputs, tb, {rid: reference[r] for rid, r in alias.items()}, helpers.TOL[dtype],
+                    f"8B shape, 2 layers, {dtype}{', two query tiles' if two_query_tiles else ''}")

@@ -98,3 +98,19 @@ def test_engine_config_validation():
         EngineConfig(max_num_seqs=8, max_num_batched_tokens=4).validate()
     with pytest.raises(ConfigError):
         EngineConfig(page_size=0).validate()
+
+
+def test_head_size_the_kernels_do_not_take_is_refused_when_the_model_is_described():
+    """Multiples of 16 up to 256 are what the attention kernels are built for; any other head
+    size is a configuration error before weights are read, not a build error at the first step."""
+    from allpaca_b200.models import resolve
+    for bad in (8, 24, 40, 272):
+        raw = {"architectures": ["LlamaForCausalLM"], "hidden_size": 4 * bad, "num_attention_heads": 4,
+               "head_dim": bad}
+        arch = resolve(raw)
+        cfg = arch.config_class.from_dict(raw)
+        with pytest.raises(ConfigError, match="head_dim"):
+            arch.spec_builder(cfg)
+    raw = {"architectures": ["LlamaForCausalLM"], "hidden_size": 192, "num_attention_heads": 4, "head_dim": 48}
+    arch = resolve(raw)
+    assert arch.spec_builder(arch.config_class.from_dict(raw)).hidden_size == 192

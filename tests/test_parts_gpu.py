@@ -32,9 +32,9 @@ class Harness:
         from allpaca_b200.parts import LayerCache
         self.env = env
         self.manager = CacheManager([GroupLayout(env.page_size, num_pages, need.window)], max_seqs=4)
-        self.storage = GroupStorage(1, num_pages, need.num_kv_heads, env.page_size, need.head_dim,
-                                    env.dtype, env.device)
-        self.cache = LayerCache(kv=self.storage.run_view(0), group=0, writes=True)
+        self.storage = GroupStorage(1, num_pages, need.page_shape(env.page_size), need.dtype or env.dtype,
+                                    env.device)
+        self.cache = LayerCache(pages=self.storage.run_view(0), group=0, writes=True)
 
     def step(self, rows):
         """rows: list of (request, number of new rows)."""
@@ -156,8 +156,8 @@ def test_attention_mixer_in_portions(dtype, hidden, nh, nkv, hd, window):
     w = mixer_weights(hidden, nh, nkv, hd, dtype, seed=hd)
     assert {n: s.shape for n, s in mixer.weights().items()} == {n: tuple(t.shape) for n, t in w.items()}
     mixer.load({n: t.to(DEV) for n, t in w.items()})
-    need = mixer.kv_need()
-    assert (need.num_kv_heads, need.head_dim, need.window) == (nkv, hd, window)
+    need = mixer.cache_need()
+    assert (need.outer, need.inner, need.window) == ((2, nkv), (hd,), window)
     h = Harness(env, need)
     g = torch.Generator().manual_seed(1)
     seqs = {"a": torch.randn(70, hidden, generator=g).to(dtype), "b": torch.randn(33, hidden, generator=g).to(dtype)}
@@ -229,7 +229,7 @@ def test_prenorm_block(dtype):
                 t = 1 + t
             w[prefix + name] = t.to(dtype)
         part.load({name: w[prefix + name].to(DEV) for name in part.weights()})
-    h = Harness(env, block.mixer.kv_need())
+    h = Harness(env, block.mixer.cache_need())
     x0 = torch.randn(41, hidden, generator=g)
     x = x0.to(DEV).clone()
     pending = torch.randn(1, 41, hidden, generator=g)            # what an earlier block left to be added

@@ -19,16 +19,21 @@ def _round64(n):
     return -(-n // 64) * 64
 
 
-def build_trace(requests):
-    """All four modes in one trace; returns (builder, reference ids -> request, max tokens)."""
+def build_trace(requests, dense=True):
+    """All four modes in one trace; returns (builder, reference ids -> request, max tokens).
+    ``dense`` False asks for fewer rows' logits (a large vocabulary makes every row half a
+    megabyte): every seventh row and the last of a whole prompt, the ends of a portion."""
     tb = TraceBuilder()
     alias = {}
     peak = 0
+
+    def rows_of(n):
+        return list(range(n)) if dense else sorted({0, n - 1} | set(range(0, n, 7)) if n > 16 else {0, n - 1})
     # 1. whole
     for r, toks in requests.items():
         rid = f"w{r}"
         alias[rid] = r
-        tb.step([(rid, toks, list(range(len(toks))))], end=[rid])
+        tb.step([(rid, toks, rows_of(len(toks)))], end=[rid])
         peak = max(peak, _round64(len(toks)))
     # 2. most of it in one step, the last 32 one by one
     for r, toks in requests.items():
@@ -49,7 +54,7 @@ def build_trace(requests):
             n = min(PORTIONS[k % len(PORTIONS)], len(toks) - i)
             k += 1
             last = i + n == len(toks)
-            tb.step([(rid, toks[i:i + n], list(range(n)))], end=[rid] if last else [])
+            tb.step([(rid, toks[i:i + n], rows_of(n))], end=[rid] if last else [])
             i += n
     # 4. mixed: up to four live, portions of some beside decoded tokens of others
     rng = random.Random(1234)
@@ -69,7 +74,7 @@ def build_trace(requests):
                 continue                       # left out of this step, goes on later
             if at < int(0.6 * len(toks)):
                 n = min(rng.choice([2, 3, 5, 8, 13, 20]), len(toks) - at)
-                want = [n - 1] if rng.random() < 0.5 else list(range(n))
+                want = [n - 1] if rng.random() < 0.5 else rows_of(n)
             else:
                 n, want = 1, [0]
             entries.append((rid, toks[at:at + n], want))

@@ -232,3 +232,33 @@ def test_two_halves_of_advance_with_a_step_in_flight():
     assert a.output_token_ids == [7, 99] and b.output_token_ids == [7, 8]
     assert cache.num_running() == 0 and cache.num_free_pages() == 64
     assert s.schedule().rows == []
+
+
+def test_windowed_group_admits_a_prompt_longer_than_its_pool():
+    """A group with a window gives back the pages the window has passed, so a prompt longer than
+    the whole pool is accepted by add() and must then be admitted and run to its end: admission
+    asks for what the request holds at once, not for every token it will ever see."""
+    page, num_pages, window = 4, 12, 8
+    cache = CacheManager([GroupLayout(page, num_pages, window)], 4)
+    s = Scheduler(cache, 4, 16, 8, 1000)
+    s.add(req("long", 100, max_tokens=6))
+    s.add(req("second", 30, max_tokens=3))
+    done = {}
+    steps = 0
+    while s.has_unfinished():
+        out = s.schedule()
+        assert out.rows, "nothing was planned although requests are pending"
+        for r in out.rows:
+            if not cache.has(r.request.request_id):
+                cache.begin(r.request.request_id)
+            cache.append(r.request.request_id, r.count)
+            cache.release_passed(r.request.request_id)
+        cache.check()
+        fin = s.advance(out, {r.request.request_id: 7 for r in out.rows if r.samples})
+        for f in fin:
+            cache.free(f.request_id)
+            done[f.request_id] = f
+        steps += 1
+        assert steps < 500
+    assert len(done["long"].output_token_ids) == 6 and len(done["second"].output_token_ids) == 3
+    assert cache.num_free_pages() == num_pages and cache.num_running() == 0

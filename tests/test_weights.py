@@ -222,3 +222,32 @@ def test_native_header_reader_agrees_with_json_on_random_headers(tmp_path):
     check()
     with pytest.raises(SafetensorsError, match="NUL"):
         SafetensorsFile(_file_with_header(p, b'{"a\\u0000b":{"dtype":"U8","shape":[0],"data_offsets":[0,0]}}'))
+
+
+def test_matrices_stored_in_32_bit_under_a_bfloat16_engine(tmp_path, capsys):
+    """A 32-bit checkpoint loaded for a bfloat16 engine: kept (and said aloud, because such
+    matrices run on the slow CUDA-core product), rounded, or refused; norm weights stay 32-bit
+    in every case; a bfloat16 checkpoint says nothing."""
+    from allpaca_b200.weights import load_checkpoint
+    d32, d16 = str(tmp_path / "f32"), str(tmp_path / "bf16")
+    write_random_model(d32, TINY_A, 0, "float32", norm_std=0.02)
+    write_random_model(d16, TINY_A, 0, "bfloat16", norm_std=0.02)
+    cpu = torch.device("cpu")
+
+    def load(path, policy):
+        model = cpu_model(TINY_A)
+        load_checkpoint(model, path, torch.bfloat16, cpu, policy)
+        block = model.blocks[0]
+        return block.mixer.qkv.weight.dtype, block.mixer_norm.weight.dtype, model.embedding.dtype
+
+    assert load(d32, "keep") == (torch.float32, torch.float32, torch.float32)
+    said = capsys.readouterr().err
+    assert "stored in 32-bit" in said and "CUDA cores" in said
+    assert load(d32, "round") == (torch.bfloat16, torch.float32, torch.bfloat16)
+    assert capsys.readouterr().err == ""
+    with pytest.raises(WeightError, match="stored in 32-bit"):
+        load(d32, "refuse")
+    assert load(d16, "keep") == (torch.bfloat16, torch.bfloat16, torch.bfloat16)
+    assert capsys.readouterr().err == ""
+    with pytest.raises(WeightError, match="float32_weights"):
+        load(d16, "sometimes")

@@ -5,8 +5,10 @@ inside a fixed carve-out of memory, or in a loop that may not touch the allocato
 them the library keeps the scratch of the split-key attention kernel in a fixed array of
 its own.  This test calls that entry point through its exported C symbol, twice in a row
 (the second call meets whatever the first left in the array), and checks both results
-against the regular entry point, which takes its scratch from the caller.  It also checks
-that a call whose scratch would not fit is refused with a message.
+against the regular entry point, which takes its scratch from the caller, and against a
+plain float64 attention over the same keys and values (so that the two entry points cannot
+be wrong together).  It also checks that a call whose scratch would not fit is refused with
+a message.
 
 The file sorts last so that a run that stops at the first failure has already run
 everything else; it passes alone in a fresh process as well.
@@ -66,6 +68,23 @@ def _regular(q, cache, table, positions, scale, window):
     return out
 
 
+def _plain(q, cache, table, positions, window):
+    """Every sequence's single query row against its own keys, gathered page by page, with the
+    plain implementation under tests/ (whole sequences: earlier positions get empty queries)."""
+    import plain_llama
+    out = torch.empty(q.shape[0], NH, HD, dtype=torch.float64)
+    cache, table = cache.double().cpu(), table.cpu()
+    for s in range(q.shape[0]):
+        n = int(positions[s]) + 1
+        pages = table[s, : -(-n // P)].long()
+        k = cache[pages, 0].permute(0, 2, 1, 3).reshape(-1, NKV, HD)[:n]
+        v = cache[pages, 1].permute(0, 2, 1, 3).reshape(-1, NKV, HD)[:n]
+        whole = torch.zeros(n, NH, HD, dtype=torch.float64)
+        whole[-1] = q[s].double().cpu().view(NH, HD)
+        out[s] = plain_llama.causal_attention(whole, k, v, window=window or None)[-1]
+    return out.view(q.shape[0], NH * HD)
+
+
 def test_static_scratch_entry_matches_the_regular_one_twice():
     lib = _library()
     stream = torch.cuda.current_stream().cuda_stream
@@ -84,6 +103,10 @@ def test_static_scratch_entry_matches_the_regular_one_twice():
         # the same kernels with a different number of key slices: the tolerance of the
         # bfloat16 attention tests
         assert err < 1.5e-2, f"call {call}: error {err:.3e}"
+        plain = _plain(q, cache, table, positions, window)
+        for what, t in (("static scratch", got), ("regular", want)):
+            err = float((t.double().cpu() - plain).abs().max() / plain.abs().max())
+            assert err < 1.5e-2, f"call {call}: {what} entry is {err:.3e} off the plain attention"
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit():
