@@ -63,10 +63,10 @@ def bench_gemm(args) -> dict:
                                               share_tiles=not args.whole_tiles)
         S = 1
     elif args.dual:
-        # two weight tiles per CTA; with --swiglu w is [gate; up]
+        # two weight tiles per CTA
         kernel = "gemm_tc_dual"
-        out = torch.empty(M, N // 2 if args.swiglu else N, device="cuda", dtype=odt)
-        fn = lambda i: ops.gemm_tc_dual(a, ws[i % copies], out, swiglu=args.swiglu)   # noqa: E731
+        out = torch.empty(M, N, device="cuda", dtype=odt)
+        fn = lambda i: ops.gemm_tc_dual(a, ws[i % copies], out)   # noqa: E731
         S = 1
     elif args.swiglu:
         # up to 256 rows: the gated activation in the epilogue of the (cluster) kernel

@@ -24,7 +24,19 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const TW* __
     tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
     const TW* src = table + (size_t)tok * H;
     float* dst = x + (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ap_to_float(src[i]) * scale;
+    // blockIdx.y walks the row in runs of blockDim.x elements (or of four times as many where the
+    // row can be moved four elements at a time)
+    if (sizeof(TW) == 2 && H % 4 == 0 && (((uintptr_t)table | (uintptr_t)x) & 15) == 0) {
+        for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < H; i += gridDim.y * blockDim.x * 4) {
+            const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(src) + i);
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+            const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+            *reinterpret_cast<float4*>(dst + i) = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+        }
+        return;
+    }
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < H; i += gridDim.y * blockDim.x)
+        dst[i] = ap_to_float(src[i]) * scale;
 }
 
 AP_EXPORT int ap_embed_gather(const int* tokens, const void* table, int table_dtype, float* x,
@@ -32,13 +44,16 @@ AP_EXPORT int ap_embed_gather(const int* tokens, const void* table, int table_dt
     AP_REQUIRE(T >= 0 && H > 0 && V > 0, "embed_gather: bad sizes T=%d H=%d V=%d", T, H, V);
     if (T == 0) return AP_OK;
     const int threads = H >= 1024 ? 256 : 128;
+    // few rows: several blocks to a row, so that a decode step's handful of rows is not one
+    // long chain of loads per thread
+    const dim3 grid(T, T <= 64 ? (H + 4 * threads - 1) / (4 * threads) : 1);
     // The first kernel of a step is launched in plain stream order: it starts when everything
     // before it on the stream has finished.  Kernels later in the step may therefore read what
     // earlier steps wrote (the cache) ahead of their own dependency wait.
     if (table_dtype == AP_F32)
-        embed_gather_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, x, H, V, scale);
+        embed_gather_kernel<float><<<grid, threads, 0, stream>>>(tokens, (const float*)table, x, H, V, scale);
     else if (table_dtype == AP_BF16)
-        embed_gather_kernel<bf16><<<T, threads, 0, stream>>>(tokens, (const bf16*)table, x, H, V, scale);
+        embed_gather_kernel<bf16><<<grid, threads, 0, stream>>>(tokens, (const bf16*)table, x, H, V, scale);
     else
         AP_REQUIRE(false, "embed_gather: unknown table dtype %d", table_dtype);
     AP_CHECK_LAUNCH("embed_gather");
@@ -254,6 +269,8 @@ AP_EXPORT int ap_logit_transform(float* logits, const void* bias, int bias_dtype
 //   cos_sin: [T][hd/2] (cos, sin) pairs from rope_table_kernel, or nullptr for no rotation
 //   pairing 0: pairs (i, i + hd/2)   (checkpoints in the Hugging Face layout)
 //   pairing 1: pairs (2i, 2i + 1)    (checkpoints whose Q/K rows were permuted)
+//   pairing 2: the input holds the pair (i, i + hd/2) side by side at (2i, 2i + 1) (the rows of
+//              the projection's weight were interleaved so); the output is in the usual order
 // ---------------------------------------------------------------------------
 template <typename TI>
 __device__ __forceinline__ float load_partial(const TI* in, int S, size_t stride, size_t idx) {
@@ -288,30 +305,63 @@ AP_EXPORT int ap_rope_table(const int* positions, const float* inv_freq, float* 
     return AP_OK;
 }
 
-// A page is first written at its slot 0 (a request's positions are contiguous).  The threads
-// that store the token of slot 0 also clear the slots of the page behind the last one this step
-// writes (`last_slot`, counted from slot 0; the slots up to it belong to other rows of this
-// launch): the attention kernels load whole pages and weigh what lies behind a row's position
-// with a probability of exactly zero, which only gives zero if it is finite, and a page that
-// was given back keeps its last owner's values, whatever they were.
-template <typename TO>
-__device__ __forceinline__ void clear_page_tail(TO* __restrict__ page, int last_slot, int nkv, int hd, int P,
-                                                int worker, int workers) {
-    const int first = last_slot + 1;
-    if (first >= P) return;
-    const int per_plane = (P - first) * hd;               // the cleared slots of one head are contiguous
-    const int total = 2 * nkv * per_plane;
-    if (sizeof(TO) == 2 && hd % 8 == 0 && (((uintptr_t)page) & 15) == 0) {
-        for (int i = worker; i < total / 8; i += workers) {
-            const int plane = (i * 8) / per_plane, e = i * 8 - plane * per_plane;
-            *reinterpret_cast<uint4*>(page + ((size_t)plane * P + first) * hd + e) = make_uint4(0, 0, 0, 0);
-        }
-    } else {
-        for (int i = worker; i < total; i += workers) {
-            const int plane = i / per_plane, e = i - plane * per_plane;
-            page[((size_t)plane * P + first) * hd + e] = ap_from_float<TO>(0.f);
-        }
+// ---------------------------------------------------------------------------
+// A page is first written at its slot 0 (a request's positions are contiguous).  Before the
+// layers of a step run, the slots of such a page behind the last one this step writes are
+// cleared in every run of the cache group: the attention kernels load whole pages and weigh
+// what lies behind a row's position with a probability of exactly zero, which only gives zero
+// if it is finite, and a page that was given back keeps its last owner's values, whatever they
+// were.  pages: [runs][num_pages][outer][P][inner] of 1-, 2- or 4-byte elements.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void clear_page_tails_kernel(T* __restrict__ pages, size_t run_stride, size_t page_stride, int runs,
+                                        int outer, int P, int inner, const int* __restrict__ positions,
+                                        const int* __restrict__ token_seq, const int* __restrict__ block_table,
+                                        int max_blocks, const int* __restrict__ context_lens) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    if (pos % P != 0) return;
+    const int seq = token_seq[t];
+    const int page = block_table[(size_t)seq * max_blocks + pos / P];
+    const int first = context_lens[seq] - pos;          // slots 0 .. first-1 are written by this step's rows
+    if (page < 0 || first >= P) return;
+    const size_t per_plane = (size_t)(P - first) * inner;  // the cleared slots of one plane are contiguous
+    const size_t total = (size_t)runs * outer * per_plane;
+    for (size_t i = blockIdx.y * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.y * blockDim.x) {
+        const size_t plane = i / per_plane, e = i - plane * per_plane;
+        const size_t run = plane / outer, o = plane - run * outer;
+        pages[run * run_stride + (size_t)page * page_stride + (o * P + first) * inner + e] = T(0);
     }
+}
+
+AP_EXPORT int ap_clear_page_tails(void* pages, int elem_bytes, long long run_stride, long long page_stride, int runs,
+                                  int outer, int P, int inner, const int* positions, const int* token_seq,
+                                  const int* block_table, int max_blocks, const int* context_lens, int T,
+                                  cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && runs > 0 && outer > 0 && P > 0 && inner > 0 && max_blocks > 0,
+               "clear_page_tails: bad sizes runs=%d outer=%d page=%d inner=%d", runs, outer, P, inner);
+    AP_REQUIRE(pages && positions && token_seq && block_table && context_lens, "clear_page_tails: a pointer is missing");
+    if (T == 0) return AP_OK;
+    // elements are cleared in the widest unit that divides a slot's bytes (zero is zero in every type)
+    long long unit = elem_bytes;
+    while (unit < 8 && ((long long)inner * elem_bytes) % (unit * 2) == 0 && ((uintptr_t)pages % (unit * 2)) == 0 &&
+           (run_stride * elem_bytes) % (unit * 2) == 0 && (page_stride * elem_bytes) % (unit * 2) == 0)
+        unit *= 2;
+    const int scale = (int)(unit / elem_bytes);
+    dim3 grid(T, 8);
+#define LAUNCH(TT)                                                                                            \
+    clear_page_tails_kernel<TT><<<grid, 256, 0, stream>>>((TT*)pages, (size_t)(run_stride / scale),          \
+                                                          (size_t)(page_stride / scale), runs, outer, P,     \
+                                                          inner / scale, positions, token_seq, block_table,   \
+                                                          max_blocks, context_lens)
+    if (unit == 8) LAUNCH(unsigned long long);
+    else if (unit == 4) LAUNCH(unsigned int);
+    else if (unit == 2) LAUNCH(unsigned short);
+    else if (unit == 1) LAUNCH(unsigned char);
+    else AP_REQUIRE(false, "clear_page_tails: elements of %d bytes", elem_bytes);
+#undef LAUNCH
+    AP_CHECK_LAUNCH("clear_page_tails");
+    return AP_OK;
 }
 
 // One thread per pair of elements: (nh + nkv) * half rotated pairs, then nkv * half pairs of V.
@@ -324,8 +374,7 @@ rope_kv_store_kernel(const TI* __restrict__ in, int S, size_t in_stride,
                      const int* __restrict__ token_seq,
                      const int* __restrict__ block_table, int max_blocks,
                      const float2* __restrict__ cos_sin, int pairing,
-                     int nh, int nkv, int hd, int P, size_t page_stride,
-                     const int* __restrict__ context_lens) {
+                     int nh, int nkv, int hd, int P, size_t page_stride) {
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int item = blockIdx.y * ROPE_THREADS + threadIdx.x;
@@ -337,23 +386,22 @@ rope_kv_store_kernel(const TI* __restrict__ in, int S, size_t in_stride,
     int page = -1, off = 0;
     if (cache) {
         const int ipos = positions[t];
-        const int seq = token_seq[t];
-        page = block_table[(size_t)seq * max_blocks + ipos / P];
+        page = block_table[(size_t)token_seq[t] * max_blocks + ipos / P];
         off = ipos % P;
-        if (context_lens && off == 0 && page >= 0)
-            clear_page_tail(cache + (size_t)page * page_stride, context_lens[seq] - 1 - ipos, nkv, hd, P,
-                            blockIdx.y * ROPE_THREADS + threadIdx.x, gridDim.y * ROPE_THREADS);
     }
     if (item >= rot_pairs + v_pairs) return;
     if (item < rot_pairs) {
         const int head = item / half, i = item - head * half;
         if (head >= nh && page < 0) return;
-        const int ia = pairing == 0 ? i : 2 * i;
-        const int ib = pairing == 0 ? i + half : 2 * i + 1;
+        // where the pair lies in the input, and where it goes (pairing 2: neighbours in, halves out)
+        const int ia = pairing == 1 ? 2 * i : i;
+        const int ib = pairing == 1 ? 2 * i + 1 : i + half;
+        const int ia_in = pairing == 0 ? i : 2 * i;
+        const int ib_in = pairing == 0 ? i + half : 2 * i + 1;
         const size_t base = row + (size_t)head * hd;
         // partial sums are rounded to the storage type once they are complete
-        const float a = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + ia)));
-        const float b = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + ib)));
+        const float a = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + ia_in)));
+        const float b = ap_to_float(ap_from_float<TO>(load_partial(in, S, in_stride, base + ib_in)));
         float ra = a, rb = b;
         if (cos_sin) {
             const float2 cs = cos_sin[(size_t)t * half + i];
@@ -381,7 +429,7 @@ rope_kv_store_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ q_ou
                             const int* __restrict__ positions, const int* __restrict__ token_seq,
                             const int* __restrict__ block_table, int max_blocks,
                             const float2* __restrict__ cos_sin, int nh, int nkv, int hd, int P,
-                            size_t page_stride, const int* __restrict__ context_lens) {
+                            size_t page_stride, int interleaved) {
     const int t = blockIdx.x;
     const int half = hd >> 1, h8 = half >> 3;             // groups of 8 pairs per head
     const int item = blockIdx.y * ROPE_THREADS + threadIdx.x;
@@ -393,20 +441,32 @@ rope_kv_store_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ q_ou
     int page = -1, off = 0;
     if (cache) {
         const int ipos = positions[t];
-        const int seq = token_seq[t];
-        page = block_table[(size_t)seq * max_blocks + ipos / P];
+        page = block_table[(size_t)token_seq[t] * max_blocks + ipos / P];
         off = ipos % P;
-        if (context_lens && off == 0 && page >= 0)
-            clear_page_tail(cache + (size_t)page * page_stride, context_lens[seq] - 1 - ipos, nkv, hd, P,
-                            blockIdx.y * ROPE_THREADS + threadIdx.x, gridDim.y * ROPE_THREADS);
     }
     if (item >= rot_items + v_items) return;
     if (item < rot_items) {
         const int head = item / h8, i = (item - head * h8) * 8;
         if (head >= nh && page < 0) return;
         const bf16* src = in + row + (size_t)head * hd;
-        const uint4 a4 = *reinterpret_cast<const uint4*>(src + i);
-        const uint4 b4 = *reinterpret_cast<const uint4*>(src + i + half);
+        uint4 a4, b4;
+        if (interleaved) {
+            // elements 2i .. 2i+15 hold the pairs (a_k, b_k) side by side: split them
+            const uint4 lo = *reinterpret_cast<const uint4*>(src + 2 * i);
+            const uint4 hi = *reinterpret_cast<const uint4*>(src + 2 * i + 8);
+            const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            uint32_t aw[4], bw[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                aw[k] = __byte_perm(w[2 * k], w[2 * k + 1], 0x5410);      // low halves: a_2k, a_2k+1
+                bw[k] = __byte_perm(w[2 * k], w[2 * k + 1], 0x7632);      // high halves: b_2k, b_2k+1
+            }
+            a4 = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+            b4 = make_uint4(bw[0], bw[1], bw[2], bw[3]);
+        } else {
+            a4 = *reinterpret_cast<const uint4*>(src + i);
+            b4 = *reinterpret_cast<const uint4*>(src + i + half);
+        }
         const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a4);
         const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b4);
         uint4 ra4 = a4, rb4 = b4;
@@ -439,16 +499,16 @@ AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in
                                void* cache, int act_dtype, const int* positions, const int* token_seq,
                                const int* block_table, int max_blocks, const float* cos_sin, int pairing,
                                int T, int nh, int nkv, int hd, int P, long long page_stride,
-                               const int* context_lens, cudaStream_t stream) {
+                               cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && nh > 0 && nkv >= 0 && hd > 0 && (hd % 2) == 0 && S >= 1,
                "rope_kv_store: bad sizes T=%d heads=%d kv_heads=%d head_dim=%d S=%d", T, nh, nkv, hd, S);
-    AP_REQUIRE(pairing == 0 || pairing == 1, "rope_kv_store: unknown pairing %d", pairing);
+    AP_REQUIRE(pairing >= 0 && pairing <= 2, "rope_kv_store: unknown pairing %d", pairing);
     AP_REQUIRE(cache == nullptr || (P > 0 && page_stride >= 2LL * nkv * P * hd),
                "rope_kv_store: page stride %lld is below one page of keys and values", page_stride);
     AP_REQUIRE(cache == nullptr || (token_seq && block_table && max_blocks > 0),
                "rope_kv_store: storing needs the block table and the rows' sequences");
     if (T == 0) return AP_OK;
-    if (in_dtype == AP_BF16 && act_dtype == AP_BF16 && S == 1 && pairing == 0 && hd % 16 == 0 &&
+    if (in_dtype == AP_BF16 && act_dtype == AP_BF16 && S == 1 && pairing != 1 && hd % 16 == 0 &&
         ((uintptr_t)in & 15) == 0 && ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)cache & 15) == 0 &&
         page_stride % 8 == 0 && ((uintptr_t)cos_sin & 15) == 0) {
         const int items8 = (nh + nkv) * (hd / 16) + (cache ? nkv * (hd / 8) : 0);
@@ -457,7 +517,7 @@ AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in
         AP_CHECK_PDL_LAUNCH("rope_kv_store", ap_launch_pdl(
             rope_kv_store_bf16x8_kernel, grid8, dim3(ROPE_THREADS), 0, stream, (const bf16*)in, (bf16*)q_out,
             (bf16*)cache, positions, token_seq, block_table, max_blocks, (const float2*)cos_sin, nh, nkv, hd, P,
-            (size_t)page_stride, context_lens));
+            (size_t)page_stride, pairing == 2 ? 1 : 0));
         return AP_OK;
     }
     const int items = (nh + nkv) * (hd / 2) + (cache ? nkv * (hd / 2) : 0);
@@ -467,8 +527,7 @@ AP_EXPORT int ap_rope_kv_store(const void* in, int in_dtype, int S, long long in
     AP_CHECK_PDL_LAUNCH("rope_kv_store", ap_launch_pdl(                                             \
         rope_kv_store_kernel<TI, TO>, grid, dim3(ROPE_THREADS), 0, stream,                          \
         (const TI*)in, S, (size_t)in_stride, (TO*)q_out, (TO*)cache, positions, token_seq,         \
-        block_table, max_blocks, (const float2*)cos_sin, pairing, nh, nkv, hd, P, (size_t)page_stride, \
-        context_lens))
+        block_table, max_blocks, (const float2*)cos_sin, pairing, nh, nkv, hd, P, (size_t)page_stride))
     if (in_dtype == AP_F32 && act_dtype == AP_F32) LAUNCH(float, float);
     else if (in_dtype == AP_F32 && act_dtype == AP_BF16) LAUNCH(float, bf16);
     else if (in_dtype == AP_BF16 && act_dtype == AP_BF16) {

@@ -29,7 +29,6 @@
 #define TC_ERR_ACCUM_WAIT 3
 
 static __device__ int g_tc_status;
-static long long g_l2_prefetch_budget = 0;      // bytes; set by ap_gemm_tc_set_l2_prefetch
 
 template <int BN, bool CLUSTER = false> struct TileCfg {
     // 64 rows in a cluster: three stages, so that two CTAs with their reduction buffers share an SM
@@ -37,7 +36,7 @@ template <int BN, bool CLUSTER = false> struct TileCfg {
     static constexpr int kBBytes = BN * TILE_K * 2;
     static constexpr int kStageBytes = A_TILE_BYTES + kBBytes;
     static constexpr int kTmemCols = BN < 32 ? 32 : BN;
-    static constexpr int kBarrierBytes = 256;
+    static constexpr int kBarrierBytes = 256 + 1024;      // barriers, then the scale of each token column
     // cluster reduction buffer: [slices][BN][rows per slice], at most 136 rows in all
     static constexpr int kReduceBytes = (TILE_W + 8) * BN * 4;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + kBarrierBytes;
@@ -47,22 +46,94 @@ template <int BN, bool CLUSTER = false> struct TileCfg {
     static_assert(!kReduceOverStages || kReduceBytes <= kStages * kStageBytes, "the reduction buffer must fit the stages");
 };
 
+// What the epilogue does with the finished sums.
+//   EPI_PLAIN     out[m, n] = sum                                  (32-bit or bfloat16 out)
+//   EPI_PAIRS     the weight's rows alternate gate, up, gate, up ...; the sums of row 2i and 2i+1
+//                 become out[m, i] = silu(gate) * up (out is [M, N/2]), so that the gated
+//                 activation of a decode step needs no kernel of its own
+//   EPI_RESIDUAL  out is the 32-bit residual stream: out[m, n] += sum; the updated value also goes
+//                 to xb[m, n] in bfloat16 (the next product's input), and partial sums of squares
+//                 of the updated rows go to ss_out[m, part] (every part is written, none added to)
+//   EPI_ROPE      the weight is [W_q; W_k; W_v] of an attention layer: the sums of every pair of
+//                 neighbouring rows of the Q and K heads are rotated by the row's position (the
+//                 table of cosines and sines) and Q goes to q_out, K and V into the cache page and
+//                 slot of the row's position.  pairing 0: the rows of each Q and K head were
+//                 interleaved beforehand so that rows 2j and 2j+1 hold elements j and j + hd/2,
+//                 and the results go back to their places; pairing 1: neighbouring elements pair
+// PLAIN and PAIRS can scale token column m by 1/sqrt(mean square + eps) of the product's input
+// row m, given as partial sums of squares (ss_in): an RMSNorm whose weight was multiplied into
+// this product's weight beforehand then needs no kernel of its own either.
+#define EPI_PLAIN 0
+#define EPI_PAIRS 1
+#define EPI_RESIDUAL 2
+#define EPI_ROPE 3
+
+struct EpiArgs {
+    const float* ss_in;      // [M][ss_in_parts] or nullptr: no scale
+    int ss_in_parts;
+    float inv_width;         // 1 / (elements of an input row that the squares were summed over)
+    float eps;
+    bf16* xb;                // EPI_RESIDUAL: [M][ldxb]
+    long long ldxb;
+    float* ss_out;           // EPI_RESIDUAL: [M][ss_out_parts]
+    int ss_out_parts;
+    // EPI_ROPE
+    bf16* q_out;             // [M][nh * hd]
+    bf16* cache;             // one layer's pages [page][2][nkv][P][hd], or nullptr: store no K, V
+    const int* positions;    // [M]
+    const int* token_seq;    // [M] row of the block table
+    const int* block_table;  // [.][max_blocks]
+    const float2* cos_sin;   // [M][hd/2] (cos, sin), or nullptr: no rotation
+    long long page_stride;
+    int max_blocks, nh, nkv, hd, P, pairing;
+};
+
+// One pair of neighbouring rows (n even, n + 1) of the stacked Q, K, V projection for token m:
+// a and b are the finished sums in the storage type's precision.
+__device__ __forceinline__ void rope_store_pair(const EpiArgs& ea, int m, int n, float a, float b) {
+    const int hd = ea.hd, half = hd >> 1;
+    const int head = n / hd, r = n - head * hd, j = r >> 1;
+    int ia = r, ib = r + 1;
+    if (head < ea.nh + ea.nkv) {
+        if (ea.pairing == 0) { ia = j; ib = j + half; }
+        if (ea.cos_sin) {
+            const float2 cs = ea.cos_sin[(size_t)m * half + j];
+            const float ra = a * cs.x - b * cs.y, rb = a * cs.y + b * cs.x;
+            a = ra;
+            b = rb;
+        }
+    }
+    bf16* dst;
+    if (head < ea.nh) {
+        dst = ea.q_out + (size_t)m * ea.nh * hd + (size_t)head * hd;
+    } else {
+        if (ea.cache == nullptr) return;
+        const int pos = ea.positions[m];
+        const int page = ea.block_table[(size_t)ea.token_seq[m] * ea.max_blocks + pos / ea.P];
+        if (page < 0) return;
+        const int kvh = head - ea.nh;                       // K heads, then V heads: the page's planes in order
+        dst = ea.cache + (size_t)page * ea.page_stride + ((size_t)kvh * ea.P + pos % ea.P) * hd;
+    }
+    dst[ia] = __float2bfloat16_rn(a);
+    dst[ib] = __float2bfloat16_rn(b);
+}
+
+__device__ __forceinline__ float gated(float gate, float up) { return __fdividef(gate, 1.0f + __expf(-gate)) * up; }
+// the four epilogue warps among themselves (barrier 1; barrier 0 is __syncthreads)
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 // CLUSTER: the gridDim.z K-slices of one output tile form a thread-block cluster and add
 // their partial tiles through distributed shared memory, each CTA finishing a band of the
-// 128 weight rows; `out` is then the finished [M, N] matrix.  Otherwise slice z writes its
-// partial sums to out + z * split_stride.
-// PAIRS: the weight's rows alternate gate, up, gate, up ...; the finished sums of row 2i and
-// 2i+1 become out[m, i] = silu(gate) * up (out is [M, N/2]), so that the gated activation of a
-// decode step needs no kernel of its own.
-__device__ __forceinline__ float gated(float gate, float up) { return __fdividef(gate, 1.0f + __expf(-gate)) * up; }
-
-template <int BN, typename TO, bool CLUSTER, bool PAIRS = false>
+// 128 weight rows; `out` is then the finished matrix.  Otherwise slice z writes its
+// partial sums to out + z * split_stride (EPI_PLAIN only).
+template <int BN, typename TO, bool CLUSTER, int EPI = EPI_PLAIN>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                TO* __restrict__ out, int M, int N, int K, long long ldc, int kb_per_split,
-               long long split_stride, int l2_prefetch_tiles) {
+               long long split_stride, const EpiArgs ea) {
     using Cfg = TileCfg<BN, CLUSTER>;
     constexpr int STAGES = Cfg::kStages;
+    constexpr bool PAIRS = EPI == EPI_PAIRS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* w_tiles = smem;
@@ -72,11 +143,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     uint64_t* accum = empty + STAGES;
     uint32_t* tmem_slot = (uint32_t*)(accum + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* inv_s = (float*)(smem + STAGES * Cfg::kStageBytes + 256);      // [BN] scale of each token column
     // CLUSTER with 128 tokens or more: the buffer the slices' partial sums are gathered in lies
     // over the operand stages, and a cluster barrier makes sure every CTA is done with them
     constexpr bool REUSE = CLUSTER && Cfg::kReduceOverStages;
     float* reduce = REUSE ? (float*)smem : (float*)(smem + STAGES * Cfg::kStageBytes + Cfg::kBarrierBytes);
     bool have_acc = false;          // epilogue threads: the accumulator is complete and may be read
+    float xin_first[16];            // epilogue threads, EPI_RESIDUAL in a cluster: see below
 
     // once a wait has expired anywhere, later CTAs do nothing: the product is void anyway.
     // (In a cluster every CTA still walks to the cluster barrier, or its peers would wait.)
@@ -122,12 +195,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             for (int i = 0; i < pre; ++i) {
                 tc::mbar_expect_tx(&full[i], Cfg::kStageBytes);
                 tc::tma_load_2d(w_tiles + i * A_TILE_BYTES, &tmap_w, (kb0 + i) * TILE_K, n0, &full[i]);
-            }
-            // ... and ask L2 for the rest of this CTA's weight slice, so that HBM keeps streaming
-            // while the kernels before this one finish
-            if (l2_prefetch_tiles > 0) {
-                const int last = min(nkb, pre + l2_prefetch_tiles);
-                for (int i = pre; i < last; ++i) tc::tma_prefetch_l2_2d(&tmap_w, (kb0 + i) * TILE_K, n0);
             }
             ap_pdl_wait();
             for (int i = 0; i < pre; ++i)
@@ -184,7 +251,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const int q = warp & 3;
         const int row = q * 32 + lane;
         const int n = n0 + row;
+        const int et = (int)threadIdx.x - 64;
         ap_pdl_wait();          // `out` may still be read by an earlier kernel
+        if (CLUSTER && EPI == EPI_RESIDUAL && !skip) {
+            // The residual's old values at the first sixteen places this thread will finish
+            // (nobody else writes the residual while this product runs): fetched now, long before
+            // the sums are complete, so that their latency is not paid at the end.
+            const int S = gridDim.z;
+            const int band = (TILE_W + S - 1) / S;
+            const int first = blockIdx.z * band;
+            const int rows = max(1, min(band, TILE_W - first));
+            const int total = rows * min(BN, M - m0);
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const int idx = u * 128 + et;
+                const int c = idx / rows, i = idx - c * rows;
+                xin_first[u] = (idx < total && n0 + first + i < N)
+                                   ? reinterpret_cast<float*>(out)[(size_t)(m0 + c) * ldc + n0 + first + i] : 0.f;
+            }
+        }
+        // the scale of every token column of this tile, from the partial sums of squares of the
+        // product's input rows (1 where there is no deferred norm): 128 / BN threads share a
+        // token's parts (each every TPT-th one) and add their sums up by butterfly
+        {
+            constexpr int TPT = BN >= 128 ? 1 : 128 / BN;               // threads per token: 1, 2, 4 or 8
+            for (int c0 = 0; c0 < BN; c0 += 128 / TPT) {
+                const int c = c0 + et / TPT, sub = et % TPT;
+                float ss = 0.f;
+                const bool live = ea.ss_in != nullptr && m0 + c < M;
+                if (live) {
+                    const float* p = ea.ss_in + (size_t)(m0 + c) * ea.ss_in_parts;
+                    for (int i = sub; i < ea.ss_in_parts; i += TPT) ss += p[i];
+                }
+#pragma unroll
+                for (int o = TPT >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (sub == 0) inv_s[c] = live ? 1.0f / sqrtf(ss * ea.inv_width + ea.eps) : 1.0f;
+            }
+        }
+        epilogue_sync();
         bool have = nkb > 0;
         if (have) {
             if (!tc::mbar_wait(accum, 0)) {
@@ -220,7 +324,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 for (int j = 0; j < 16; ++j)
                     tc::st_cluster_f32(base + (uint32_t)((c + j) * band) * 4u, __uint_as_float(v[j]));
             }
-        } else if (have) {
+        } else if (__all_sync(0xffffffffu, have)) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 if (m0 + c >= M) break;
@@ -235,20 +339,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const uint32_t other = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[8 + j], 1);
-                        const float gt = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? other : v[j])));
-                        const float up = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? v[8 + j] : other)));
-                        const int m = m0 + c + (odd ? 8 : 0) + j;
+                        const int col = c + (odd ? 8 : 0) + j;
+                        const float sc = inv_s[col];
+                        const float gt = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? other : v[j]) * sc));
+                        const float up = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? v[8 + j] : other) * sc));
+                        const int m = m0 + col;
                         if (m < M && n < N) out[(size_t)m * ldc + (n >> 1)] = ap_from_float<TO>(gated(gt, up));
+                    }
+                } else if (EPI == EPI_ROPE) {
+                    // even lane: row n, odd lane: row n + 1 of a pair; the even lane finishes token
+                    // columns c..c+7, the odd lane c+8..c+15, each with the other's half
+                    const bool odd = lane & 1;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t other = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[8 + j], 1);
+                        const int col = c + (odd ? 8 : 0) + j;
+                        const float sc = inv_s[col];
+                        const float a = ap_to_float(__float2bfloat16_rn(__uint_as_float(odd ? other : v[j]) * sc));
+                        const float b = ap_to_float(__float2bfloat16_rn(__uint_as_float(odd ? v[8 + j] : other) * sc));
+                        const int m = m0 + col;
+                        if (m < M && n < N) rope_store_pair(ea, m, n & ~1, a, b);
+                    }
+                } else if (EPI == EPI_RESIDUAL) {
+                    // lane = weight row n: add into the residual, keep its bfloat16 copy, and sum the
+                    // squares of this warp's 32 rows for every token (lanes by butterfly: a fixed order)
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = m0 + c + j;
+                        float xv = 0.f;
+                        if (m < M && n < N) {
+                            float* px = reinterpret_cast<float*>(out) + (size_t)m * ldc + n;
+                            xv = *px + __uint_as_float(v[j]);
+                            *px = xv;
+                            ea.xb[(size_t)m * ea.ldxb + n] = __float2bfloat16_rn(xv);
+                        }
+                        const float sq = ap_warp_sum(xv * xv);
+                        if (lane == 0 && m < M) ea.ss_out[(size_t)m * ea.ss_out_parts + blockIdx.y * 4 + q] = sq;
                     }
                 } else if (n < N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + c + j;
-                        if (m < M) out[(size_t)m * ldc + n] = ap_from_float<TO>(__uint_as_float(v[j]));
+                        if (m < M) out[(size_t)m * ldc + n] = ap_from_float<TO>(__uint_as_float(v[j]) * inv_s[c + j]);
                     }
                 }
             }
-        } else if (nkb == 0 && n < N && (!PAIRS || !(lane & 1))) {
+        } else if (nkb == 0 && EPI != EPI_RESIDUAL && EPI != EPI_ROPE && n < N && (!PAIRS || !(lane & 1))) {
             for (int c = 0; c < BN; ++c) {
                 const int m = m0 + c;
                 if (m < M) out[(size_t)m * ldc + (PAIRS ? n >> 1 : n)] = ap_from_float<TO>(0.f);
@@ -288,13 +424,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
     }
     if (CLUSTER) {
-        __syncwarp();
-        tc::cluster_sync();                 // every slice has delivered its partial sums
         const int S = gridDim.z;
         const int band = (TILE_W + S - 1) / S;
         const int first = blockIdx.z * band;
         const int rows = max(0, min(band, TILE_W - first));
         const int e = (int)threadIdx.x - 64;              // the four epilogue warps add the band
+        __syncwarp();
+        tc::cluster_sync();                 // every slice has delivered its partial sums
         if (e >= 0 && !skip) {
             const int mcols = min(BN, M - m0);
             if (PAIRS) {
@@ -307,10 +443,65 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         gt += reduce[(s * BN + c) * band + 2 * i];
                         up += reduce[(s * BN + c) * band + 2 * i + 1];
                     }
-                    gt = ap_to_float(ap_from_float<TO>(gt));
-                    up = ap_to_float(ap_from_float<TO>(up));
+                    gt = ap_to_float(ap_from_float<TO>(gt * inv_s[c]));
+                    up = ap_to_float(ap_from_float<TO>(up * inv_s[c]));
                     const int n = n0 + first + 2 * i;
                     if (n < N) out[(size_t)(m0 + c) * ldc + (n >> 1)] = ap_from_float<TO>(gated(gt, up));
+                }
+            } else if (EPI == EPI_ROPE) {
+                const int prs = rows / 2;
+                for (int idx = e; idx < prs * mcols; idx += 128) {
+                    const int c = idx / prs, i = idx - c * prs;
+                    float a = 0.f, b = 0.f;
+                    for (int s = 0; s < S; ++s) {                                          // slices in order
+                        a += reduce[(s * BN + c) * band + 2 * i];
+                        b += reduce[(s * BN + c) * band + 2 * i + 1];
+                    }
+                    a = ap_to_float(__float2bfloat16_rn(a * inv_s[c]));
+                    b = ap_to_float(__float2bfloat16_rn(b * inv_s[c]));
+                    const int n = n0 + first + 2 * i;
+                    if (n < N) rope_store_pair(ea, m0 + c, n, a, b);
+                }
+            } else if (EPI == EPI_RESIDUAL) {
+                // Thread idx owns (token c, row i) of the band.  The squares of a token's rows are
+                // summed over runs of min(rows, 32) lanes, which hold consecutive rows of one token
+                // (rows is a power of two: 128 over 2, 4 or 8 slices), and every run writes one part.
+                // The residual's old values are fetched sixteen at a time, the first sixteen before
+                // the cluster barrier above (xin_first), so that their latency is not paid here.
+                const int total = rows * mcols;
+                const int width = rows < 32 ? rows : 32;
+                const int groups = rows < 32 ? 1 : rows / 32;
+                for (int base = 0; base < total; base += 128 * 16) {        // the same trips for every lane
+                    float xin[16];
+#pragma unroll
+                    for (int u = 0; u < 16; ++u) {
+                        const int idx = base + u * 128 + e;
+                        const int c = idx / rows, i = idx - c * rows;
+                        xin[u] = base == 0 ? xin_first[u]
+                                           : ((idx < total && n0 + first + i < N)
+                                                  ? reinterpret_cast<float*>(out)[(size_t)(m0 + c) * ldc + n0 + first + i] : 0.f);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 16; ++u) {
+                        if (base + u * 128 >= total) break;                 // uniform
+                        const int idx = base + u * 128 + e;
+                        const bool valid = idx < total;
+                        const int c = valid ? idx / rows : 0, i = valid ? idx - c * rows : 0;
+                        const int n = n0 + first + i;
+                        float xv = 0.f;
+                        if (valid && n < N) {
+                            float sum = 0.f;
+                            for (int s = 0; s < S; ++s) sum += reduce[(s * BN + c) * band + i];   // slices in order
+                            xv = xin[u] + sum;
+                            reinterpret_cast<float*>(out)[(size_t)(m0 + c) * ldc + n] = xv;
+                            ea.xb[(size_t)(m0 + c) * ea.ldxb + n] = __float2bfloat16_rn(xv);
+                        }
+                        float sq = xv * xv;
+                        for (int o = width >> 1; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                        if (valid && (lane & (width - 1)) == 0)
+                            ea.ss_out[(size_t)(m0 + c) * ea.ss_out_parts +
+                                      ((size_t)blockIdx.y * S + blockIdx.z) * groups + (i >> 5)] = sq;
+                    }
                 }
             } else {
                 for (int idx = e; idx < rows * mcols; idx += 128) {
@@ -318,7 +509,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     float sum = 0.f;
                     for (int s = 0; s < S; ++s) sum += reduce[(s * BN + c) * band + i];   // slices in order
                     const int n = n0 + first + i;
-                    if (n < N) out[(size_t)(m0 + c) * ldc + n] = ap_from_float<TO>(sum);
+                    if (n < N) out[(size_t)(m0 + c) * ldc + n] = ap_from_float<TO>(sum * inv_s[c]);
                 }
             }
         }
@@ -337,9 +528,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 // two accumulators (2 * BN tensor-memory columns).  Every activation tile that reaches
 // shared memory now feeds twice the FLOPs, which matters once many rows are in flight and
 // the product is bound by what L2 can deliver to the SMs.  The second weight tile starts
-// `w1_offset` rows after the first: 128 for two adjacent tiles, or the intermediate size
-// when the weight is [W_gate; W_up] stacked; then (SWIGLU) the epilogue writes
-// silu(gate) * up, so the gated activation never makes a round trip through memory.
+// `w1_offset` (128) rows after the first.
 // ---------------------------------------------------------------------------
 template <int BN> struct DualCfg {
     static constexpr int kStages = BN >= 256 ? 3 : 4;
@@ -349,7 +538,7 @@ template <int BN> struct DualCfg {
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 };
 
-template <int BN, typename TO, bool SWIGLU>
+template <int BN, typename TO>
 __global__ void __launch_bounds__(192)
 gemm_tc_dual_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                     TO* __restrict__ out, int M, int N, int K, long long ldc, int w1_offset) {
@@ -367,9 +556,7 @@ gemm_tc_dual_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
 
     if (*(volatile int*)&g_tc_status != 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // SWIGLU: N counts output columns (the intermediate size); tile x covers gate rows
-    // [128x, 128x+128) and the up rows w1_offset further on.  Else tile x covers 256 rows.
-    const int n0 = blockIdx.y * (SWIGLU ? TILE_W : 2 * TILE_W);
+    const int n0 = blockIdx.y * 2 * TILE_W;        // tile y covers 256 weight rows
     const int m0 = blockIdx.x * BN;            // row tiles side by side: they share the weight tiles
     const int nkb = (K + TILE_K - 1) / TILE_K;
 
@@ -464,23 +651,7 @@ gemm_tc_dual_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 tc::tmem_ld_x16(lane_base + (uint32_t)c, v0);
                 tc::tmem_ld_x16(lane_base + (uint32_t)(BN + c), v1);
                 tc::tmem_ld_wait();
-                if (SWIGLU) {
-                    const int n = n0 + row;
-                    if (n < N) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int m = m0 + c + j;
-                            if (m >= M) break;
-                            // the gate and the up value pass through the storage type, as when the
-                            // activation is a kernel of its own
-                            const float g = ap_to_float(ap_from_float<TO>(__uint_as_float(v0[j])));
-                            const float u = ap_to_float(ap_from_float<TO>(__uint_as_float(v1[j])));
-                            // the result is rounded to the storage type: the fast exponential and
-                            // division (a few 32-bit ulps) are far below that rounding
-                            out[(size_t)m * ldc + n] = ap_from_float<TO>(__fdividef(g, 1.0f + __expf(-g)) * u);
-                        }
-                    }
-                } else {
+                {
                     const int na = n0 + row, nb = n0 + w1_offset + row;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -563,11 +734,11 @@ AP_EXPORT int ap_gemm_tc_plan(int M, int N, int K) {
     return (kb_total + per - 1) / per;
 }
 
-template <int BN, typename TO, bool CLUSTER, bool PAIRS = false>
+template <int BN, typename TO, bool CLUSTER, int EPI = EPI_PLAIN>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K,
-                     long long ldc, int nsplit, long long split_stride, cudaStream_t stream) {
+                     long long ldc, int nsplit, long long split_stride, const EpiArgs& ea, cudaStream_t stream) {
     using Cfg = TileCfg<BN, CLUSTER>;
-    auto kern = gemm_tc_kernel<BN, TO, CLUSTER, PAIRS>;
+    auto kern = gemm_tc_kernel<BN, TO, CLUSTER, EPI>;
     constexpr int smem = CLUSTER ? Cfg::kSmemBytesCluster : Cfg::kSmemBytes;
     static bool configured = false;
     if (!configured) {
@@ -599,14 +770,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, in
     }
     cfg.attrs = attr;
     cfg.numAttrs = nattr;
-    // Weight tiles each CTA asks L2 for before it waits for the kernels ahead of it: only
-    // for single-wave grids, and only as much as L2 can hold without pushing out what is
-    // in use (a budget of 32 MiB over the whole grid).
-    const long long ctas = (long long)cfg.gridDim.x * cfg.gridDim.y * cfg.gridDim.z;
-    int l2_tiles = 0;
-    if (ap_pdl_enabled() && ctas <= 2 * 148 && g_l2_prefetch_budget > 0)
-        l2_tiles = (int)(g_l2_prefetch_budget / (ctas * A_TILE_BYTES));
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, ma, (TO*)out, M, N, K, ldc, per, split_stride, l2_tiles);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mw, ma, (TO*)out, M, N, K, ldc, per, split_stride, ea);
     if (e != cudaSuccess) {
         ap_set_error("gemm_tc: launch failed: %s", cudaGetErrorString(e));
         return AP_ERR_LAUNCH;
@@ -616,19 +780,51 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, void* out, in
 
 #define AP_MAX_CLUSTER 8
 
+// Parts of the sums of squares that ap_gemm_tc writes per row with epi == 2 (see there).
+AP_EXPORT int ap_gemm_tc_residual_parts(int N, int nsplit) {
+    const int tiles = (N + TILE_W - 1) / TILE_W;
+    if (nsplit <= 1) return tiles * 4;
+    const int band = (TILE_W + nsplit - 1) / nsplit;
+    return tiles * nsplit * (band < 32 ? 1 : band / 32);
+}
+
+static int gemm_tc_run(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K,
+                       long long lda, long long ldw, long long ldc, int nsplit, long long split_stride,
+                       int reduce, int epi, const float* ss_in, int ss_in_parts, float inv_width, float eps,
+                       void* xb, long long ldxb, float* ss_out, int ss_out_parts, const EpiArgs* rope,
+                       cudaStream_t stream);
+
 // reduce != 0: the K slices add up inside a thread-block cluster and `out` is the finished
-// [M, N] matrix (any output type, nsplit <= 8, M <= 64); else slice z writes 32-bit partial
-// sums at out + z * split_stride.
-// pairs != 0 (bfloat16 out, M <= 64, finished sums only): w's rows alternate gate and up, and
-// out is [M, N/2] = silu(gate) * up.
+// matrix (nsplit <= 8, M <= 256); else slice z writes 32-bit partial sums at out + z * split_stride.
+// epi: what becomes of the finished sums (nsplit == 1, or reduce):
+//   0  out[M, N] = sums, 32-bit or bfloat16;
+//   1  w's rows alternate gate and up, out[M, N/2] = silu(gate) * up (bfloat16, M <= 256);
+//   2  out is the 32-bit residual [M, N] and is added to; xb [M, ldxb] receives its bfloat16
+//      copy and ss_out [M, ap_gemm_tc_residual_parts(N, nsplit)] partial sums of squares of the
+//      updated rows (nsplit 1, 2, 4 or 8; one tile of rows: M <= 256).
+// ss_in (epi 0 and 1; nullptr: none): [M, ss_in_parts] partial sums of squares of the rows of
+// the product's input before they were rounded to `a`; row m of the result is multiplied by
+// 1/sqrt(sum(ss_in[m]) * inv_width + eps).
 AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K,
                          long long lda, long long ldw, long long ldc, int nsplit, long long split_stride,
-                         int reduce, int pairs, cudaStream_t stream) {
+                         int reduce, int epi, const float* ss_in, int ss_in_parts, float inv_width, float eps,
+                         void* xb, long long ldxb, float* ss_out, int ss_out_parts, cudaStream_t stream) {
     AP_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     if (M == 0) return AP_OK;
     AP_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
                "gemm_tc: K=%d and the leading dimensions must be multiples of 8 (16-byte rows for TMA)", K);
     AP_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
+    AP_REQUIRE(epi == EPI_PLAIN || epi == EPI_PAIRS || epi == EPI_RESIDUAL, "gemm_tc: unknown epilogue %d", epi);
+    return gemm_tc_run(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, epi, ss_in,
+                       ss_in_parts, inv_width, eps, xb, ldxb, ss_out, ss_out_parts, nullptr, stream);
+}
+
+static int gemm_tc_run(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K,
+                       long long lda, long long ldw, long long ldc, int nsplit, long long split_stride,
+                       int reduce, int epi, const float* ss_in, int ss_in_parts, float inv_width, float eps,
+                       void* xb, long long ldxb, float* ss_out, int ss_out_parts, const EpiArgs* rope,
+                       cudaStream_t stream) {
+    const bool pairs = epi == EPI_PAIRS;
     AP_REQUIRE(lda >= K && ldw >= K && ldc >= (pairs ? N / 2 : N), "gemm_tc: a leading dimension is below its row length");
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     AP_REQUIRE(nsplit >= 1 && nsplit <= kb_total && nsplit <= 65535, "gemm_tc: cannot split K=%d into %d", K, nsplit);
@@ -645,57 +841,87 @@ AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype,
                "gemm_tc: slices are added in a cluster only for up to %d slices and 256 rows (got %d, %d)",
                AP_MAX_CLUSTER, nsplit, M);
     AP_REQUIRE(cluster || nsplit == 1 || out_dtype == AP_F32, "gemm_tc: partial sums must be 32-bit");
+    AP_REQUIRE(ss_in == nullptr || ((nsplit == 1 || cluster) && ss_in_parts > 0 && inv_width > 0.f && epi != EPI_RESIDUAL),
+               "gemm_tc: the scale of the rows applies to finished sums, and needs its parts and the rows' width");
+    EpiArgs ea = {};
+    if (rope) ea = *rope;
+    ea.ss_in = ss_in; ea.ss_in_parts = ss_in_parts; ea.inv_width = inv_width; ea.eps = eps;
+    if (epi == EPI_RESIDUAL) {
+        AP_REQUIRE(out_dtype == AP_F32 && M <= 256 && (nsplit == 1 || (cluster && (nsplit == 2 || nsplit == 4 || nsplit == 8))),
+                   "gemm_tc: the residual epilogue adds into a 32-bit matrix of at most 256 rows, with 1, 2, 4 or 8 "
+                   "slices of K added in a cluster");
+        AP_REQUIRE(xb && ss_out && ldxb >= N && ss_out_parts == ap_gemm_tc_residual_parts(N, nsplit),
+                   "gemm_tc: the residual epilogue needs the bfloat16 copy and %d parts of sums of squares per row",
+                   ap_gemm_tc_residual_parts(N, nsplit));
+        ea.xb = (bf16*)xb; ea.ldxb = ldxb; ea.ss_out = ss_out; ea.ss_out_parts = ss_out_parts;
+    }
     CUtensorMap mw, ma;
     AP_REQUIRE(make_map(&mw, w, N, K, ldw, TILE_W), "gemm_tc: cannot encode the weight's tensor map");
     AP_REQUIRE(make_map(&ma, a, M, K, lda, bn), "gemm_tc: cannot encode the activations' tensor map");
 #define GO(BN, CL)                                                                                       \
     return out_dtype == AP_F32                                                                           \
-               ? launch_tc<BN, float, CL>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, stream)       \
-               : launch_tc<BN, bf16, CL>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, stream)
-#define GOP(BN, CL) return launch_tc<BN, bf16, CL, true>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, stream)
-    if (pairs && cluster) {
-        switch (bn) {
-            case 16: GOP(16, true);
-            case 32: GOP(32, true);
-            case 64: GOP(64, true);
-            case 128: GOP(128, true);
-            default: GOP(256, true);
-        }
+               ? launch_tc<BN, float, CL>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, ea, stream)   \
+               : launch_tc<BN, bf16, CL>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, ea, stream)
+#define GOE(BN, CL, TT, EP) return launch_tc<BN, TT, CL, EP>(mw, ma, out, M, N, K, ldc, nsplit, split_stride, ea, stream)
+#define BY_BN(MACRO, ...)                      \
+    switch (bn) {                              \
+        case 16: MACRO(16, __VA_ARGS__);       \
+        case 32: MACRO(32, __VA_ARGS__);       \
+        case 64: MACRO(64, __VA_ARGS__);       \
+        case 128: MACRO(128, __VA_ARGS__);     \
+        default: MACRO(256, __VA_ARGS__);      \
     }
-    if (pairs) {
-        switch (bn) {
-            case 16: GOP(16, false);
-            case 32: GOP(32, false);
-            case 64: GOP(64, false);
-            case 128: GOP(128, false);
-            default: GOP(256, false);
-        }
+    if (epi == EPI_PAIRS) {
+        if (cluster) BY_BN(GOE, true, bf16, EPI_PAIRS)
+        BY_BN(GOE, false, bf16, EPI_PAIRS)
     }
-#undef GOP
-    if (cluster) {
-        switch (bn) {
-            case 16: GO(16, true);
-            case 32: GO(32, true);
-            case 64: GO(64, true);
-            case 128: GO(128, true);
-            default: GO(256, true);
-        }
+    if (epi == EPI_RESIDUAL) {
+        if (cluster) BY_BN(GOE, true, float, EPI_RESIDUAL)
+        BY_BN(GOE, false, float, EPI_RESIDUAL)
     }
-    switch (bn) {
-        case 16: GO(16, false);
-        case 32: GO(32, false);
-        case 64: GO(64, false);
-        case 128: GO(128, false);
-        default: GO(256, false);
+    if (epi == EPI_ROPE) {
+        if (cluster) BY_BN(GOE, true, bf16, EPI_ROPE)
+        BY_BN(GOE, false, bf16, EPI_ROPE)
     }
+    if (cluster) BY_BN(GO, true)
+    BY_BN(GO, false)
+#undef BY_BN
+#undef GOE
 #undef GO
 }
 
-template <int BN, typename TO, bool SWIGLU>
+// The stacked Q, K, V projection of an attention layer for at most 256 rows, with the rotation
+// of Q and K and the store of K and V into the cache in its epilogue (EPI_ROPE): w is
+// [(nh + 2 nkv) * hd, K]; q_out [M, nh * hd] bfloat16; cache one layer's pages
+// [page][2][nkv][P][hd] bfloat16 (nullptr: K and V are not stored); cos_sin [M][hd/2] pairs
+// (nullptr: no rotation); pairing 0: the rows of every Q and K head interleaved (2j: element j,
+// 2j + 1: element j + hd/2), 1: neighbouring elements pair.  ss_in as for ap_gemm_tc.
+AP_EXPORT int ap_gemm_tc_rope(const void* a, const void* w, int M, int K, long long lda, long long ldw, int nsplit,
+                              const float* ss_in, int ss_in_parts, float inv_width, float eps, void* q_out,
+                              void* cache, const int* positions, const int* token_seq, const int* block_table,
+                              int max_blocks, const float* cos_sin, int pairing, int nh, int nkv, int hd, int P,
+                              long long page_stride, cudaStream_t stream) {
+    AP_REQUIRE(nh > 0 && nkv >= 0 && hd > 0 && hd % 2 == 0, "gemm_tc_rope: bad heads %d/%d of size %d", nh, nkv, hd);
+    AP_REQUIRE(pairing == 0 || pairing == 1, "gemm_tc_rope: unknown pairing %d", pairing);
+    AP_REQUIRE(q_out && positions, "gemm_tc_rope: the queries' destination and the positions are needed");
+    AP_REQUIRE(cache == nullptr || (token_seq && block_table && max_blocks > 0 && P > 0 &&
+                                    page_stride >= 2LL * nkv * P * hd),
+               "gemm_tc_rope: storing needs the block table, the rows' sequences and whole pages");
+    AP_REQUIRE(M <= 256, "gemm_tc_rope: at most 256 rows (got %d)", M);
+    EpiArgs ea = {};
+    ea.q_out = (bf16*)q_out; ea.cache = (bf16*)cache; ea.positions = positions; ea.token_seq = token_seq;
+    ea.block_table = block_table; ea.cos_sin = (const float2*)cos_sin; ea.page_stride = page_stride;
+    ea.max_blocks = max_blocks; ea.nh = nh; ea.nkv = nkv; ea.hd = hd; ea.P = P; ea.pairing = pairing;
+    const int N = (nh + 2 * nkv) * hd;
+    return gemm_tc_run(a, w, q_out, AP_BF16, M, N, K, lda, ldw, N, nsplit, 0, nsplit > 1 ? 1 : 0, EPI_ROPE, ss_in,
+                       ss_in_parts, inv_width, eps, nullptr, 0, nullptr, 0, &ea, stream);
+}
+
+template <int BN, typename TO>
 static int launch_dual(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K,
-                       long long ldc, int w1_offset, cudaStream_t stream) {
+                       long long ldc, cudaStream_t stream) {
     using Cfg = DualCfg<BN>;
-    auto kern = gemm_tc_dual_kernel<BN, TO, SWIGLU>;
+    auto kern = gemm_tc_dual_kernel<BN, TO>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -703,18 +929,16 @@ static int launch_dual(const CUtensorMap& mw, const CUtensorMap& ma, void* out, 
                    cudaGetErrorString(e));
         configured = true;
     }
-    const int tile_n = SWIGLU ? TILE_W : 2 * TILE_W;
-    dim3 grid((M + BN - 1) / BN, (N + tile_n - 1) / tile_n, 1);
+    dim3 grid((M + BN - 1) / BN, (N + 2 * TILE_W - 1) / (2 * TILE_W), 1);
     AP_CHECK_PDL_LAUNCH("gemm_tc_dual", ap_launch_pdl(kern, grid, dim3(192), (size_t)Cfg::kSmemBytes, stream, mw, ma,
-                                                      (TO*)out, M, N, K, ldc, w1_offset));
+                                                      (TO*)out, M, N, K, ldc, TILE_W));
     return AP_OK;
 }
 
-// Two weight tiles per CTA (see gemm_tc_dual_kernel), for products with more than 64 rows.
-//   swiglu == 0: out[M, N] = a * w^T for w [N, K].
-//   swiglu != 0: w is [2N, K] = [W_gate; W_up]; out[M, N] = silu(a W_gate^T) * (a W_up^T).
+// Two weight tiles per CTA (see gemm_tc_dual_kernel), for products with more than 64 rows:
+// out[M, N] = a * w^T for w [N, K].
 AP_EXPORT int ap_gemm_tc_dual(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K,
-                              long long lda, long long ldw, long long ldc, int swiglu, cudaStream_t stream) {
+                              long long lda, long long ldw, long long ldc, cudaStream_t stream) {
     AP_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     if (M == 0) return AP_OK;
     AP_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
@@ -725,18 +949,13 @@ AP_EXPORT int ap_gemm_tc_dual(const void* a, const void* w, void* out, int out_d
     const int bn = M <= 128 ? 128 : 256;
     AP_REQUIRE((N + TILE_W - 1) / TILE_W <= 65535, "gemm_tc: %d output features exceed the grid", N);
     CUtensorMap mw, ma;
-    AP_REQUIRE(make_map(&mw, w, swiglu ? 2LL * N : N, K, ldw, TILE_W), "gemm_tc: cannot encode the weight's tensor map");
+    AP_REQUIRE(make_map(&mw, w, N, K, ldw, TILE_W), "gemm_tc: cannot encode the weight's tensor map");
     AP_REQUIRE(make_map(&ma, a, M, K, lda, bn), "gemm_tc: cannot encode the activations' tensor map");
-    const int off = swiglu ? N : TILE_W;
-#define GO(BN, SW)                                                                             \
-    return out_dtype == AP_F32 ? launch_dual<BN, float, SW>(mw, ma, out, M, N, K, ldc, off, stream) \
-                               : launch_dual<BN, bf16, SW>(mw, ma, out, M, N, K, ldc, off, stream)
-    if (swiglu) {
-        if (bn == 128) GO(128, true);
-        GO(256, true);
-    }
-    if (bn == 128) GO(128, false);
-    GO(256, false);
+#define GO(BN)                                                                             \
+    return out_dtype == AP_F32 ? launch_dual<BN, float>(mw, ma, out, M, N, K, ldc, stream) \
+                               : launch_dual<BN, bf16>(mw, ma, out, M, N, K, ldc, stream)
+    if (bn == 128) GO(128);
+    GO(256);
 #undef GO
 }
 
@@ -821,9 +1040,6 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 __device__ __forceinline__ void st_release_gpu(int* p, int v) {
     asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// the four epilogue warps among themselves (barrier 1; barrier 0 is __syncthreads)
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
 template <int BN, typename TO, bool PAIRS>
 __global__ void __launch_bounds__(192)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
@@ -1206,12 +1422,6 @@ AP_EXPORT int ap_gemm_tc_status(void) {
     int v = -1;
     if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
     return v;
-}
-
-// Bytes of weight a single-wave product may ask L2 for ahead of its dependency wait (0: none).
-AP_EXPORT int ap_gemm_tc_set_l2_prefetch(long long bytes) {
-    g_l2_prefetch_budget = bytes < 0 ? 0 : bytes;
-    return AP_OK;
 }
 
 // Clear the status word so that products run again after a reported expiry.

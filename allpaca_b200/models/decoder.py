@@ -18,7 +18,7 @@ from typing import Dict, List, Mapping, Optional, Tuple
 import torch
 
 from .. import ops
-from ..parts import (Block, BuildEnv, CacheNeed, LayerCache, ModelSpec, Part, WeightSpec, build)
+from ..parts import (Block, BuildEnv, CacheNeed, Deferred, LayerCache, ModelSpec, Part, WeightSpec, build)
 from ..parts.linear import Linear
 
 
@@ -41,6 +41,7 @@ class DecoderModel:
         self.head_bias: Optional[torch.Tensor] = None
         self._validate_order()
         self.caches: List[LayerCache] = [LayerCache() for _ in spec.order]
+        self._group_pages: List[Tuple[torch.Tensor, int]] = []
 
     def _validate_order(self) -> None:
         for r, run in enumerate(self.spec.order):
@@ -80,6 +81,8 @@ class DecoderModel:
             per_part.setdefault(id(part), (part, {}))[1][local] = tensors[full]
         for part, got in per_part.values():
             part.load(got)
+        for block in self.blocks:
+            block.finalize()
         s = self.spec
         self.embedding = tensors[s.embedding_name].contiguous()
         if s.tie_word_embeddings or s.head_name not in tensors:
@@ -121,6 +124,8 @@ class DecoderModel:
         """``storages[g]`` backs group ``g`` of ``plan``; ``states[r]`` is the state rows of
         run ``r`` or None."""
         where: Dict[int, Tuple[int, int]] = {}
+        # (all pages of a group, index of the page-size dimension), for the clearing of fresh pages
+        self._group_pages = [(storages[g].pages, 2 + len(grp.need.outer)) for g, grp in enumerate(plan)]
         for g, grp in enumerate(plan):
             for i, r in enumerate(grp.runs):
                 where[r] = (g, i)
@@ -140,6 +145,10 @@ class DecoderModel:
         ws = self.env.workspace
         s = self.spec
         step.shared.clear()
+        # pages that get their first token in this step: nothing of their last owner stays readable
+        for g, (pages, page_dim) in enumerate(self._group_pages):
+            ops.clear_page_tails(pages, page_dim, step.positions, step.token_seq, step.block_tables[g],
+                                 step.context_lens)
         x = ws.get("model.residual", (T, s.hidden_size), torch.float32)
         ops.embed_gather(step.token_ids, self.embedding, x,
                          s.embedding_scale if s.embedding_scale is not None else 1.0)
@@ -151,6 +160,8 @@ class DecoderModel:
         if R == 0:
             return logits            # a portion nobody wants logits of: the cache is written, that is all
         h = ws.get("model.final_normed", (R, s.hidden_size), self.env.dtype)
+        if isinstance(delta, Deferred):
+            delta = None                 # the last block has added into the residual itself
         self.final_norm.forward(x, h, delta=delta, rows=step.logit_rows)
         out = self.head.forward(h, "model.logits", "float32")
         if self.head_bias is not None or s.logit_scale is not None or s.logit_softcap:

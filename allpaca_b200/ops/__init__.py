@@ -130,14 +130,8 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
 def rope_kv_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[torch.Tensor],
                   positions: torch.Tensor, token_seq: Optional[torch.Tensor],
                   block_table: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
-                  pairing: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                  context_lens: Optional[torch.Tensor] = None) -> None:
+                  pairing: int, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
     """Rotate Q and K of ``qkv [T, (nh+2nkv)*hd]`` and store K, V into cache pages.
-
-    ``context_lens`` (int32 per sequence: the tokens it holds after this step): a page that
-    gets its first token in this step has the slots behind the sequence's last token cleared,
-    so that a page taken over from another request holds nothing of it that a kernel could
-    read.  The engine always gives it.
 
     ``cache_layer`` is one layer's pages ``[pages, 2, nkv, P, hd]``; a row's page is
     ``block_table[token_seq[t], pos // P]`` and its slot ``pos % P``.  ``cos_sin`` is the
@@ -168,13 +162,33 @@ def rope_kv_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[
         _check(cos_sin, "cos_sin", torch.float32, 3)
         if cos_sin.shape[0] < T or tuple(cos_sin.shape[1:]) != (head_dim // 2, 2):
             raise KernelError("rope_kv_store: cos_sin must be [T, head_dim/2, 2]")
-    if context_lens is not None:
-        _check(context_lens, "context_lens", torch.int32, 1)
     call(core(), "ap_rope_kv_store", ptr, code, S, stride, q_out.data_ptr(), cptr,
          dtype_code(q_out.dtype), positions.data_ptr(), tsptr, btptr, maxb,
          cos_sin.data_ptr() if cos_sin is not None else 0, int(pairing), T, num_heads,
-         num_kv_heads, head_dim, P, page_stride,
-         context_lens.data_ptr() if context_lens is not None and cache_layer is not None else 0, stream_handle())
+         num_kv_heads, head_dim, P, page_stride, stream_handle())
+
+
+def clear_page_tails(pages: torch.Tensor, page_size_dim: int, positions: torch.Tensor, token_seq: torch.Tensor,
+                     block_table: torch.Tensor, context_lens: torch.Tensor) -> None:
+    """For every row of the step that lands in slot 0 of a page: clear, in all runs of the cache
+    group ``pages [runs, num_pages, *outer, P, *inner]`` (``page_size_dim`` is the index of the
+    ``P`` dimension), the slots of that page behind the sequence's last token of this step.  A page
+    taken over from another request then holds nothing of it that a kernel could read."""
+    _check(pages, "pages")
+    for t, n in ((positions, "positions"), (token_seq, "token_seq"), (context_lens, "context_lens")):
+        _check(t, n, torch.int32, 1)
+    _check(block_table, "block_table", torch.int32, 2)
+    if not (2 <= page_size_dim < pages.dim()):
+        raise KernelError("clear_page_tails: pages must be [runs, num_pages, ..., P, ...]")
+    outer = 1
+    for d in pages.shape[2:page_size_dim]:
+        outer *= d
+    inner = 1
+    for d in pages.shape[page_size_dim + 1:]:
+        inner *= d
+    call(core(), "ap_clear_page_tails", pages.data_ptr(), pages.element_size(), pages.stride(0), pages.stride(1),
+         pages.shape[0], outer, pages.shape[page_size_dim], inner, positions.data_ptr(), token_seq.data_ptr(),
+         block_table.data_ptr(), block_table.shape[1], context_lens.data_ptr(), positions.shape[0], stream_handle())
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor) -> None:
@@ -218,15 +232,38 @@ def tensor_core_gemm_available() -> bool:
     return hasattr(core(), "ap_gemm_tc")
 
 
+class RowScale:
+    """Partial sums of squares ``ss [rows, parts]`` (float32) of the rows a product's input was
+    rounded from, with the rows' width and the norm's eps: the product's result row ``m`` is
+    multiplied by ``1/sqrt(sum(ss[m]) / width + eps)``.  With the norm's weight multiplied into
+    the product's weight beforehand, that is the RMSNorm of the input, applied afterwards."""
+
+    __slots__ = ("ss", "parts", "width", "eps")
+
+    def __init__(self, ss: torch.Tensor, parts: int, width: int, eps: float):
+        self.ss, self.parts, self.width, self.eps = ss, int(parts), int(width), float(eps)
+
+
+def _scale_args(scale: Optional[RowScale], M: int):
+    if scale is None:
+        return 0, 0, 0.0, 0.0
+    _check(scale.ss, "scale.ss", torch.float32, 2)
+    if scale.ss.shape[0] < M or scale.ss.shape[1] != scale.parts:
+        raise KernelError(f"gemm_tc: the sums of squares {tuple(scale.ss.shape)} do not cover {M} rows of "
+                          f"{scale.parts} parts")
+    return scale.ss.data_ptr(), scale.parts, 1.0 / scale.width, scale.eps
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1,
-            reduce: bool = False, pairs: bool = False) -> None:
+            reduce: bool = False, pairs: bool = False, scale: Optional[RowScale] = None) -> None:
     """bfloat16 ``a[M,K] @ w[N,K]^T`` on the tcgen05 tensor cores.
 
     ``nsplit`` K slices run as separate CTAs.  With ``reduce`` they add up inside a
-    thread-block cluster (at most 8 slices, at most 64 rows) and ``out`` is the finished
+    thread-block cluster (at most 8 slices, at most 256 rows) and ``out`` is the finished
     ``[M,N]`` in bfloat16 or float32; without it ``out`` is float32 ``[nsplit, M, N]`` partial
-    sums (``[M,N]`` for ``nsplit == 1``).  ``pairs`` (at most 64 rows, finished sums, bfloat16
+    sums (``[M,N]`` for ``nsplit == 1``).  ``pairs`` (at most 256 rows, finished sums, bfloat16
     out): the rows of ``w`` alternate gate and up, and ``out[M,N/2] = silu(gate) * up``.
+    ``scale`` (finished sums only): see :class:`RowScale`.
     """
     _check(a, "a", torch.bfloat16, 2)
     _check(w, "w", torch.bfloat16, 2)
@@ -247,26 +284,89 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1
         if tuple(out.shape) != (nsplit, M, N) or out.dtype != torch.float32:
             raise KernelError("gemm_tc: partial sums must be float32 [nsplit,M,N]")
         stride = M * N
+    ss, parts, inv_width, eps = _scale_args(scale, M)
     call(core(), "ap_gemm_tc", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
          M, N, K, K, K, N // 2 if pairs else N, nsplit, stride, 1 if reduce else 0, 1 if pairs else 0,
-         stream_handle())
+         ss, parts, inv_width, eps, 0, 0, 0, 0, stream_handle())
 
 
-def gemm_tc_dual(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> None:
-    """The tensor-core product with two weight tiles per CTA, for more than 64 rows.
+def gemm_tc_residual_parts(N: int, nsplit: int) -> int:
+    """Parts of sums of squares per row that :func:`gemm_tc_residual` writes."""
+    return int(core().ap_gemm_tc_residual_parts(int(N), int(nsplit)))
 
-    ``swiglu`` False: ``out[M,N] = a[M,K] @ w[N,K]^T``.  True: ``w`` is ``[2N, K]``, gate rows
-    then up rows, and ``out[M,N] = silu(a @ w_gate^T) * (a @ w_up^T)``.
-    """
+
+def gemm_tc_residual(a: torch.Tensor, w: torch.Tensor, x: torch.Tensor, xb: torch.Tensor, ss: torch.Tensor,
+                     nsplit: int = 1) -> int:
+    """``x[M,N] += a[M,K] @ w[N,K]^T`` into the 32-bit residual (at most 256 rows; 1, 2, 4 or 8 K
+    slices added in a cluster), with the updated rows copied to ``xb`` in bfloat16 and partial sums of
+    their squares written to ``ss [M, parts]``; returns ``parts``."""
+    _check(a, "a", torch.bfloat16, 2)
+    _check(w, "w", torch.bfloat16, 2)
+    _check(x, "x", torch.float32, 2)
+    _check(xb, "xb", torch.bfloat16, 2)
+    _check(ss, "ss", torch.float32, 2)
+    M, K = a.shape
+    N = w.shape[0]
+    parts = gemm_tc_residual_parts(N, nsplit)
+    if w.shape[1] != K or tuple(x.shape) != (M, N) or tuple(xb.shape) != (M, N) or ss.shape[0] < M \
+            or ss.shape[1] != parts:
+        raise KernelError(f"gemm_tc_residual: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, x {tuple(x.shape)}, "
+                          f"xb {tuple(xb.shape)}, ss {tuple(ss.shape)} (parts {parts})")
+    call(core(), "ap_gemm_tc", a.data_ptr(), w.data_ptr(), x.data_ptr(), AP_F32, M, N, K, K, K, N, nsplit, 0,
+         1 if nsplit > 1 else 0, 2, 0, 0, 0.0, 0.0, xb.data_ptr(), N, ss.data_ptr(), parts, stream_handle())
+    return parts
+
+
+def gemm_tc_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[torch.Tensor],
+                 positions: torch.Tensor, token_seq: Optional[torch.Tensor], block_table: Optional[torch.Tensor],
+                 cos_sin: Optional[torch.Tensor], pairing: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 nsplit: int = 1, scale: Optional[RowScale] = None) -> None:
+    """The stacked Q, K, V projection of at most 256 rows ``a [M,K]`` with :func:`rope_kv_store` in
+    its epilogue: Q rotated into ``q_out [M, nh*hd]``, K rotated and V into the pages of
+    ``cache_layer`` (None: not stored).  ``pairing`` 0: the rows of every Q and K head of ``w`` are
+    interleaved (row 2j: element j, row 2j+1: element j + hd/2) and the results go back to their
+    places; 1: neighbouring elements pair.  ``scale``: see :class:`RowScale`."""
+    _check(a, "a", torch.bfloat16, 2)
+    _check(w, "w", torch.bfloat16, 2)
+    _check(q_out, "q_out", torch.bfloat16, 2)
+    _check(positions, "positions", torch.int32, 1)
+    M, K = a.shape
+    if w.shape != ((num_heads + 2 * num_kv_heads) * head_dim, K) or q_out.shape[0] < M \
+            or q_out.shape[1] != num_heads * head_dim or positions.shape[0] < M:
+        raise KernelError(f"gemm_tc_rope: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, q_out {tuple(q_out.shape)}")
+    P, page_stride, cptr, tsptr, btptr, maxb = 1, 0, 0, 0, 0, 0
+    if cache_layer is not None:
+        _check(cache_layer, "cache_layer", torch.bfloat16, 5)
+        _, two, nkv, P, hd = cache_layer.shape
+        if two != 2 or nkv != num_kv_heads or hd != head_dim or token_seq is None or block_table is None:
+            raise KernelError("gemm_tc_rope: the cache layer does not match the heads, or its block table is missing")
+        _check(token_seq, "token_seq", torch.int32, 1)
+        _check(block_table, "block_table", torch.int32, 2)
+        page_stride, cptr = cache_layer.stride(0), cache_layer.data_ptr()
+        tsptr, btptr, maxb = token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1]
+    if cos_sin is not None:
+        _check(cos_sin, "cos_sin", torch.float32, 3)
+        if cos_sin.shape[0] < M or tuple(cos_sin.shape[1:]) != (head_dim // 2, 2):
+            raise KernelError("gemm_tc_rope: cos_sin must be [M, head_dim/2, 2]")
+    ss, parts, inv_width, eps = _scale_args(scale, M)
+    call(core(), "ap_gemm_tc_rope", a.data_ptr(), w.data_ptr(), M, K, K, K, nsplit, ss, parts, inv_width, eps,
+         q_out.data_ptr(), cptr, positions.data_ptr(), tsptr, btptr, maxb,
+         cos_sin.data_ptr() if cos_sin is not None else 0, int(pairing), num_heads, num_kv_heads, head_dim, P,
+         page_stride, stream_handle())
+
+
+def gemm_tc_dual(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """The tensor-core product with two weight tiles per CTA, for more than 64 rows:
+    ``out[M,N] = a[M,K] @ w[N,K]^T``."""
     _check(a, "a", torch.bfloat16, 2)
     _check(w, "w", torch.bfloat16, 2)
     _check(out, "out", dims=2)
     M, K = a.shape
-    N = w.shape[0] // 2 if swiglu else w.shape[0]
-    if w.shape[1] != K or tuple(out.shape) != (M, N) or (swiglu and w.shape[0] % 2):
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
         raise KernelError(f"gemm_tc_dual: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     call(core(), "ap_gemm_tc_dual", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
-         M, N, K, K, K, N, 1 if swiglu else 0, stream_handle())
+         M, N, K, K, K, N, stream_handle())
 
 
 _persistent_scratch = {}

@@ -27,7 +27,8 @@ _CORE_SIGNATURES = {
     "ap_logit_transform": [_P, _P, _I, _I, _I, _F, _F, _P],
     "ap_add_rmsnorm": [_P, _P, _I, _L, _P, _I, _F, _P, _I, _P, _I, _I, _P],
     "ap_residual_add": [_P, _P, _I, _L, _L, _P],
-    "ap_rope_kv_store": [_P, _I, _I, _L, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _L, _P, _P],
+    "ap_rope_kv_store": [_P, _I, _I, _L, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _L, _P],
+    "ap_clear_page_tails": [_P, _I, _L, _L, _I, _I, _I, _I, _P, _P, _P, _I, _P, _I, _P],
     "ap_rope_table": [_P, _P, _P, _I, _I, _P],
     "ap_swiglu": [_P, _I, _I, _L, _P, _I, _I, _I, _I, _P],
     "ap_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _L, _L, _L, _P],
@@ -35,14 +36,19 @@ _CORE_SIGNATURES = {
     "ap_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
 }
 _OPTIONAL_CORE_SIGNATURES = {
-    # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, pairs, stream)
-    "ap_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _L, _I, _I, _P],
-    "ap_gemm_tc_dual": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P],
+    # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, epi,
+    #                ss_in, ss_in_parts, inv_width, eps, xb, ldxb, ss_out, ss_out_parts, stream)
+    "ap_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _L, _I, _I, _P, _I, _F, _F, _P, _L, _P, _I, _P],
+    "ap_gemm_tc_residual_parts": [_I, _I],
+    # int ap_gemm_tc_rope(a, w, M, K, lda, ldw, nsplit, ss_in, ss_in_parts, inv_width, eps, q_out, cache, positions,
+    #                     token_seq, block_table, max_blocks, cos_sin, pairing, nh, nkv, hd, P, page_stride, stream)
+    "ap_gemm_tc_rope": [_P, _P, _I, _I, _L, _L, _I, _P, _I, _F, _F, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I,
+                        _L, _P],
+    "ap_gemm_tc_dual": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "ap_gemm_tc_persistent": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P, _L, _P],
     "ap_gemm_tc_plan": [_I, _I, _I],
     "ap_gemm_tc_prefers_dual": [_I, _I, _I],
     "ap_gemm_tc_prefers_persistent": [_I, _I, _I],
-    "ap_gemm_tc_set_l2_prefetch": [_L],
     "ap_gemm_tc_status": [],
     "ap_gemm_tc_reset_status": [],
 }

@@ -173,6 +173,17 @@ class LayerCache:
     state: Optional[torch.Tensor] = None
 
 
+@dataclass
+class Deferred:
+    """What a block that fuses its norms into the neighbouring products hands on instead of a
+    32-bit delta: the residual is already updated; ``xb`` is its bfloat16 copy and ``ss [T, parts]``
+    the partial sums of squares of its rows, from which the next product scales its result."""
+
+    xb: torch.Tensor
+    ss: torch.Tensor
+    parts: int
+
+
 class Part:
     """Common face of every part."""
 
@@ -274,6 +285,10 @@ class Block(Part):
 
     def forward(self, x, delta, step, cache: LayerCache):
         raise NotImplementedError
+
+    def finalize(self) -> None:
+        """Called once every part of the block has its weights: the place to precompute what
+        spans parts (a norm's weight multiplied into the product that follows it)."""
 
 
 # ---------------------------------------------------------------------------

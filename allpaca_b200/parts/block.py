@@ -11,7 +11,9 @@ from typing import Dict
 
 import torch
 
-from .base import Block, BuildEnv, LayerCache, Part, build, register
+from .. import ops
+from .base import Block, BuildEnv, Deferred, LayerCache, Part, build, register
+from .norm import RMSNorm
 
 
 @register("block", "prenorm")
@@ -35,12 +37,47 @@ class PreNormBlock(Block):
             params.get("feed_forward_norm_prefix", "feed_forward_norm."): self.feed_forward_norm,
         }
 
+        self.fused = False
+
     def sub_parts(self) -> Dict[str, Part]:
         return dict(self._prefixes)
+
+    def finalize(self) -> None:
+        """In bfloat16, where both norms are RMSNorm and mixer and feed-forward can take it: the
+        norms' weights are multiplied into the products that follow them.  A step of few rows then
+        runs without norm kernels (the products scale their result rows by the root mean square,
+        which the product before them summed up while it added into the residual); a step of many
+        rows runs the norm kernels as before, without their weights."""
+        if self.env.dtype != torch.bfloat16:
+            return
+        if not (type(self.mixer_norm) is RMSNorm and type(self.feed_forward_norm) is RMSNorm):
+            return
+        if self.mixer_norm.folded or self.feed_forward_norm.folded:
+            return                      # done before (weights are folded once per load)
+        self.fused = False
+        can = [getattr(part, "can_fold_input_norm", lambda: False)() for part in (self.mixer, self.feed_forward)]
+        if not all(can):
+            return
+        self.mixer.fold_input_norm(self.mixer_norm.weight)
+        self.feed_forward.fold_input_norm(self.feed_forward_norm.weight)
+        self.mixer_norm.fold()
+        self.feed_forward_norm.fold()
+        self.fused = True
 
     def forward(self, x: torch.Tensor, delta, step, cache: LayerCache):
         T = x.shape[0]
         h = self.env.workspace.get("block.normed", (T, self.hidden), self.env.dtype)
+        if self.fused and self.mixer.fused_rows_ok(T) and self.feed_forward.fused_rows_ok(T):
+            if isinstance(delta, Deferred):
+                inp, scale = delta.xb, ops.RowScale(delta.ss, delta.parts, self.hidden, self.mixer_norm.eps)
+            else:
+                self.mixer_norm.forward(x, h, delta=delta)
+                inp, scale = h, None
+            d = self.mixer.forward_fused(inp, scale, x, step, cache)
+            scale = ops.RowScale(d.ss, d.parts, self.hidden, self.feed_forward_norm.eps)
+            return self.feed_forward.forward_fused(d.xb, scale, x, step)
+        if isinstance(delta, Deferred):
+            delta = None                 # the block before has added into the residual itself
         self.mixer_norm.forward(x, h, delta=delta)
         delta = self.mixer.forward(h, step, cache)
         self.feed_forward_norm.forward(x, h, delta=delta)

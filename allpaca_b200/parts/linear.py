@@ -17,7 +17,7 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import BuildEnv
+from .base import BuildEnv, Deferred
 
 
 class Linear:
@@ -43,13 +43,47 @@ class Linear:
         return (self.weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
                 and ops.tensor_core_gemm_available())
 
-    def forward(self, a: torch.Tensor, buffer_name: str, kind: str) -> torch.Tensor:
+    # Rows up to which the products of a step take the norm before them as a scale of their result
+    # and add into the residual themselves.  Measured on the 8B shape (decode, 4096 keys): a gain of
+    # 2 to 5 % of the step up to 16 rows; from 32 rows on the separate norm kernels are faster (a
+    # product then has to sum up 128 and more partial sums of squares for each of its many rows).
+    FUSED_MAX_ROWS = 16
+
+    def fold_input_scale(self, scale: torch.Tensor) -> None:
+        """Multiply ``scale [in]`` (the weight of the norm that produces this product's input) into
+        the weight's columns; the sum is formed in 32-bit and rounded once."""
+        self.weight = (self.weight.float() * scale.float()[None, :]).to(self.weight.dtype).contiguous()
+
+    def fusable(self) -> bool:
+        return self.weight is not None and self.uses_tensor_cores() and self.bias is None
+
+    def residual_rows_ok(self, T: int) -> bool:
+        """Whether :meth:`forward_residual` takes ``T`` rows (the K slices of the plan must form a
+        cluster of 2, 4 or 8, or be one)."""
+        return (self.fusable() and T <= self.FUSED_MAX_ROWS
+                and ops.gemm_tc_splits(T, self.out_features, self.in_features) in (1, 2, 4, 8))
+
+    def forward_residual(self, a: torch.Tensor, x: torch.Tensor, buffer_name: str) -> Deferred:
+        """``x += a W^T`` in the product's epilogue; returns the updated residual's bfloat16 copy and
+        the partial sums of squares of its rows."""
+        T, N = a.shape[0], self.out_features
+        ws = self.env.workspace
+        nsplit = ops.gemm_tc_splits(T, N, self.in_features)
+        parts = ops.gemm_tc_residual_parts(N, nsplit)
+        xb = ws.get(buffer_name + ".xb", (T, N), torch.bfloat16)
+        ss = ws.get(buffer_name + ".ss", (T, parts), torch.float32)
+        ops.gemm_tc_residual(a, self.weight, x, xb, ss, nsplit)
+        return Deferred(xb, ss, parts)
+
+    def forward(self, a: torch.Tensor, buffer_name: str, kind: str, scale=None) -> torch.Tensor:
         """``a [T, in]`` times the weight.
 
         ``kind`` says what the consumer takes:
         ``"delta"``   32-bit ``[1, T, out]`` for the residual (consumers take ``[S, T, out]``);
         ``"either"``  ``[T, out]`` in the activation type;
         ``"float32"`` 32-bit ``[T, out]`` (logits).
+        ``scale`` (:class:`ops.RowScale`, at most ``FUSED_MAX_ROWS`` rows on the tensor cores): the
+        result's rows are scaled in the epilogue.
         """
         T = a.shape[0]
         N = self.out_features
@@ -72,14 +106,17 @@ class Linear:
         elif tc and nsplit == 1 and ops.gemm_tc_prefers_dual(T, N, self.in_features):
             ops.gemm_tc_dual(a, self.weight, target)
         elif tc:
-            ops.gemm_tc(a, self.weight, target, nsplit, reduce=nsplit > 1)
+            ops.gemm_tc(a, self.weight, target, nsplit, reduce=nsplit > 1, scale=scale)
+            scale = None
         else:
             ops.gemm_simt(a, self.weight, target)
+        if scale is not None:
+            raise ValueError("a scale of the rows is only applied by the tensor-core kernel for few rows")
         if self.bias is not None:
             ops.bias_add(target, self.bias)
         return out
 
-    def forward_gated(self, a: torch.Tensor, buffer_name: str) -> Optional[torch.Tensor]:
+    def forward_gated(self, a: torch.Tensor, buffer_name: str, scale=None) -> Optional[torch.Tensor]:
         """For a weight whose rows alternate gate and up: ``silu(a W_gate^T) * (a W_up^T)`` in one
         kernel, ``[T, out/2]`` in the activation type; None when the shape is not one the fused
         kernel is used for (the caller then multiplies and activates separately)."""
@@ -89,7 +126,9 @@ class Linear:
         out = self.env.workspace.get(buffer_name, (T, self.out_features // 2), self.env.dtype)
         nsplit = ops.gemm_tc_splits(T, self.out_features, self.in_features)
         if T > 64 and nsplit == 1:
+            if scale is not None:
+                raise ValueError("a scale of the rows is only applied by the tensor-core kernel for few rows")
             ops.gemm_tc_persistent(a, self.weight, out, pairs=True)
         else:
-            ops.gemm_tc(a, self.weight, out, nsplit, reduce=nsplit > 1, pairs=True)
+            ops.gemm_tc(a, self.weight, out, nsplit, reduce=nsplit > 1, pairs=True, scale=scale)
         return out

@@ -49,6 +49,22 @@ class SwiGLU(FeedForward):
         self.gate_up.load(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden), gu_bias)
         self.down.load(tensors["down_proj.weight"], tensors["down_proj.bias"] if self.bias else None)
 
+    def can_fold_input_norm(self) -> bool:
+        return self.gate_up.fusable() and self.down.fusable()
+
+    def fold_input_norm(self, weight: torch.Tensor) -> None:
+        """Multiply the weight of the norm before this feed-forward into its first product."""
+        self.gate_up.fold_input_scale(weight)
+
+    def fused_rows_ok(self, T: int) -> bool:
+        return T <= Linear.FUSED_MAX_ROWS and self.down.residual_rows_ok(T)
+
+    def forward_fused(self, h: torch.Tensor, scale, x: torch.Tensor, step):
+        """For few rows: ``h`` with ``scale`` (an ``ops.RowScale``) stands for the normed input;
+        the down projection adds into ``x`` itself.  Returns a :class:`Deferred`."""
+        act = self.gate_up.forward_gated(h, "ffn.act", scale=scale)
+        return self.down.forward_residual(act, x, "ffn")
+
     def forward(self, h: torch.Tensor, step) -> torch.Tensor:
         T = h.shape[0]
         act = self.gate_up.forward_gated(h, "ffn.act")        # one kernel when there are many rows

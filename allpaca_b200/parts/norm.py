@@ -24,12 +24,23 @@ class RMSNorm(Norm):
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.weight = None
+        self._kernel_weight = None
 
     def weights(self) -> Dict[str, WeightSpec]:
         return {"weight": WeightSpec((self.size,), "norm")}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"].contiguous()
+        self._kernel_weight = self.weight
+
+    def fold(self) -> None:
+        """The weight has been multiplied into the product that consumes this norm's output:
+        from now on the kernel only divides by the root mean square."""
+        self._kernel_weight = torch.ones_like(self.weight)
+
+    @property
+    def folded(self) -> bool:
+        return self._kernel_weight is not self.weight
 
     def forward(self, x, out, delta=None, rows=None) -> None:
-        ops.add_rmsnorm(x, self.weight, self.eps, out, delta=delta, rows=rows)
+        ops.add_rmsnorm(x, self._kernel_weight, self.eps, out, delta=delta, rows=rows)
