@@ -55,12 +55,18 @@ def bench_gemm(args) -> dict:
     S = args.splits or ops.gemm_tc_splits(M, N, K)
     odt = torch.float32 if args.out == "float32" else torch.bfloat16
     kernel = "gemm_tc"
-    if M > 64 and not args.dual and not args.single and (S == 1 or args.whole_tiles):
+    if M > 64 and not args.dual and not args.pair and not args.single and (S == 1 or args.whole_tiles):
         # the persistent kernel; with --swiglu the rows of w alternate gate and up
         kernel = "gemm_tc_persistent"
         out = torch.empty(M, N // 2 if args.swiglu else N, device="cuda", dtype=odt)
         fn = lambda i: ops.gemm_tc_persistent(a, ws[i % copies], out, pairs=args.swiglu,   # noqa: E731
                                               share_tiles=not args.whole_tiles)
+        S = 1
+    elif args.pair:
+        # a pair of CTAs to a tile of 256 weight rows (cta_group::2); with --swiglu the rows of w alternate
+        kernel = "gemm_tc_pair"
+        out = torch.empty(M, N // 2 if args.swiglu else N, device="cuda", dtype=odt)
+        fn = lambda i: ops.gemm_tc_pair(a, ws[i % copies], out, pairs=args.swiglu)   # noqa: E731
         S = 1
     elif args.dual:
         # two weight tiles per CTA
@@ -308,6 +314,7 @@ def main(argv=None) -> int:
             s.add_argument("--partials", action="store_true", help="write partial sums instead of adding in a cluster")
             s.add_argument("--out", choices=["float32", "bfloat16"], default="bfloat16")
             s.add_argument("--dual", action="store_true", help="more than 64 rows: two weight tiles per CTA")
+            s.add_argument("--pair", action="store_true", help="more than 64 rows: a pair of CTAs to a tile (cta_group::2)")
             s.add_argument("--single", action="store_true", help="more than 64 rows: one tile per CTA, not persistent")
             s.add_argument("--whole-tiles", action="store_true",
                            help="persistent kernel: never share a tile's K among several CTAs")

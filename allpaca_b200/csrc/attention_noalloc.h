@@ -11,7 +11,9 @@
 // What the caller must know:
 //  * Inputs and outputs are still the caller's: q, out, the cache pages and the tables.
 //  * The scratch is AP_ATTENTION_STATIC_SCRATCH_FLOATS floats (8 MiB) of device memory that
-//    every GPU loading this library holds until the process exits.
+//    every GPU loading this library holds until the process exits.  The attention library is
+//    built once per head size: a process that loads the libraries of several head sizes
+//    holds one such array for each of them.
 //  * A call needs nsplit * T * num_heads * (head_dim + 2) floats of it when nsplit > 1 and
 //    none when nsplit == 1; a call that needs more is refused with AP_ERR_INVALID and a
 //    message from ap_last_error(), and nothing is launched.

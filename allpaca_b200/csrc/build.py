@@ -37,7 +37,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
                 "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 
-CORE_SOURCES = ["errors.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu",
+CORE_SOURCES = ["errors.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_pair.cu",
                 "sampling.cu"]
 ATTN_SOURCES = ["errors.cu", "attention.cu", "attention_tc.cu", "attention_tcgen05.cu",
                 "attention_tcgen05_wide.cu"]

@@ -47,6 +47,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     }
     return true;
 }
+// The same wait for a barrier that another CTA of the cluster arrives on (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, long long limit_cycles = 400000000LL) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if (((++spins) & 0x3ffu) == 0 && clock64() - t0 > limit_cycles) return false;
+    }
+    return true;
+}
+// One arrival on a barrier in another CTA of the cluster (`cluster_addr` from map_to_rank).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -163,6 +188,29 @@ __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint6
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
                  : "memory");
+}
+
+// ---- a pair of CTAs on one tile (cta_group::2) -------------------------------------------
+// One thread of the pair's first CTA issues the instruction for both: each CTA's tensor cores
+// multiply its own 128 rows of A (from its own shared memory, at the descriptor's offset) with
+// all N rows of B, half of which lie in each CTA's shared memory, into its own tensor memory
+// at `d_tmem`.  M in the instruction descriptor is 256.
+__device__ __forceinline__ void mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The barrier at this offset gets one arrival in BOTH CTAs of the pair when every MMA issued so
+// far by this thread has finished.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(smem_addr(bar)), "h"((uint16_t)3)
+        : "memory");
 }
 
 // ---- tensor memory -> registers ----------------------------------------------------

@@ -369,6 +369,25 @@ def gemm_tc_dual(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
          M, N, K, K, K, N, stream_handle())
 
 
+def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pairs: bool = False) -> None:
+    """The tensor-core product on pairs of SMs (``tcgen05.mma.cta_group::2``), for many rows: two
+    CTAs share a tile of 256 weight rows x up to 256 rows of ``a``, each loading half of either.
+
+    ``pairs`` False: ``out[M,N] = a[M,K] @ w[N,K]^T``.  True: the rows of ``w [N,K]`` alternate
+    gate, up, gate, up ... and ``out[M,N/2] = silu(gate) * up``.
+    """
+    _check(a, "a", torch.bfloat16, 2)
+    _check(w, "w", torch.bfloat16, 2)
+    _check(out, "out", dims=2)
+    M, K = a.shape
+    N = w.shape[0]
+    n_out = N // 2 if pairs else N
+    if w.shape[1] != K or tuple(out.shape) != (M, n_out) or (pairs and N % 2):
+        raise KernelError(f"gemm_tc_pair: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    call(core(), "ap_gemm_tc_pair", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+         M, N, K, K, K, n_out, 1 if pairs else 0, stream_handle())
+
+
 _persistent_scratch = {}
 
 
@@ -648,6 +667,11 @@ def check_kernel_status() -> None:
         if hasattr(lib, "ap_attention_decode_tma_status") and int(lib.ap_attention_decode_tma_status()) != 0:
             raise KernelError(f"the TMA-fed decode attention kernel (head size {hd}) gave up waiting on its "
                               f"pipeline; its results are void")
+    lib = core()
+    if hasattr(lib, "ap_gemm_tc_pair_status") and int(lib.ap_gemm_tc_pair_status()) != 0:
+        raise KernelError(f"the tensor-core matrix product on pairs of SMs gave up waiting (code "
+                          f"{int(lib.ap_gemm_tc_pair_status())}: 1 free stage, 2 operands, 3 accumulator, 4 the two "
+                          f"CTAs' tensor memory differs); its results are void")
     code = gemm_tc_status()
     if code != 0:
         raise KernelError(f"the tensor-core matrix product gave up waiting (code {code}: "
