@@ -74,6 +74,14 @@ def bench_gemm(args) -> dict:
         out = torch.empty(M, N, device="cuda", dtype=odt)
         fn = lambda i: ops.gemm_tc_dual(a, ws[i % copies], out)   # noqa: E731
         S = 1
+    elif args.residual:
+        # few rows: the product adds into the 32-bit residual, writes its bfloat16 copy and the
+        # partial sums of squares of its rows (the epilogue of the O and down products of a decode step)
+        kernel = "gemm_tc (residual epilogue)"
+        out = torch.randn(M, N, device="cuda", dtype=torch.float32)
+        xb = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ss = torch.empty(M, ops.gemm_tc_residual_parts(N, S), device="cuda", dtype=torch.float32)
+        fn = lambda i: ops.gemm_tc_residual(a, ws[i % copies], out, xb, ss, S)     # noqa: E731
     elif args.swiglu:
         # up to 256 rows: the gated activation in the epilogue of the (cluster) kernel
         out = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
@@ -319,6 +327,8 @@ def main(argv=None) -> int:
             s.add_argument("--whole-tiles", action="store_true",
                            help="persistent kernel: never share a tile's K among several CTAs")
             s.add_argument("--swiglu", action="store_true", help="w holds gate and up rows: fused gated activation")
+            s.add_argument("--residual", action="store_true",
+                           help="few rows: add into a 32-bit residual in the epilogue (with its bfloat16 copy and sums of squares)")
         else:
             s.add_argument("--heads", type=int, default=32)
             s.add_argument("--kv-heads", type=int, default=8)

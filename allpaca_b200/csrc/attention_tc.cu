@@ -994,6 +994,22 @@ AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cach
     return AP_OK;
 }
 
+// CTAs of the TMA-fed decode kernel that the GPU holds at once (for planning the key slices)
+AP_EXPORT int ap_attention_decode_tma_slots(void) {
+    static int slots = 0;
+    if (slots == 0) {
+        int dev = 0, sms = 0, per_sm = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            configure_smem((const void*)attention_split_tma_kernel<true>, DtSmem::kTotal) != AP_OK ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_split_tma_kernel<true>, DT_THREADS,
+                                                          DtSmem::kTotal) != cudaSuccess || per_sm <= 0)
+            return 296;
+        slots = sms * per_sm;
+    }
+    return slots;
+}
+
 AP_EXPORT int ap_attention_decode_tma_status(void) {
     int v = -1;
     if (cudaMemcpyFromSymbol(&v, g_dt_status, sizeof(int)) != cudaSuccess) return -1;
@@ -1002,6 +1018,7 @@ AP_EXPORT int ap_attention_decode_tma_status(void) {
 #else
 AP_EXPORT int ap_attention_decode_tma_supports(int, int, int, int) { return 0; }
 AP_EXPORT int ap_attention_decode_tma_in_cluster(int, int, int) { return 0; }
+AP_EXPORT int ap_attention_decode_tma_slots(void) { return 0; }
 #endif
 
 // ---------------------------------------------------------------------------

@@ -439,8 +439,11 @@ def _decode_attention(lib, q, out, cache_layer, block_table, positions, rows, nu
     if tma:
         # 16 slices (a cluster size the kernel has to opt into) where the exchange buffer holds them
         sizes = (2, 4, 8, 16) if lib.ap_attention_decode_tma_in_cluster(num_heads, num_kv_heads, 16) else (2, 4, 8)
-    nsplit = decode_splits(rows, num_heads, num_kv_heads, max_context, window, slots=296 if tma else 444,
-                           cluster_sizes=sizes)
+    # CTAs the GPU holds at once: of the TMA-fed kernel two per SM at head size 128, four at 64
+    slots = 444
+    if tma:
+        slots = int(lib.ap_attention_decode_tma_slots()) if hasattr(lib, "ap_attention_decode_tma_slots") else 296
+    nsplit = decode_splits(rows, num_heads, num_kv_heads, max_context, window, slots=slots, cluster_sizes=sizes)
     po = pm = 0
     needs_scratch = nsplit > 1 and not (tma and lib.ap_attention_decode_tma_in_cluster(num_heads, num_kv_heads, nsplit))
     if needs_scratch:

@@ -138,6 +138,7 @@ _OPTIONAL_ATTN_SIGNATURES: Dict[str, list] = {
     "ap_attention_decode_tma_supports": [_I, _I, _I, _I],
     "ap_attention_decode_tma_in_cluster": [_I, _I, _I],
     "ap_attention_decode_tma_status": [],
+    "ap_attention_decode_tma_slots": [],
 }
 
 

@@ -229,6 +229,7 @@ def test_prenorm_block(dtype):
                 t = 1 + t
             w[prefix + name] = t.to(dtype)
         part.load({name: w[prefix + name].to(DEV) for name in part.weights()})
+    block.finalize()            # bfloat16: the norms' weights go into the products that follow them
     h = Harness(env, block.mixer.cache_need())
     x0 = torch.randn(41, hidden, generator=g)
     x = x0.to(DEV).clone()
@@ -238,7 +239,10 @@ def test_prenorm_block(dtype):
         step = h.step([("s", n)])
         xs = x[at:at + n].clone()
         d = block.forward(xs, pending[:, at:at + n].to(DEV).contiguous(), step, h.cache)
-        outs.append((xs + d.sum(0)).cpu())
+        # what comes back is a 32-bit delta still to be added, or nothing of the kind where the
+        # block's last product has added into the residual itself (None, or the Deferred hand-over
+        # of steps of few rows)
+        outs.append((xs + d.sum(0) if isinstance(d, torch.Tensor) else xs).cpu())
         at += n
     # the plain block
     wf = {"p." + n: t.float() for n, t in w.items()}
