@@ -74,7 +74,7 @@ def host_library() -> ctypes.CDLL:
         lib.apc_cache_destroy.restype = None
         lib.apc_prepare_step.argtypes = [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
-                                         c_void_p]
+                                         c_void_p, c_void_p]
         lib.apc_prepare_step.restype = c_int
         lib.aps_create.argtypes = [c_void_p, c_int, c_int64, c_int64, c_int64]
         lib.aps_create.restype = c_void_p
@@ -180,8 +180,6 @@ class CacheManager:
     def __init__(self, groups: Sequence[GroupLayout], max_seqs: int):
         if max_seqs <= 0:
             raise CacheError("max_seqs must be positive")
-        if len(groups) > 8:
-            raise CacheError("at most 8 cache groups are supported")
         for g in groups:
             if g.page_size <= 0:
                 raise CacheError("page_size must be positive")

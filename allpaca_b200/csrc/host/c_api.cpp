@@ -31,7 +31,7 @@ APC_EXPORT int apc_pool_held(void* p, int page) { return ((PagePool*)p)->held(pa
 // ---- cache manager -----------------------------------------------------------------------
 APC_EXPORT void* apc_cache_create(int ngroups, const int* page_size, const int* num_pages, const int* window,
                                   int max_seqs) {
-    if (ngroups < 0 || ngroups > 8 || max_seqs <= 0) return nullptr;
+    if (ngroups < 0 || max_seqs <= 0) return nullptr;
     std::vector<GroupLayout> groups;
     for (int g = 0; g < ngroups; ++g) {
         if (page_size[g] <= 0 || num_pages[g] <= 0) return nullptr;
@@ -82,30 +82,29 @@ APC_EXPORT int apc_cache_table(void* c, int64_t req, int g, int* out, int cap) {
 }
 
 // ---- one step's batch ----------------------------------------------------------------------
-// layout_out: 5 int32 (T, nseq, R, max query, max context) then 8 + 8 int64 (total, 7 offsets,
-// 8 table offsets) then 8 int32 widths, as the struct below.
+// layout: as the struct below; the block tables of the groups follow one another from off_tables,
+// [nseq, widths[g]] each.  widths: [groups] output.
 struct ApcStepLayout {
     int32_t num_tokens, num_seqs, num_logit_rows, max_query_len, max_context_len, pad;
     int64_t total, off_tokens, off_positions, off_seq, off_start, off_context, off_slot, off_rows;
-    int64_t off_table[8];
-    int32_t width[8];
+    int64_t off_tables;
 };
 APC_EXPORT int apc_prepare_step(void* c, int vocab, int64_t max_model_len, int64_t max_batched_tokens, int nseq,
                                 const int64_t* reqs, const int32_t* tok_off, const int32_t* tokens,
                                 const int32_t* want_off, const int32_t* want, const int32_t* fixed_widths,
-                                int32_t* buf, int64_t cap, ApcStepLayout* layout, int64_t* first_position,
-                                int32_t* state_slot) {
+                                int32_t* buf, int64_t cap, ApcStepLayout* layout, int32_t* widths,
+                                int64_t* first_position, int32_t* state_slot) {
     StepLimits lim{vocab, max_model_len, max_batched_tokens};
     StepLayout L;
     const int rc = prepare_step(*(CacheManager*)c, lim, nseq, reqs, tok_off, tokens, want_off, want, fixed_widths,
-                                buf, cap, &L, first_position, state_slot, &g_error);
+                                buf, cap, &L, widths, first_position, state_slot, &g_error);
     if (rc != kOk) return rc;
     layout->num_tokens = L.num_tokens; layout->num_seqs = L.num_seqs; layout->num_logit_rows = L.num_logit_rows;
     layout->max_query_len = L.max_query_len; layout->max_context_len = L.max_context_len; layout->pad = 0;
     layout->total = L.total; layout->off_tokens = L.off_tokens; layout->off_positions = L.off_positions;
     layout->off_seq = L.off_seq; layout->off_start = L.off_start; layout->off_context = L.off_context;
     layout->off_slot = L.off_slot; layout->off_rows = L.off_rows;
-    for (int g = 0; g < 8; ++g) { layout->off_table[g] = L.off_table[g]; layout->width[g] = L.width[g]; }
+    layout->off_tables = L.off_tables;
     return kOk;
 }
 

@@ -1,6 +1,7 @@
 #include "scheduler.hpp"
 
 #include <algorithm>
+#include <vector>
 
 namespace allpaca {
 
@@ -76,8 +77,8 @@ bool Scheduler::fits(const SchedRequest& r, int64_t count) const {
 }
 
 void Scheduler::reserve(const SchedRequest& r, int64_t count) {
-    int missing[8] = {0};
-    cache_->pages_missing(key(r), count, missing);
+    std::vector<int> missing(cache_->num_groups(), 0);
+    cache_->pages_missing(key(r), count, missing.data());
     for (int g = 0; g < cache_->num_groups(); ++g) reserved_[g] += missing[g];
 }
 

@@ -21,17 +21,17 @@
 namespace allpaca {
 
 // fixed_widths: block-table widths to use (graph replay keeps them constant) or nullptr for the
-// narrowest that fits.  first_position / state_slot: [nseq] outputs.
+// narrowest that fits.  widths: [groups] output, the width used for each group's table.
+// first_position / state_slot: [nseq] outputs.
 int prepare_step(CacheManager& cache, const StepLimits& lim, int nseq, const int64_t* reqs,
                  const int32_t* tok_off, const int32_t* tokens, const int32_t* want_off, const int32_t* want,
-                 const int32_t* fixed_widths, int32_t* buf, int64_t cap, StepLayout* out,
+                 const int32_t* fixed_widths, int32_t* buf, int64_t cap, StepLayout* out, int32_t* widths,
                  int64_t* first_position, int32_t* state_slot, std::string* error) {
     auto fail = [&](int status, const std::string& what) {
         *error = what;
         return status;
     };
     if (nseq <= 0) return fail(kMisuse, "a step needs at least one entry");
-    if (cache.num_groups() > 8) return fail(kMisuse, "more than 8 cache groups");
     const int G = cache.num_groups();
     std::unordered_set<int64_t> seen;
     int64_t T = 0, R = 0;
@@ -86,6 +86,8 @@ int prepare_step(CacheManager& cache, const StepLimits& lim, int nseq, const int
     L.num_tokens = (int32_t)T;
     L.num_seqs = nseq;
     L.num_logit_rows = (int32_t)R;
+    std::vector<int32_t> width(G);
+    std::vector<int64_t> off_table(G);
     for (int g = 0; g < G; ++g) {
         int w = 0;
         if (fixed_widths) {
@@ -93,7 +95,7 @@ int prepare_step(CacheManager& cache, const StepLimits& lim, int nseq, const int
         } else {
             for (int s = 0; s < nseq; ++s) w = std::max(w, (int)cache.find(reqs[s])->tables[g].size());
         }
-        L.width[g] = w;
+        width[g] = w;
     }
     int64_t o = 0;
     L.off_tokens = o; o += T;
@@ -103,9 +105,10 @@ int prepare_step(CacheManager& cache, const StepLimits& lim, int nseq, const int
     L.off_context = o; o += nseq;
     L.off_slot = o; o += nseq;
     L.off_rows = o; o += R;
+    L.off_tables = o;
     for (int g = 0; g < G; ++g) {
-        L.off_table[g] = o;
-        o += (int64_t)nseq * L.width[g];
+        off_table[g] = o;
+        o += (int64_t)nseq * width[g];
     }
     L.total = o;
     if (o > cap) return fail(kMisuse, "the staging buffer of " + std::to_string(cap) + " integers is too small for " +
@@ -125,17 +128,18 @@ int prepare_step(CacheManager& cache, const StepLimits& lim, int nseq, const int
         buf[L.off_slot + s] = seq->state_slot;
         for (int g = 0; g < G; ++g) {
             const auto& table = seq->tables[g];
-            int32_t* dst = buf + L.off_table[g] + (int64_t)s * L.width[g];
-            const int have = std::min((int)table.size(), L.width[g]);
-            if ((int)table.size() > L.width[g]) return fail(kMisuse, "a block table is wider than the fixed width");
+            int32_t* dst = buf + off_table[g] + (int64_t)s * width[g];
+            const int have = std::min((int)table.size(), (int)width[g]);
+            if ((int)table.size() > width[g]) return fail(kMisuse, "a block table is wider than the fixed width");
             std::memcpy(dst, table.data(), sizeof(int32_t) * have);
-            for (int j = have; j < L.width[g]; ++j) dst[j] = kFreed;
+            for (int j = have; j < width[g]; ++j) dst[j] = kFreed;
         }
         row += n;
         L.max_query_len = std::max(L.max_query_len, (int32_t)n);
         L.max_context_len = std::max(L.max_context_len, (int32_t)(first_position[s] + n));
     }
     buf[L.off_start + nseq] = (int32_t)row;
+    std::copy(width.begin(), width.end(), widths);
     *out = L;
     return kOk;
 }

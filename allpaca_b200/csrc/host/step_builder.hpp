@@ -19,13 +19,12 @@ struct StepLayout {
     int32_t max_query_len, max_context_len;
     int64_t total;                       // integers used
     int64_t off_tokens, off_positions, off_seq, off_start, off_context, off_slot, off_rows;
-    int64_t off_table[8];
-    int32_t width[8];
+    int64_t off_tables;                  // the block tables follow one another from here: [nseq, width_g] each
 };
 
 int prepare_step(CacheManager& cache, const StepLimits& lim, int nseq, const int64_t* reqs,
                  const int32_t* tok_off, const int32_t* tokens, const int32_t* want_off, const int32_t* want,
-                 const int32_t* fixed_widths, int32_t* buf, int64_t cap, StepLayout* out,
+                 const int32_t* fixed_widths, int32_t* buf, int64_t cap, StepLayout* out, int32_t* widths,
                  int64_t* first_position, int32_t* state_slot, std::string* error);
 
 }  // namespace allpaca

@@ -214,14 +214,17 @@ class ModelRunner:
 
         def view(off, n):
             return dev[off:off + n]
+        tables, off = [], int(layout.off_tables)
+        for w in built.table_widths:
+            tables.append(view(off, nseq * w).view(nseq, w))
+            off += nseq * w
         return StepBatch(
             num_tokens=T, num_seqs=nseq, num_logit_rows=R,
             token_ids=view(layout.off_tokens, T), positions=view(layout.off_positions, T),
             token_seq=view(layout.off_seq, T), seq_start=view(layout.off_start, nseq + 1),
             context_lens=view(layout.off_context, nseq), state_slots=view(layout.off_slot, nseq),
             logit_rows=view(layout.off_rows, R),
-            block_tables=[view(layout.off_table[g], nseq * layout.width[g]).view(nseq, layout.width[g])
-                          for g in range(G)],
+            block_tables=tables,
             host_seq_start=tok_off, host_first_position=firsts,
             host_query_lens=lens, host_state_slots=slots,
             max_query_len=int(layout.max_query_len), max_context_len=int(layout.max_context_len))

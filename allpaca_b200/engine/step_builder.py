@@ -32,13 +32,13 @@ class StepLayout(ctypes.Structure):
                 ("max_query_len", ctypes.c_int32), ("max_context_len", ctypes.c_int32), ("pad", ctypes.c_int32),
                 ("total", ctypes.c_int64), ("off_tokens", ctypes.c_int64), ("off_positions", ctypes.c_int64),
                 ("off_seq", ctypes.c_int64), ("off_start", ctypes.c_int64), ("off_context", ctypes.c_int64),
-                ("off_slot", ctypes.c_int64), ("off_rows", ctypes.c_int64), ("off_table", ctypes.c_int64 * 8),
-                ("width", ctypes.c_int32 * 8)]
+                ("off_slot", ctypes.c_int64), ("off_rows", ctypes.c_int64), ("off_tables", ctypes.c_int64)]
 
 
 @dataclass
 class BuiltStep:
     layout: StepLayout
+    table_widths: List[int]        # per cache group; the tables lie one after another from off_tables
     first_position: List[int]      # position of each request's first row
     state_slot: List[int]
     query_lens: List[int]
@@ -78,12 +78,13 @@ def build_step(cache: CacheManager, entries: Sequence[BatchEntry], vocab_size: i
     layout = StepLayout()
     firsts = np.zeros(nseq, dtype=np.int64)
     slots = np.zeros(nseq, dtype=np.int32)
+    widths = np.zeros(max(1, len(cache.groups)), dtype=np.int32)
     lib = host_library()
     rc = lib.apc_prepare_step(
         cache.native, int(vocab_size), int(max_model_len), int(max_batched_tokens), nseq,
         reqs.ctypes.data, tok_off.ctypes.data, tokens.ctypes.data, want_off.ctypes.data, want.ctypes.data,
         fixed.ctypes.data if fixed is not None else None, host.ctypes.data, host.shape[0],
-        ctypes.addressof(layout), firsts.ctypes.data, slots.ctypes.data)
+        ctypes.addressof(layout), widths.ctypes.data, firsts.ctypes.data, slots.ctypes.data)
     if rc != 0:
         for r in fresh:
             cache.forget(r)
@@ -91,4 +92,5 @@ def build_step(cache: CacheManager, entries: Sequence[BatchEntry], vocab_size: i
         if rc == 2:
             raise OutOfPages(msg)
         raise StepError(msg)
-    return BuiltStep(layout, firsts.tolist(), slots.tolist(), lens.tolist(), tok_off.tolist())
+    return BuiltStep(layout, widths[:len(cache.groups)].tolist(), firsts.tolist(), slots.tolist(), lens.tolist(),
+                     tok_off.tolist())

@@ -17,6 +17,16 @@ def build(cache, host, entries, vocab=100, max_len=64, budget=64, widths=None):
     return build_step(cache, entries, vocab, max_len, budget, host, widths)
 
 
+def tables(built, host):
+    """The block tables of a built step, one [nseq, width] array per cache group."""
+    out, off, n = [], built.layout.off_tables, built.layout.num_seqs
+    for w in built.table_widths:
+        out.append(host[off:off + n * w].reshape(n, w).tolist())
+        off += n * w
+    assert off == built.layout.total
+    return out
+
+
 def test_mixed_batch_layout():
     cache, host = make()
     b = build(cache, host, [BatchEntry("a", [5, 6, 7, 8, 9], [4])])
@@ -32,9 +42,8 @@ def test_mixed_batch_layout():
     assert host[L.off_context:L.off_context + 2].tolist() == [6, 3]
     assert host[L.off_rows:L.off_rows + 3].tolist() == [0, 1, 3]
     assert host[L.off_slot:L.off_slot + 2].tolist() == [cache.state_slot("a"), cache.state_slot("b")] == b.state_slot
-    w = L.width[0]
-    assert w == 2                                              # "a" holds 6 tokens = 2 pages of 4
-    table = host[L.off_table[0]:L.off_table[0] + 2 * w].reshape(2, w).tolist()
+    assert b.table_widths == [2]                               # "a" holds 6 tokens = 2 pages of 4
+    table = tables(b, host)[0]
     assert table[0] == cache.block_table("a", 0) and table[1] == cache.block_table("b", 0) + [FREED]
     assert b.first_position == [5, 0]
     cache.check()
@@ -43,9 +52,8 @@ def test_mixed_batch_layout():
 def test_fixed_widths_for_graph_replay():
     cache, host = make()
     b = build(cache, host, [BatchEntry("a", [1, 2], [1])], widths=[5])
-    L = b.layout
-    assert L.width[0] == 5
-    assert host[L.off_table[0]:L.off_table[0] + 5].tolist() == cache.block_table("a", 0) + [FREED] * 4
+    assert b.table_widths == [5]
+    assert tables(b, host)[0] == [cache.block_table("a", 0) + [FREED] * 4]
 
 
 def test_windowed_group_gets_its_own_table():
@@ -53,10 +61,23 @@ def test_windowed_group_gets_its_own_table():
     build(cache, host, [BatchEntry("a", list(range(10)), [])])
     cache.release_passed("a")
     b = build(cache, host, [BatchEntry("a", [1], [0])])
-    L = b.layout
-    full = host[L.off_table[0]:L.off_table[0] + L.width[0]].tolist()
-    win = host[L.off_table[1]:L.off_table[1] + L.width[1]].tolist()
+    (full,), (win,) = tables(b, host)
     assert FREED not in full and win[0] == FREED and win[1:] == cache.block_table("a", 1)[1:]
+
+
+def test_any_number_of_cache_groups():
+    """Twelve groups with pages of different sizes: each gets a table of its own width."""
+    pages = [2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 16]
+    cache = CacheManager([GroupLayout(p, 64) for p in pages], 3)
+    host = np.zeros(8192, dtype=np.int32)
+    build(cache, host, [BatchEntry("a", list(range(30)), [])])
+    b = build(cache, host, [BatchEntry("b", list(range(7)), [6]), BatchEntry("a", [1], [0])])
+    assert b.table_widths == [-(-31 // p) for p in pages]
+    for g, table in enumerate(tables(b, host)):
+        assert table[1] == cache.block_table("a", g)
+        held = cache.block_table("b", g)
+        assert table[0] == held + [FREED] * (b.table_widths[g] - len(held))
+    cache.check()
 
 
 @pytest.mark.parametrize("entries, word", [
