@@ -31,18 +31,23 @@
 static __device__ int g_tc_status;
 
 template <int BN, bool CLUSTER = false> struct TileCfg {
-    // 64 rows in a cluster: three stages, so that two CTAs with their reduction buffers share an SM
-    static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : ((CLUSTER && BN == 64) ? 3 : 4));
     static constexpr int kBBytes = BN * TILE_K * 2;
     static constexpr int kStageBytes = A_TILE_BYTES + kBBytes;
     static constexpr int kTmemCols = BN < 32 ? 32 : BN;
     static constexpr int kBarrierBytes = 256 + 1024;      // barriers, then the scale of each token column
     // cluster reduction buffer: [slices][BN][rows per slice], at most 136 rows in all
     static constexpr int kReduceBytes = (TILE_W + 8) * BN * 4;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + kBarrierBytes;
     // 128 tokens and more: the reduction buffer lies over the stages, which are idle by then
     static constexpr bool kReduceOverStages = BN >= 128;
+    static constexpr int kFixedBytes = 1024 /*alignment*/ + kBarrierBytes + ((CLUSTER && !kReduceOverStages) ? kReduceBytes : 0);
+    // Up to 64 tokens: as many stages as let two CTAs share an SM (227 KB, 1 KB of each CTA the
+    // system's), so that the CTAs of the next product can load their weights beside this one's.
+    // One stage fewer or more than that costs 3 to 25 % of a decode step.
+    static constexpr int kHalfSm = 232448 / 2 - 1024;
+    static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : (kHalfSm - kFixedBytes) / kStageBytes);
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;
     static constexpr int kSmemBytesCluster = kSmemBytes + (kReduceOverStages ? 0 : kReduceBytes);
+    static_assert(kStages >= 3 && kStages <= 8, "stage count out of range");
     static_assert(!kReduceOverStages || kReduceBytes <= kStages * kStageBytes, "the reduction buffer must fit the stages");
 };
 
