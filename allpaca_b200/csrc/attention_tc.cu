@@ -676,10 +676,16 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     if (warp == 4) {
-        // producer: lane j owns page j of every tile
-        const int pages_per_tile = BKV / p.P;
-        const int page_bytes = p.P * 128;                 // one page, 64 columns of the head
+        // producer: lane j owns page j of every tile; a page larger than a tile is lane 0's, and
+        // the tile a part of it
+        const bool big_pages = p.P > BKV;
+        const int pages_per_tile = big_pages ? 1 : BKV / p.P;
+        const int page_bytes = (big_pages ? BKV : p.P) * 128;   // one page (or tile), 64 columns of the head
         auto page_of = [&](int it) {
+            if (big_pages) {
+                const int lp = (t_lo + it) * BKV / p.P;
+                return (it >= n || lane != 0 || lp >= p.max_blocks) ? -1 : table[lp];
+            }
             const int lp = (t_lo + it) * pages_per_tile + lane;
             if (it >= n || lane >= pages_per_tile || lp >= p.max_blocks || lp * p.P > kmax ||
                 lp * p.P + p.P - 1 < kmin)
@@ -715,7 +721,8 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __
             // pages of a tile that follow one another in memory (a sequence's pages are handed out
             // in rising order) come with one box per half: loads are issued at a limited rate
             const int page0 = __shfl_sync(0xffffffffu, page, 0);
-            const bool run = page0 >= 0 && __all_sync(0xffffffffu, lane >= pages_per_tile || page == page0 + lane);
+            const bool run = !big_pages && page0 >= 0 &&
+                             __all_sync(0xffffffffu, lane >= pages_per_tile || page == page0 + lane);
             if (run) {
                 if (lane == 0) {
                     uint8_t* dst = smem + s * DT_STAGE_BYTES;
@@ -728,8 +735,9 @@ attention_split_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __
                 }
             } else if (page >= 0) {
                 uint8_t* dst = smem + s * DT_STAGE_BYTES + lane * page_bytes;
-                const int krow = ((page * 2 + 0) * p.nkv + kvh) * p.P;
-                const int vrow = ((page * 2 + 1) * p.nkv + kvh) * p.P;
+                const int within = big_pages ? ((t_lo + it) * BKV) % p.P : 0;
+                const int krow = ((page * 2 + 0) * p.nkv + kvh) * p.P + within;
+                const int vrow = ((page * 2 + 1) * p.nkv + kvh) * p.P + within;
 #pragma unroll
                 for (int h = 0; h < DT_NHALF; ++h) {
                     tc::tma_load_2d(dst + h * SWZ_HALF_BYTES, &tmap_kv, h * 64, krow, &full[s]);
@@ -886,7 +894,8 @@ static DtEncodeFn dt_encode_fn() {
 // 1 when ap_attention_decode_tma takes this shape, else 0 (the caller then uses ap_attention_tc)
 AP_EXPORT int ap_attention_decode_tma_supports(int nh, int nkv, int hd, int P) {
     if (hd != HD || nkv <= 0 || nh % nkv) return 0;
-    if (P < 8 || P > BKV || BKV % P) return 0;
+    // pages that divide a key tile, or that whole key tiles divide
+    if (P < 8 || (P <= BKV ? BKV % P : (P % BKV || P > 1024))) return 0;
     return dt_encode_fn() != nullptr;
 }
 
@@ -918,7 +927,7 @@ AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cach
     {
         cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)(num_pages * 2 * nkv * P)};
         cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-        cuuint32_t box[2] = {64, (cuuint32_t)P};
+        cuuint32_t box[2] = {64, (cuuint32_t)(P < BKV ? P : BKV)};
         cuuint32_t es[2] = {1, 1};
         AP_REQUIRE(dt_encode_fn()(&mkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides,
                                   box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -930,7 +939,8 @@ AP_EXPORT int ap_attention_decode_tma(const void* q, void* out, const void* cach
         // the same cache as [page][row within the page][column]: a box spans the pages of a key tile
         cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)(2 * nkv * P), (cuuint64_t)num_pages};
         cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)page_stride * 2};
-        cuuint32_t box[3] = {64, (cuuint32_t)P, (cuuint32_t)(BKV / P)};
+        // (pages larger than a tile are never loaded through this map)
+        cuuint32_t box[3] = {64, (cuuint32_t)(P < BKV ? P : BKV), (cuuint32_t)(P < BKV ? BKV / P : 1)};
         cuuint32_t es[3] = {1, 1, 1};
         AP_REQUIRE(dt_encode_fn()(&mrun, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(cache), dims, strides,
                                   box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,

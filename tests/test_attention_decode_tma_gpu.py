@@ -11,7 +11,7 @@ from test_kernels_gpu import dev, paged_case, reference_attention, rel_err
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(8, 2, 128, 16), (32, 8, 128, 16), (4, 4, 128, 8), (16, 2, 64, 32), (8, 8, 64, 16), (16, 1, 128, 64),
-          (40, 2, 64, 16)]
+          (40, 2, 64, 16), (32, 8, 128, 128), (8, 2, 64, 256), (8, 8, 64, 128)]
 DECODE = [(700, 1), (129, 1), (64, 1), (1, 1), (65, 1), (1500, 1), (3000, 1)]
 
 
@@ -44,6 +44,8 @@ def test_shapes_are_taken_or_left(ops):
     assert lib.ap_attention_decode_tma_supports(32, 8, 128, 16)
     assert not lib.ap_attention_decode_tma_supports(32, 8, 128, 4)       # page of 4: below one swizzle atom
     assert not lib.ap_attention_decode_tma_supports(32, 8, 128, 48)      # does not divide a tile
+    assert lib.ap_attention_decode_tma_supports(32, 8, 128, 128)         # two tiles to a page
+    assert not lib.ap_attention_decode_tma_supports(32, 8, 128, 96)      # no whole number of tiles
     assert not lib.ap_attention_decode_tma_supports(32, 8, 64, 16)       # another head size's library
     assert not library.attention(48).ap_attention_decode_tma_supports(6, 2, 48, 16)
 
@@ -64,7 +66,7 @@ def test_against_plain_and_cp_async(ops, nh, nkv, hd, P, window, sequential):
 
 
 @pytest.mark.parametrize("splits", [1, 2, 3, 4, 7, 8, 16, 24, 47])
-@pytest.mark.parametrize("nh,nkv,hd,P", [(8, 2, 128, 16), (16, 1, 128, 64), (40, 2, 64, 16)])
+@pytest.mark.parametrize("nh,nkv,hd,P", [(8, 2, 128, 16), (16, 1, 128, 64), (40, 2, 64, 16), (8, 2, 128, 128)])
 def test_any_number_of_key_slices(ops, splits, nh, nkv, hd, P, monkeypatch):
     """Slices that hold one tile, many tiles or none at all (more slices than tiles); 2, 4, 8
     and 16 slices are combined inside a thread-block cluster where their results fit, the other
@@ -76,8 +78,9 @@ def test_any_number_of_key_slices(ops, splits, nh, nkv, hd, P, monkeypatch):
 
 
 @pytest.mark.parametrize("far", [0, 7, 8, 15, 16, 63, 64, 127, 128, 500, 1023])
-def test_finds_one_far_key(ops, far):
-    nh, nkv, hd, P = 4, 2, 64, 16
+@pytest.mark.parametrize("P", [16, 128])
+def test_finds_one_far_key(ops, far, P):
+    nh, nkv, hd = 4, 2, 64
     ctx = 1024
     seqs = [(ctx, 1), (ctx - 3, 1)]
     case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=far)
@@ -100,8 +103,9 @@ def test_finds_one_far_key(ops, far):
 
 
 @pytest.mark.parametrize("sequential", [False, True])
-def test_pages_given_back_are_not_read(ops, sequential):
-    nh, nkv, hd, P, window = 8, 2, 128, 16, 150
+@pytest.mark.parametrize("P", [16, 128])
+def test_pages_given_back_are_not_read(ops, sequential, P):
+    nh, nkv, hd, window = 8, 2, 128, 150
     seqs = [(900, 1), (500, 1), (149, 1)]
     freed = [900 - 1 - window + 1, 500 - 1 - window + 1, 0]
     case = paged_case(seqs, nh, nkv, hd, P, torch.bfloat16, seed=9, freed_before=freed, sequential=sequential)

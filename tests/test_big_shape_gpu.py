@@ -8,10 +8,11 @@ import plain_llama
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("two_query_tiles", [False, True])
-def test_two_layers_of_the_8b_shape(tmp_path, monkeypatch, two_query_tiles):
+@pytest.mark.parametrize("two_query_tiles,page", [(False, 16), (True, 16), (False, 128)])
+def test_two_layers_of_the_8b_shape(tmp_path, monkeypatch, two_query_tiles, page):
     """``two_query_tiles``: the prompt attention with two query tiles to a CTA, which the engine
-    otherwise keeps for longer portions, takes every portion of 64 rows or more."""
+    otherwise keeps for longer portions, takes every portion of 64 rows or more.  ``page``: 128
+    tokens to a page (two key tiles of the decode kernel, one of the prompt kernel's)."""
     from allpaca_b200 import ops
     if two_query_tiles:
         monkeypatch.setattr(ops, "WIDE_ATTENTION_MIN_CTAS", 1)
@@ -30,7 +31,7 @@ def test_two_layers_of_the_8b_shape(tmp_path, monkeypatch, two_query_tiles):
     want_rows = [0, 1, 63, 64, 127, 128, 149]
     w = None
     for dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, 3e-2)):
-        env = BuildEnv(dtype, dev, Workspace(dev), page_size=16, max_seqs=2)
+        env = BuildEnv(dtype, dev, Workspace(dev), page_size=page, max_seqs=2)
         cfg, model = random_model_on_device(raw, 2, env)
         if w is None:
             # weights are drawn on the GPU in 32-bit (bfloat16 is their rounding): the plain
@@ -58,7 +59,7 @@ def test_two_layers_of_the_8b_shape(tmp_path, monkeypatch, two_query_tiles):
         else:
             plain = plain_llama.llama_forward(raw, {k: v.bfloat16() for k, v in w.items()}, tokens,
                                               torch.float32, round_to=torch.bfloat16)[want_rows].double()
-        runner = ModelRunner(None, EngineConfig(dtype=dtype, page_size=16, max_cache_tokens=512, max_num_seqs=2,
+        runner = ModelRunner(None, EngineConfig(dtype=dtype, page_size=page, max_cache_tokens=512, max_num_seqs=2,
                                                 max_num_batched_tokens=256, use_cuda_graphs=False), model=model)
         whole = runner.step([BatchEntry("w", tokens, want_rows)]).double().cpu()
         err = float((whole - plain).abs().max() / plain.abs().max())
