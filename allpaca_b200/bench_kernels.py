@@ -306,6 +306,27 @@ def bench_versus_reference(args) -> dict:
     return {"rows": [{"operation": n, "reference_us": a, "ours_float32_us": b, "ours_bfloat16_us": c} for n, a, b, c in rows]}
 
 
+def bench_sampling(args) -> dict:
+    """The choice of the next token for ``--rows`` rows of logits over ``--vocab`` entries."""
+    from allpaca_b200 import ops
+    R, V = args.rows, args.vocab
+    copies = max(2, int(math.ceil(300e6 / (R * V * 4))))
+    logits = [torch.randn(R, V, device="cuda") * args.spread for _ in range(copies)]
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    temp = torch.full((R,), args.temperature, device="cuda")
+    top_k = torch.full((R,), args.top_k, dtype=torch.int32, device="cuda")
+    top_p = torch.full((R,), args.top_p, device="cuda")
+    uniform = torch.rand(R, device="cuda")
+    if args.temperature <= 1e-5:
+        kernel, fn = "argmax", (lambda i: ops.argmax(logits[i % copies], out))     # noqa: E731
+    else:
+        kernel = "sample"
+        fn = lambda i: ops.sample(logits[i % copies], temp, top_k, top_p, uniform, out)   # noqa: E731
+    us = _time(fn, args.iters, args.warmup, not args.no_graph)
+    return {"kernel": kernel, "rows": R, "vocab": V, "temperature": args.temperature, "top_k": args.top_k,
+            "top_p": args.top_p, "us": round(us, 2), "GBps": round(R * V * 4 / us / 1e3, 1)}
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="python -m allpaca_b200.bench_kernels")
     sub = p.add_subparsers(dest="what", required=True)
@@ -344,12 +365,22 @@ def main(argv=None) -> int:
                            help="prompt attention on tcgen05: query tiles to a CTA (auto: by the number of CTAs)")
             s.add_argument("--scattered-pages", action="store_true",
                            help="block tables in random order instead of rising page numbers")
+    s = sub.add_parser("sampling")
+    s.add_argument("--iters", type=int, default=50)
+    s.add_argument("--warmup", type=int, default=5)
+    s.add_argument("--no-graph", action="store_true", help="launch from the host (for ncu)")
+    s.add_argument("--rows", type=int, default=8)
+    s.add_argument("--vocab", type=int, default=128256)
+    s.add_argument("--temperature", type=float, default=0.8, help="0: the arg-max kernel")
+    s.add_argument("--top-k", type=int, default=40, help="0: off")
+    s.add_argument("--top-p", type=float, default=0.95, help="1: off")
+    s.add_argument("--spread", type=float, default=3.0, help="standard deviation of the random logits")
     s = sub.add_parser("versus-reference")
     s.add_argument("--iters", type=int, default=20)
     s.add_argument("--warmup", type=int, default=3)
     args = p.parse_args(argv)
     fn = {"gemm": bench_gemm, "attention": bench_attention, "prefill-attention": bench_prefill_attention,
-          "versus-reference": bench_versus_reference}[args.what]
+          "sampling": bench_sampling, "versus-reference": bench_versus_reference}[args.what]
     print(json.dumps(fn(args)))
     return 0
 

@@ -38,7 +38,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
                 "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 
 CORE_SOURCES = ["errors.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_pair.cu",
-                "sampling.cu"]
+                "sampling.cu", "sampling_cluster.cu"]
 ATTN_SOURCES = ["errors.cu", "attention.cu", "attention_tc.cu", "attention_tcgen05.cu",
                 "attention_tcgen05_wide.cu"]
 HEADERS = ["common.cuh", "tcgen05.cuh", "attention_noalloc.h"]

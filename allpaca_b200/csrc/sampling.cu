@@ -303,12 +303,29 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
     }
 }
 
-AP_EXPORT int ap_sample(const float* logits, long long row_stride, int R, int V, const float* temperature,
-                        const int* top_k, const float* top_p, const float* uniform, int* out,
-                        cudaStream_t stream) {
+// The kernel above: one CTA per row, any vocabulary.
+AP_EXPORT int ap_sample_rows(const float* logits, long long row_stride, int R, int V, const float* temperature,
+                             const int* top_k, const float* top_p, const float* uniform, int* out,
+                             cudaStream_t stream) {
     AP_REQUIRE(R >= 0 && V > 0 && row_stride >= V, "sample: bad sizes R=%d V=%d", R, V);
     if (R == 0) return AP_OK;
     sample_kernel<<<R, SAMP_THREADS, 0, stream>>>(logits, row_stride, V, temperature, top_k, top_p, uniform, out);
     AP_CHECK_LAUNCH("sample");
     return AP_OK;
+}
+
+// sampling_cluster.cu: a cluster of CTAs per row, the row in registers
+extern "C" int ap_sample_cluster_max_vocab(void);
+extern "C" int ap_sample_cluster(const float* logits, long long row_stride, int R, int V, const float* temperature,
+                                 const int* top_k, const float* top_p, const float* uniform, int* out,
+                                 cudaStream_t stream);
+
+// One token per row: the cluster kernel where the vocabulary fits its registers (up to 262144
+// entries), else one CTA per row.
+AP_EXPORT int ap_sample(const float* logits, long long row_stride, int R, int V, const float* temperature,
+                        const int* top_k, const float* top_p, const float* uniform, int* out,
+                        cudaStream_t stream) {
+    if (V > 0 && V <= ap_sample_cluster_max_vocab() && R <= 65535)
+        return ap_sample_cluster(logits, row_stride, R, V, temperature, top_k, top_p, uniform, out, stream);
+    return ap_sample_rows(logits, row_stride, R, V, temperature, top_k, top_p, uniform, out, stream);
 }

@@ -616,8 +616,11 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
-           top_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:
-    """One token per row: greedy where temperature <= 1e-5, else temperature/top-k/top-p."""
+           top_p: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor, method: str = "auto") -> None:
+    """One token per row: greedy where temperature <= 1e-5, else temperature/top-k/top-p.
+
+    ``method``: "cluster" (eight CTAs hold a row in registers; vocabularies of up to 262144
+    entries), "rows" (one CTA per row, any vocabulary) or "auto" (the first where it fits)."""
     _check(logits, "logits", torch.float32, 2)
     R, V = logits.shape
     for t, n, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
@@ -626,7 +629,10 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
         _check(t, n, dt, 1)
         if t.shape[0] < R:
             raise KernelError(f"sample: {n} has fewer than {R} entries")
-    call(core(), "ap_sample", logits.data_ptr(), V, R, V, temperature.data_ptr(), top_k.data_ptr(),
+    entry = {"auto": "ap_sample", "cluster": "ap_sample_cluster", "rows": "ap_sample_rows"}.get(method)
+    if entry is None:
+        raise KernelError(f"sample: unknown method {method!r}")
+    call(core(), entry, logits.data_ptr(), V, R, V, temperature.data_ptr(), top_k.data_ptr(),
          top_p.data_ptr(), uniform.data_ptr(), out.data_ptr(), stream_handle())
 
 

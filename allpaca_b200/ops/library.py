@@ -34,6 +34,8 @@ _CORE_SIGNATURES = {
     "ap_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "ap_argmax": [_P, _L, _I, _I, _P, _P],
     "ap_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
+    "ap_sample_rows": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
+    "ap_sample_cluster": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
 }
 _OPTIONAL_CORE_SIGNATURES = {
     # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, epi,

@@ -245,8 +245,27 @@ def test_argmax_first_maximum(ops):
     assert out.cpu().tolist() == want
 
 
+def check_samples(ops, logits, cases, method):
+    """``cases``: (temperature, top_k, top_p, uniform) per row of ``logits``."""
+    R = len(cases)
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits), dev(torch.tensor([c[0] for c in cases])),
+               dev(torch.tensor([c[1] for c in cases], dtype=torch.int32)),
+               dev(torch.tensor([c[2] for c in cases])), dev(torch.tensor([c[3] for c in cases])), out,
+               method=method)
+    got = out.cpu().tolist()
+    for r, (temp, k, p, u) in enumerate(cases):
+        want = plain_llama.sample_plain(logits[r], temp, k, p, u)
+        if got[r] != want:
+            # allowed only when u sits on a boundary of the cumulative distribution (rounding)
+            alt = {plain_llama.sample_plain(logits[r], temp, k, p, min(max(u + d, 0.0), 0.999999))
+                   for d in (-2e-6, 2e-6)}
+            assert got[r] in alt, (r, cases[r], got[r], want)
+
+
+@pytest.mark.parametrize("method", ["cluster", "rows"])
 @pytest.mark.parametrize("V", [64, 301, 5000])
-def test_sample_matches_plain(ops, V):
+def test_sample_matches_plain(ops, V, method):
     g = torch.Generator().manual_seed(V)
     cases = []
     for temp, k, p in [(0.0, 0, 1.0), (0.8, 0, 1.0), (1.3, 5, 1.0), (0.7, 0, 0.9), (0.8, 40, 0.95),
@@ -257,18 +276,68 @@ def test_sample_matches_plain(ops, V):
     logits = torch.randn(R, V, generator=g) * 2
     logits[5, 3] = logits[5, 9] = logits[5].max() + 1      # ties at the top
     logits[7, ::3] = float("-inf")                           # non-finite entries are dropped
-    out = torch.empty(R, dtype=torch.int32, device="cuda")
-    ops.sample(dev(logits), dev(torch.tensor([c[0] for c in cases])),
-               dev(torch.tensor([c[1] for c in cases], dtype=torch.int32)),
-               dev(torch.tensor([c[2] for c in cases])), dev(torch.tensor([c[3] for c in cases])), out)
-    got = out.cpu().tolist()
-    for r, (temp, k, p, u) in enumerate(cases):
-        want = plain_llama.sample_plain(logits[r], temp, k, p, u)
-        if got[r] != want:
-            # allowed only when u sits on a boundary of the cumulative distribution (rounding)
-            alt = {plain_llama.sample_plain(logits[r], temp, k, p, min(max(u + d, 0.0), 0.999999))
-                   for d in (-2e-6, 2e-6)}
-            assert got[r] in alt, (r, cases[r], got[r], want)
+    check_samples(ops, logits, cases, method)
+
+
+@pytest.mark.parametrize("method", ["cluster", "rows"])
+def test_sample_where_many_logits_are_equal_or_far_away(ops, method):
+    """Rows that defeat a search by value: thousands of equal logits at the cut (more than the
+    sorted list of the cluster kernel holds), a few logits far below the rest, a single finite
+    logit, and a row of two values only."""
+    V = 6000
+    g = torch.Generator().manual_seed(11)
+    rows, cases = [], []
+
+    def add(row, temp, k, p, us=(0.0, 0.3, 0.77, 0.999)):
+        for u in us:
+            rows.append(row.clone())
+            cases.append((temp, k, p, u))
+    flat = torch.zeros(V)
+    add(flat, 1.0, 0, 1.0)
+    add(flat, 1.0, 10, 1.0)
+    add(flat, 0.7, 3000, 1.0)
+    add(flat, 1.0, 0, 0.5003)            # (not 0.5: 3000 equal shares would reach it up to rounding only)
+    add(flat, 1.0, 4000, 0.9003)
+    two = torch.zeros(V)
+    two[::2] = 1.5                       # 3000 equal logits above 3000 equal ones
+    add(two, 1.0, 3500, 1.0)
+    add(two, 1.0, 2500, 0.7003)
+    add(two, 0.9, 0, 0.95)
+    far = torch.randn(V, generator=g)
+    far[100:130] = -1e9                  # masked out by a large negative number
+    far[7] = -3e38
+    add(far, 0.8, 40, 0.95)
+    add(far, 0.8, V - 5, 1.0)            # the cut lies among the far ones
+    add(far, 1.2, 0, 0.999)
+    lone = torch.full((V,), float("-inf"))
+    lone[4321] = 0.25
+    add(lone, 0.8, 40, 0.95)
+    add(lone, 0.8, 0, 0.2)
+    check_samples(ops, torch.stack(rows), cases, method)
+
+
+@pytest.mark.parametrize("V", [128256, 200003])
+def test_sample_large_vocabulary(ops, V):
+    """The cluster kernel at the sizes it is for (32 and 64 logits a thread), against the plain
+    sampler on a few rows and against the kernel with one CTA per row on all of them."""
+    g = torch.Generator().manual_seed(V)
+    settings = [(0.8, 40, 0.95), (0.8, 0, 1.0), (1.0, 0, 0.9), (0.6, 3000, 0.99), (1.5, 1, 1.0), (0.0, 0, 1.0),
+                (0.9, 2048, 0.5), (1.0, 0, 0.0)]
+    cases = [(t, k, p, u) for (t, k, p) in settings for u in (0.0, 0.41, 0.93)]
+    R = len(cases)
+    logits = torch.randn(R, V, generator=g) * 3
+    logits[:, 1000:1010] = float("nan")
+    outs = {}
+    for method in ("cluster", "rows"):
+        out = torch.empty(R, dtype=torch.int32, device="cuda")
+        ops.sample(dev(logits), dev(torch.tensor([c[0] for c in cases])),
+                   dev(torch.tensor([c[1] for c in cases], dtype=torch.int32)),
+                   dev(torch.tensor([c[2] for c in cases])), dev(torch.tensor([c[3] for c in cases])), out,
+                   method=method)
+        outs[method] = out.cpu().tolist()
+    differ = [r for r in range(R) if outs["cluster"][r] != outs["rows"][r]]
+    assert len(differ) <= 1, differ          # a draw on a boundary of the cumulative distribution may differ
+    check_samples(ops, logits[:4], cases[:4], "cluster")
 
 
 def test_sample_distribution(ops):
