@@ -55,7 +55,7 @@ def bench_gemm(args) -> dict:
     S = args.splits or ops.gemm_tc_splits(M, N, K)
     odt = torch.float32 if args.out == "float32" else torch.bfloat16
     kernel = "gemm_tc"
-    if M > 64 and not args.dual and not args.pair and not args.single and (S == 1 or args.whole_tiles):
+    if M > 128 and not args.dual and not args.pair and not args.single and (S == 1 or args.whole_tiles):
         # the persistent kernel; with --swiglu the rows of w alternate gate and up
         kernel = "gemm_tc_persistent"
         out = torch.empty(M, N // 2 if args.swiglu else N, device="cuda", dtype=odt)

@@ -32,6 +32,8 @@ def main(argv=None) -> int:
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all)")
     p.add_argument("--requests", type=int, default=0, help="another number of requests (0: the workload's)")
     p.add_argument("--no-graphs", action="store_true")
+    p.add_argument("--sampling", choices=["greedy", "default"], default="greedy",
+                   help="default: temperature 0.8, top-k 40, top-p 0.95 (the reference's defaults), seeded")
     args = p.parse_args(argv)
 
     from allpaca_b200.config import EngineConfig
@@ -66,7 +68,8 @@ def main(argv=None) -> int:
     runner = ModelRunner(None, engine, model=model, model_config=cfg)
     runner.workspace = env.workspace
     llm = LLM(runner=runner)
-    params = SamplingParams.greedy_params(max_tokens=new_tokens)
+    params = SamplingParams.greedy_params(max_tokens=new_tokens) if args.sampling == "greedy" else \
+        SamplingParams(max_tokens=new_tokens, seed=seed)
 
     # a short run first: libraries loaded, graphs of the small batches captured
     llm.generate(prompts[:2], SamplingParams.greedy_params(max_tokens=4))
@@ -83,7 +86,7 @@ def main(argv=None) -> int:
         "requests": nreq, "prompt_tokens": sum(lengths), "generated_tokens": generated, "seconds": round(wall, 3),
         "generated_tok_s": round(generated / wall, 1), "total_tok_s": round((generated + sum(lengths)) / wall, 1),
         "steps": stats.get("steps", 0) - steps0, "preemptions": stats.get("preemptions", 0),
-        "portion": portion, "page_size": page, "dtype": "bf16", "data": "synthetic"}))
+        "portion": portion, "page_size": page, "sampling": args.sampling, "dtype": "bf16", "data": "synthetic"}))
     return 0
 
 

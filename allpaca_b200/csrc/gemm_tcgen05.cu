@@ -40,11 +40,11 @@ template <int BN, bool CLUSTER = false> struct TileCfg {
     // 128 tokens and more: the reduction buffer lies over the stages, which are idle by then
     static constexpr bool kReduceOverStages = BN >= 128;
     static constexpr int kFixedBytes = 1024 /*alignment*/ + kBarrierBytes + ((CLUSTER && !kReduceOverStages) ? kReduceBytes : 0);
-    // Up to 64 tokens: as many stages as let two CTAs share an SM (227 KB, 1 KB of each CTA the
+    // Up to 128 tokens: as many stages as let two CTAs share an SM (227 KB, 1 KB of each CTA the
     // system's), so that the CTAs of the next product can load their weights beside this one's.
     // One stage fewer or more than that costs 3 to 25 % of a decode step.
     static constexpr int kHalfSm = 232448 / 2 - 1024;
-    static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : (kHalfSm - kFixedBytes) / kStageBytes);
+    static constexpr int kStages = BN >= 256 ? 4 : (kHalfSm - kFixedBytes) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kBarrierBytes;
     static constexpr int kSmemBytesCluster = kSmemBytes + (kReduceOverStages ? 0 : kReduceBytes);
     static_assert(kStages >= 3 && kStages <= 8, "stage count out of range");
@@ -721,20 +721,17 @@ AP_EXPORT int ap_gemm_tc_plan(int M, int N, int K) {
     const int kb_total = (K + TILE_K - 1) / TILE_K;
     const int bn = pick_bn(M);
     const long long tiles = (long long)((N + TILE_W - 1) / TILE_W) * ((M + bn - 1) / bn);
-    if (M > 256 || tiles >= 148) return 1;
-    // as many slices as keep the whole grid resident at once (two CTAs per SM, or one from 65
-    // rows on, whose tiles fill an SM's shared memory; a little slack so that the clusters
-    // find room side by side)
-    int ns = (int)((M > 64 ? 148 : 288) / tiles);
-    if (M > 64) ns = min(ns, kb_total / 8);
-    else {
-        ns = min(ns, kb_total / 4);
-        ns = min(ns, max(1, K / (16 * M)));    // more rows: fewer, longer slices
-    }
+    const bool wide = bn > 128;             // a tile of 256 tokens fills an SM; narrower ones go two to an SM
+    if (M > 256 || tiles >= (wide ? 148 : 288)) return 1;
+    // as many slices as keep the whole grid resident at once, with a little slack so that the
+    // clusters find room side by side.  Measured inside the decode step and alone, 8 to 128
+    // rows: the 8B QKV weight (48 tiles) wants 4 slices, O and down (32 tiles) 8, at every row count.
+    int ns = (int)((wide ? 148 : 288) / tiles);
+    ns = min(ns, wide ? kb_total / 8 : kb_total / 4);
     ns = min(ns, 8);                       // one thread-block cluster adds the slices
     if (ns < 1) ns = 1;
     while (ns & (ns - 1)) ns &= ns - 1;    // clusters of 2, 4 or 8 CTAs find room side by side; odd sizes do not
-    if (M > 64 && ns < 4) return 1;        // two slices of a wide tile cost more to add than they save
+    if (wide && ns < 4) return 1;          // two slices of a wide tile cost more to add than they save
     const int per = (kb_total + ns - 1) / ns;
     return (kb_total + per - 1) / per;
 }
@@ -968,7 +965,7 @@ AP_EXPORT int ap_gemm_tc_dual(const void* a, const void* w, void* out, int out_d
 // times as long as a single one, and either kind runs in waves of one CTA per SM.
 AP_EXPORT int ap_gemm_tc_prefers_dual(int M, int N, int K) {
     (void)K;
-    if (M <= 64) return 0;
+    if (M <= 128) return 0;
     const int bn = M <= 128 ? 128 : 256;
     const long long rows = (M + bn - 1) / bn;
     const long long single = ((N + TILE_W - 1) / TILE_W) * rows, dual = ((N + 2 * TILE_W - 1) / (2 * TILE_W)) * rows;
@@ -1411,7 +1408,10 @@ AP_EXPORT int ap_gemm_tc_persistent(const void* a, const void* w, void* out, int
 // covers the whole product in a single, well-filled wave.
 AP_EXPORT int ap_gemm_tc_prefers_persistent(int M, int N, int K) {
     (void)K;
-    if (M <= 64) return 0;
+    // up to 128 rows every weight tile is one CTA of the kernel above, two to an SM, all resident
+    // at once: they stream the weight at one rate, where tiles dealt out to one CTA per SM leave
+    // the SMs with one tile fewer idle (8B gate+up at 128 rows: 48 against 59 us)
+    if (M <= 128) return 0;
     const int bn = M <= 128 ? 128 : 256;
     const long long rows = (M + bn - 1) / bn;
     const long long tiles = ((N + TILE_W - 1) / TILE_W) * rows, dual = ((N + 2 * TILE_W - 1) / (2 * TILE_W)) * rows;

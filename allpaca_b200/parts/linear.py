@@ -99,7 +99,7 @@ class Linear:
             out = ws.get(buffer_name, (T, N), torch.float32 if kind == "float32" else self.env.dtype)
             target = out
         if tc and T > 64 and nsplit > 1:
-            # 65 to 256 rows against few weight tiles: K slices in a cluster, as for decoding
+            # up to 256 rows against few weight tiles: K slices in a cluster, as for decoding
             ops.gemm_tc(a, self.weight, target, nsplit, reduce=True)
         elif tc and T > 64 and ops.gemm_tc_prefers_persistent(T, N, self.in_features):
             ops.gemm_tc_persistent(a, self.weight, target)
@@ -125,7 +125,7 @@ class Linear:
             return None
         out = self.env.workspace.get(buffer_name, (T, self.out_features // 2), self.env.dtype)
         nsplit = ops.gemm_tc_splits(T, self.out_features, self.in_features)
-        if T > 64 and nsplit == 1:
+        if T > 128 and nsplit == 1:
             if scale is not None:
                 raise ValueError("a scale of the rows is only applied by the tensor-core kernel for few rows")
             ops.gemm_tc_persistent(a, self.weight, out, pairs=True)

@@ -36,9 +36,10 @@ def test_plan_stays_within_a_cluster():
             s = ops.gemm_tc_splits(M, N, K)
             kb = -(-K // 64)
             assert 1 <= s <= 8 and (s - 1) * (-(-kb // s)) < kb
-            assert M <= 64 or s != 2          # from 65 rows on two slices do not pay: four or more, or none
-    # 65 to 256 rows against few weight tiles are still split; more rows never
-    assert ops.gemm_tc_splits(65, 4096, 4096) == 4 and ops.gemm_tc_splits(257, 4096, 4096) == 1
+            assert M <= 128 or s != 2         # tiles of 256 tokens: two slices do not pay: four or more, or none
+    # up to 256 rows against few weight tiles are split (two CTAs to an SM up to 128 rows, one beyond); more rows never
+    assert ops.gemm_tc_splits(64, 4096, 4096) == 8 and ops.gemm_tc_splits(128, 6144, 4096) == 4
+    assert ops.gemm_tc_splits(129, 4096, 4096) == 4 and ops.gemm_tc_splits(257, 4096, 4096) == 1
     assert ops.gemm_tc_splits(2048, 4096, 4096) == 1 and ops.gemm_tc_splits(200, 28672, 4096) == 1
 
 
