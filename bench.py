@@ -13,11 +13,14 @@ A step is one decode step of the whole batch.
               the step's positions and tables are still built on the host and uploaded;
 * ``e2e``     the same through ``LLM.step()`` (scheduler, pinned-memory upload of the step's
               tokens and tables, read-back of the chosen tokens), by the host clock;
-* ``prefill`` one prompt of 2048 tokens in one step: tokens/s, ms and the fraction of the
-              bf16 peak its FLOPs reach;
+* ``prefill`` one prompt of 2048 tokens in one step: tokens/s, the best time of five runs (``ms``)
+              and their median (``median_ms``: repeated back to back the runs slow down as the
+              power cap pulls the clock down), and the fractions of the bf16 peak their FLOPs reach;
 * ``roofline`` bytes a decode step must read (every weight once, the cache of the live
               requests) over its time, against the measured HBM copy rate;
-* ``points``  decode at batch 1 and 64.
+* ``points``  decode at batch 1 and 64, and at batch 8 of the other benchmark shapes
+              (``--no-presets`` leaves those out), each with its fraction of the copy rate;
+* ``clocks``  SM clocks and throttle reasons sampled by nvidia-smi across the timed regions.
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from the fallback
 figures measured earlier on the same pool (6650 GB/s, 1590 TFLOP/s).
 """
