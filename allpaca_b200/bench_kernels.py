@@ -55,7 +55,8 @@ def bench_gemm(args) -> dict:
     S = args.splits or ops.gemm_tc_splits(M, N, K)
     odt = torch.float32 if args.out == "float32" else torch.bfloat16
     kernel = "gemm_tc"
-    if M > 128 and not args.dual and not args.pair and not args.single and (S == 1 or args.whole_tiles):
+    if (M > 128 and not args.dual and not args.pair and not args.single and (S == 1 or args.whole_tiles)) \
+            or args.persistent:
         # the persistent kernel; with --swiglu the rows of w alternate gate and up
         kernel = "gemm_tc_persistent"
         out = torch.empty(M, N // 2 if args.swiglu else N, device="cuda", dtype=odt)
@@ -345,6 +346,7 @@ def main(argv=None) -> int:
             s.add_argument("--dual", action="store_true", help="more than 64 rows: two weight tiles per CTA")
             s.add_argument("--pair", action="store_true", help="more than 64 rows: a pair of CTAs to a tile (cta_group::2)")
             s.add_argument("--single", action="store_true", help="more than 64 rows: one tile per CTA, not persistent")
+            s.add_argument("--persistent", action="store_true", help="the persistent kernel, whatever the plan says")
             s.add_argument("--whole-tiles", action="store_true",
                            help="persistent kernel: never share a tile's K among several CTAs")
             s.add_argument("--swiglu", action="store_true", help="w holds gate and up rows: fused gated activation")

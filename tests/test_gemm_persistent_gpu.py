@@ -13,7 +13,10 @@ def ops():
     return o
 
 
-SHAPES = [(65, 128, 64), (128, 384, 256), (200, 1000, 520), (257, 4096, 1024), (700, 18944, 128), (2048, 1536, 4096)]
+# the last three: whole rounds of tiles and a rest that is shared out along K (88 tiles of 384, 12 of 160),
+# and a rest of one tile
+SHAPES = [(65, 128, 64), (128, 384, 256), (200, 1000, 520), (257, 4096, 1024), (700, 18944, 128), (2048, 1536, 4096),
+          (2048, 6144, 512), (1100, 4000, 1024), (1000, 4800, 2048)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -31,7 +34,8 @@ def test_plain_product(ops, M, N, K, out_dtype, share):
     assert float((out.cpu().double() - ref).abs().max() / ref.abs().max()) < tol
 
 
-@pytest.mark.parametrize("M,I,K", [(65, 64, 64), (130, 333, 256), (513, 1409, 512), (2048, 2048, 1024)])
+@pytest.mark.parametrize("M,I,K", [(65, 64, 64), (130, 333, 256), (513, 1409, 512), (2048, 2048, 1024), (600, 3000, 2048),
+                                   (2048, 3072, 1024)])
 def test_gated_activation_over_alternating_rows(ops, M, I, K):
     g = torch.Generator().manual_seed(M + I + K)
     a = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
@@ -53,7 +57,8 @@ def test_shared_tiles_repeat_bit_for_bit_and_agree_with_whole_tiles(ops):
     The flags must be left ready for the next product, the sums must not depend on timing, and
     the result must agree with whole tiles."""
     g = torch.Generator().manual_seed(3)
-    for M, N, K, pairs in ((300, 2176, 4160, False), (576, 2048, 8192, False), (130, 512, 2048, True)):
+    for M, N, K, pairs in ((300, 2176, 4160, False), (576, 2048, 8192, False), (130, 512, 2048, True),
+                           (2048, 6144, 1024, False), (1100, 4000, 1024, True), (256, 6144, 4096, False)):
         a = (torch.randn(M, K, generator=g) * 0.5).bfloat16().cuda()
         w = (torch.randn(N, K, generator=g) * 0.5).bfloat16().cuda()
         n_out = N // 2 if pairs else N
