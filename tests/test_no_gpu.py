@@ -41,6 +41,7 @@ def test_plan_of_key_slices_for_decoding():
     from allpaca_b200.ops import decode_splits
     tma = dict(slots=296, cluster_sizes=(2, 4, 8, 16))
     assert decode_splits(64, 32, 8, 4096, **tma) == 1
+    assert decode_splits(128, 32, 8, 2048, **tma) == 1 and decode_splits(80, 32, 8, 2048, **tma) == 1
     assert decode_splits(8, 32, 8, 4096, **tma) == 4
     assert decode_splits(1, 32, 8, 4096, **tma) == 8
     assert decode_splits(1, 32, 8, 8192, **tma) == 16
