@@ -35,6 +35,9 @@ class GroupedQueryAttention(Mixer):
     #: rotation and cache store in the projection's epilogue for steps of few rows (a switch for
     #: measurements; the separate kernel gives the same results)
     FUSE_ROPE = True
+    #: rows up to which that pays (8B shape, 1024 keys: 1 % of the step at 24 and 32 rows, a loss of
+    #: 0.6 % at 64 and of 2 % at 128, where the epilogue's scattered stores hold the product up)
+    FUSE_ROPE_MAX_ROWS = 32
 
     def __init__(self, params, env: BuildEnv):
         super().__init__(params, env)
@@ -141,7 +144,7 @@ class GroupedQueryAttention(Mixer):
         q = ws.get("attn.q", (T, self.q_size), self.env.dtype)
         table = self.position.rotation_for(step) if self.position is not None else None
         writes = cache.writes and not self.shares_kv
-        if (self.FUSE_ROPE and T <= Linear.FUSED_MAX_ROWS and not self.shares_kv and self.qkv.fusable()
+        if (self.FUSE_ROPE and T <= self.FUSE_ROPE_MAX_ROWS and not self.shares_kv and self.qkv.fusable()
                 and (self.position is None or table is not None) and (table is None or table[1] == 1 or self._interleaved)):
             # few rows: rotation and the store of keys and values in the projection's epilogue
             cos_sin, pairing = table if table is not None else (None, 1)
