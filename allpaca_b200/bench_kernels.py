@@ -133,14 +133,24 @@ def bench_attention(args) -> dict:
             bufs[key] = torch.empty(shape, device="cuda", dtype=dtype)
         return bufs[key]
 
+    mean = C
+    if args.short_context:
+        # one long sequence among short ones
+        pos[1:] = args.short_context - 1
+        mean = (C + (B - 1) * args.short_context) // B
+        per = per * mean // C
+
     def fn(i):
         cache, table = caches[i % copies]
         ops.attention(q, out, cache, table, seq, pos, nh, nkv, hd, 1.0 / math.sqrt(hd), 0, seq_start=start,
-                      query_lens=[1] * B, max_context=C, scratch=scratch, use_tma=not args.cp_async)
+                      query_lens=[1] * B, max_context=C, scratch=scratch, use_tma=not args.cp_async,
+                      mean_context=0 if args.plan_by_longest else mean)
     us = _time(fn, args.iters, args.warmup, not args.no_graph)
     return {"kernel": "attention_split+merge" if args.cp_async else "attention_split_tma+merge", "batch": B, "context": C, "heads": nh, "kv_heads": nkv,
-            "head_dim": hd, "splits": ops.decode_splits(B, nh, nkv, C, slots=444 if args.cp_async else 296,
-                                        cluster_sizes=() if args.cp_async else (2, 4, 8, 16)),
+            "head_dim": hd, "mean_context": mean,
+            "splits": ops.decode_splits(B, nh, nkv, C, slots=444 if args.cp_async else 296,
+                                        cluster_sizes=() if args.cp_async else (2, 4, 8, 16),
+                                        mean_context=0 if args.plan_by_longest else mean),
             "us": round(us, 2),
             "GBps": round(per / us / 1e3, 1)}
 
@@ -361,6 +371,10 @@ def main(argv=None) -> int:
             s.add_argument("--context", type=int, default=4096)
             s.add_argument("--tokens", type=int, default=2048)
             s.add_argument("--cp-async", action="store_true", help="decode: the cp.async kernel instead of the TMA one")
+            s.add_argument("--short-context", type=int, default=0,
+                           help="decode: every sequence but the first holds this many keys (0: all hold --context)")
+            s.add_argument("--plan-by-longest", action="store_true",
+                           help="decode: plan the key slices as if every sequence were as long as the longest")
             s.add_argument("--splits", type=int, default=0, help="key slices (0: the kernel's own plan)")
             s.add_argument("--mma-sync", action="store_true", help="prompt attention with the mma.sync tile kernel")
             s.add_argument("--query-tiles", choices=["auto", "one", "two"], default="auto",

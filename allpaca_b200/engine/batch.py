@@ -47,3 +47,4 @@ class StepBatch:
     shared: dict = field(default_factory=dict)    # per-step values parts share (cleared per forward)
     max_query_len: int = 0
     max_context_len: int = 0
+    mean_context_len: int = 0         # of the sequences that bring one row (0: not known, taken as the longest)

@@ -147,17 +147,24 @@ class ModelRunner:
         B = len(entries)
         # the number of key slices of the attention kernel is part of the graph: graphs are kept
         # per power-of-two bound on the longest context, so it suits the contexts it serves
-        longest = max(self.cache.num_tokens(en.request) if self.cache.has(en.request) else 0
-                      for en in entries) + 1
+        held = [self.cache.num_tokens(en.request) if self.cache.has(en.request) else 0 for en in entries]
+        longest = max(held) + 1
         bound = 256
         while bound < longest:
             bound *= 2
         bound = min(bound, max(self.max_model_len, 256))
-        gs = self._graphs.get((B, bound))
+        # ... and per power-of-two bound on the average context, where that lies below the longest:
+        # sequences of unequal length want more slices than their number alone suggests
+        mean_bound = 256
+        while mean_bound < sum(held) // B + 1:
+            mean_bound *= 2
+        mean_bound = min(mean_bound, bound)
+        gs = self._graphs.get((B, bound, mean_bound))
         if gs is None:
-            gs = self._graphs[(B, bound)] = _DecodeGraph(self, B)
+            gs = self._graphs[(B, bound, mean_bound)] = _DecodeGraph(self, B)
         batch = self.prepare(entries, staging=gs, widths=gs.widths, device_tokens=device_tokens)
         batch.max_context_len = bound
+        batch.mean_context_len = mean_bound
         if gs.graph is not None and gs.generation == self.workspace.generation:
             gs.graph.replay()
             self.graph_replays += 1
@@ -227,7 +234,14 @@ class ModelRunner:
             block_tables=tables,
             host_seq_start=tok_off, host_first_position=firsts,
             host_query_lens=lens, host_state_slots=slots,
-            max_query_len=int(layout.max_query_len), max_context_len=int(layout.max_context_len))
+            max_query_len=int(layout.max_query_len), max_context_len=int(layout.max_context_len),
+            mean_context_len=self._mean_decode_context(firsts, lens))
+
+    @staticmethod
+    def _mean_decode_context(firsts, lens) -> int:
+        """Average number of keys of the sequences that bring one row (0: there are none)."""
+        ones = [f + 1 for f, n in zip(firsts, lens) if n == 1]
+        return sum(ones) // len(ones) if ones else 0
 
     def _staging(self, n: int):
         if n > self._staging_cap:

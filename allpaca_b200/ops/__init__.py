@@ -430,7 +430,7 @@ def gemm_tc_persistent(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pair
 
 
 def _decode_attention(lib, q, out, cache_layer, block_table, positions, rows, num_heads, num_kv_heads, head_dim, P,
-                      scale, window, max_context, scratch, use_tma) -> None:
+                      scale, window, max_context, scratch, use_tma, mean_context=0) -> None:
     """The first ``rows`` rows of the batch, one per sequence: the split kernels."""
     tma = (use_tma and hasattr(lib, "ap_attention_decode_tma")
            and bool(lib.ap_attention_decode_tma_supports(num_heads, num_kv_heads, head_dim, P))
@@ -443,7 +443,8 @@ def _decode_attention(lib, q, out, cache_layer, block_table, positions, rows, nu
     slots = 444
     if tma:
         slots = int(lib.ap_attention_decode_tma_slots()) if hasattr(lib, "ap_attention_decode_tma_slots") else 296
-    nsplit = decode_splits(rows, num_heads, num_kv_heads, max_context, window, slots=slots, cluster_sizes=sizes)
+    nsplit = decode_splits(rows, num_heads, num_kv_heads, max_context, window, slots=slots, cluster_sizes=sizes,
+                           mean_context=mean_context)
     po = pm = 0
     needs_scratch = nsplit > 1 and not (tma and lib.ap_attention_decode_tma_in_cluster(num_heads, num_kv_heads, nsplit))
     if needs_scratch:
@@ -515,7 +516,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
               window: int = 0, seq_start: Optional[torch.Tensor] = None,
               query_lens: Optional[Sequence[int]] = None, max_context: int = 0,
               scratch=None, use_tcgen05: bool = True, use_tma: bool = True,
-              wide: Optional[bool] = None) -> None:
+              wide: Optional[bool] = None, mean_context: int = 0) -> None:
     """Causal attention of every row of ``q [T, nh*hd]`` over its sequence's cached keys.
 
     float32 runs the general CUDA-core kernel (the true 32-bit path).  bfloat16 runs on the
@@ -524,7 +525,9 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
     the shapes it takes, a tcgen05 kernel (``use_tcgen05``; ``wide`` picks the one with two query
     tiles to a CTA, ``None`` by the number of CTAs), and otherwise the tile kernel.
     ``scratch(name, shape, dtype)`` supplies the partial-result buffers of the split kernel
-    where its key slices are not combined inside a thread-block cluster.
+    where its key slices are not combined inside a thread-block cluster.  ``max_context`` and
+    ``mean_context`` (0: all alike) are bounds on the longest and the average number of keys of
+    the one-row sequences, from which the number of key slices is planned.
     """
     _check(q, "q", dims=2)
     _check(out, "out", q.dtype, 2)
@@ -554,7 +557,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
             nd += 1
         if nd > 0:
             _decode_attention(lib, q, out, cache_layer, block_table, positions, nd, num_heads, num_kv_heads,
-                              head_dim, P, scale, window, max_context, scratch, use_tma)
+                              head_dim, P, scale, window, max_context, scratch, use_tma, mean_context)
         if nd < nseq:
             _prompt_attention(lib, q, out, cache_layer, block_table, seq_start, positions, nd, query_lens[nd:], T,
                               num_heads, num_kv_heads, head_dim, P, scale, window, use_tcgen05, wide)
@@ -566,15 +569,18 @@ def attention(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
 
 
 def decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: int, window: int = 0,
-                  slots: int = 444, cluster_sizes: Sequence[int] = ()) -> int:
+                  slots: int = 444, cluster_sizes: Sequence[int] = (), mean_context: int = 0) -> int:
     """Key slices for the split kernels (see :func:`_decode_splits`; results are remembered)."""
+    mean = int(mean_context or 0)
+    if mean <= 0 or mean > max_context:
+        mean = int(max_context)
     return _decode_splits(int(rows), int(num_heads), int(num_kv_heads), int(max_context), int(window or 0),
-                          int(slots), tuple(cluster_sizes))
+                          int(slots), tuple(cluster_sizes), mean)
 
 
 @functools.lru_cache(maxsize=4096)
 def _decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: int, window: int,
-                   slots: int, cluster_sizes: tuple) -> int:
+                   slots: int, cluster_sizes: tuple, mean_context: int = 0) -> int:
     """Key slices for the split kernels.
 
     The cp.async kernel runs three CTAs per SM (``slots`` 444), the one fed by TMA two (296).
@@ -586,12 +592,32 @@ def _decode_splits(rows: int, num_heads: int, num_kv_heads: int, max_context: in
     only a few at a time (one or two to a GPC): they are considered for up to 8 of them, at the
     price of three tiles (one sequence of 32768 keys: 48 -> 33 us; two such sequences are slower
     with 16 slices than with 8).
+
+    Sequences of unequal length (``mean_context`` below three quarters of ``max_context``): a
+    row's keys are cut into the slices whatever their number, so the longest row sets the time
+    of the slowest CTA, ``longest tiles / slices + 4``, while all CTAs together have
+    ``CTAs * (mean tiles + 4 * slices)`` to walk; the larger of the two (the second spread over
+    the slots) is minimised instead.  One sequence of 32768 keys among 31 short ones is then cut
+    into 8 or 16 slices instead of being walked by one CTA per KV head.
     """
     reps = num_heads // num_kv_heads
     chunks = -(-reps // min(reps, 16))
     ctas = max(1, rows * num_kv_heads * chunks)
     keys = max_context if not window else min(max_context, window)
     tiles = max(1, -(-max(keys, 1) // 64))
+    mean_keys = mean_context if mean_context > 0 else max_context
+    if window:
+        mean_keys = min(mean_keys, window)
+    if mean_keys * 4 < keys * 3:
+        mean_tiles = max(1.0, mean_keys / 64.0)
+        best, best_cost = 1, None
+        for ns in ([1] + [n for n in (cluster_sizes or (2, 4, 8)) if n <= tiles]):
+            cost = max(-(-tiles // ns) + 4, ctas * (mean_tiles + 4 * ns) / slots) + 0.15 * ns
+            if ns > 8:
+                cost += 3
+            if best_cost is None or cost < best_cost - 1e-9:
+                best, best_cost = ns, cost
+        return best
     if ctas >= 2 * slots:
         # several rounds of CTAs even without slices: they follow one another without gaps, which
         # the whole waves of the rule below do not know (batch 128 at 2048 keys: 165 us whole, 188 in two)

@@ -145,9 +145,10 @@ def test_long_decoding_stays_on_the_plain_logits(tmp_path, dtype):
         err = abs(row - plain[i]).max() / abs(plain[i]).max()
         assert err <= helpers.TOL[dtype], (i, err)
     # these steps were replayed graphs (all but the first few of each bound on the context), and
-    # crossing 256 tokens recorded a second graph for the same batch size
+    # crossing 256 tokens recorded a second graph for the same batch size (keys: rows, bound on
+    # the longest context, bound on the average context)
     recorded = sorted(key for key, g in runner._graphs.items() if g.graph is not None)
-    assert recorded == [(1, 256), (1, 512)], recorded
+    assert recorded == [(1, 256, 256), (1, 512, 512)], recorded
     assert runner.graph_replays >= 390
 
 

@@ -42,6 +42,10 @@ def test_plan_of_key_slices_for_decoding():
     tma = dict(slots=296, cluster_sizes=(2, 4, 8, 16))
     assert decode_splits(64, 32, 8, 4096, **tma) == 1
     assert decode_splits(128, 32, 8, 2048, **tma) == 1 and decode_splits(80, 32, 8, 2048, **tma) == 1
+    # sequences of unequal length: the longest sets the slowest CTA's time, so it is cut finer
+    assert decode_splits(8, 32, 8, 32768, **tma) == 4 and decode_splits(8, 32, 8, 32768, mean_context=4500, **tma) == 16
+    assert decode_splits(128, 32, 8, 16384, **tma) == 1 and decode_splits(128, 32, 8, 16384, mean_context=600, **tma) == 4
+    assert decode_splits(8, 32, 8, 4096, mean_context=3500, **tma) == decode_splits(8, 32, 8, 4096, **tma)
     assert decode_splits(8, 32, 8, 4096, **tma) == 4
     assert decode_splits(1, 32, 8, 4096, **tma) == 8
     assert decode_splits(1, 32, 8, 8192, **tma) == 16
