@@ -47,4 +47,7 @@ class StepBatch:
     shared: dict = field(default_factory=dict)    # per-step values parts share (cleared per forward)
     max_query_len: int = 0
     max_context_len: int = 0
-    mean_context_len: int = 0         # of the sequences that bring one row (0: not known, taken as the longest)
+    # of the sequences that bring one row, whose attention is cut into key slices by these two
+    # (0: not known; the longest context of all stands in)
+    max_decode_context_len: int = 0
+    mean_context_len: int = 0

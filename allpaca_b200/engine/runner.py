@@ -163,7 +163,7 @@ class ModelRunner:
         if gs is None:
             gs = self._graphs[(B, bound, mean_bound)] = _DecodeGraph(self, B)
         batch = self.prepare(entries, staging=gs, widths=gs.widths, device_tokens=device_tokens)
-        batch.max_context_len = bound
+        batch.max_context_len = batch.max_decode_context_len = bound
         batch.mean_context_len = mean_bound
         if gs.graph is not None and gs.generation == self.workspace.generation:
             gs.graph.replay()
@@ -235,13 +235,15 @@ class ModelRunner:
             host_seq_start=tok_off, host_first_position=firsts,
             host_query_lens=lens, host_state_slots=slots,
             max_query_len=int(layout.max_query_len), max_context_len=int(layout.max_context_len),
-            mean_context_len=self._mean_decode_context(firsts, lens))
+            **self._decode_contexts(firsts, lens))
 
     @staticmethod
-    def _mean_decode_context(firsts, lens) -> int:
-        """Average number of keys of the sequences that bring one row (0: there are none)."""
+    def _decode_contexts(firsts, lens) -> dict:
+        """Longest and average number of keys of the sequences that bring one row."""
         ones = [f + 1 for f, n in zip(firsts, lens) if n == 1]
-        return sum(ones) // len(ones) if ones else 0
+        if not ones:
+            return {}
+        return {"max_decode_context_len": max(ones), "mean_context_len": sum(ones) // len(ones)}
 
     def _staging(self, n: int):
         if n > self._staging_cap:

@@ -174,7 +174,8 @@ class GroupedQueryAttention(Mixer):
         ops.attention(q, attn, cache.pages, step.block_tables[cache.group], step.token_seq,
                       step.positions, self.nh, self.nkv, self.hd, self.scale,
                       self.window or 0, seq_start=step.seq_start, query_lens=step.host_query_lens,
-                      max_context=step.max_context_len, scratch=ws.get, mean_context=step.mean_context_len)
+                      max_context=step.max_decode_context_len or step.max_context_len, scratch=ws.get,
+                      mean_context=step.mean_context_len)
         return attn
 
     def _materialise(self, qkv: torch.Tensor, T: int) -> torch.Tensor:
