@@ -1407,7 +1407,6 @@ AP_EXPORT int ap_gemm_tc_persistent(const void* a, const void* w, void* out, int
 // tiles fill the last round of SMs badly while the kernel with two weight tiles per CTA
 // covers the whole product in a single, well-filled wave.
 AP_EXPORT int ap_gemm_tc_prefers_persistent(int M, int N, int K) {
-    (void)K;
     // up to 128 rows every weight tile is one CTA of the kernel above, two to an SM, all resident
     // at once: they stream the weight at one rate, where tiles dealt out to one CTA per SM leave
     // the SMs with one tile fewer idle (8B gate+up at 128 rows: 48 against 59 us)
@@ -1418,7 +1417,13 @@ AP_EXPORT int ap_gemm_tc_prefers_persistent(int M, int N, int K) {
     const long long rounds = (tiles + 147) / 148;
     const bool badly_filled = tiles * 100 < rounds * 148 * 90;
     const bool dual_one_wave = dual <= 148 && dual >= 118;
-    return (badly_filled && dual_one_wave && rounds <= 2) ? 0 : 1;
+    if (badly_filled && dual_one_wave && rounds <= 2) return 0;
+    // A long K: a wave of two-tile CTAs takes 1.8 times a round of single tiles (its epilogue is
+    // paid once per two tiles and its two accumulators hide some of the instruction's latency;
+    // at K = 4096 it is 2.0 and nothing is gained).  4096 x 4096 x 14336: 353 against 392 us.
+    const long long waves = (dual + 147) / 148;
+    if (K >= 8192 && waves * 180 < rounds * 100) return 0;
+    return 1;
 }
 
 // 0 when every tensor-core product so far ran to its end; else the code of the wait that
