@@ -18,7 +18,7 @@ A step is one decode step of the whole batch.
               power cap pulls the clock down), and the fractions of the bf16 peak their FLOPs reach;
 * ``roofline`` bytes a decode step must read (every weight once, the cache of the live
               requests) over its time, against the measured HBM copy rate;
-* ``points``  decode at batch 1 and 64, and at batch 8 of the other benchmark shapes
+* ``points``  decode at batch 1, 64 and 128, and at batch 8 of the other benchmark shapes
               (``--no-presets`` leaves those out), each with its fraction of the copy rate;
 * ``clocks``  SM clocks and throttle reasons sampled by nvidia-smi across the timed regions.
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from the fallback
@@ -289,7 +289,7 @@ def main() -> int:
 
     from allpaca_b200 import ops
     pk = peaks()
-    max_batch = args.batch if args.no_points else max(args.batch, 64)
+    max_batch = args.batch if args.no_points else max(args.batch, 128)
     bench = Workbench(args.preset, args.layers, args, max_batch)
     cfg, layers = bench.cfg, bench.layers
     if args.prefill_only:
@@ -330,7 +330,7 @@ def main() -> int:
                              "of": pk["source"]}
         points = {}
         side_steps = max(8, min(args.steps // 4, 64))
-        for b in (1, 64):
+        for b in (1, 64, 128):
             v, bms, _, _, _, _, _ = bench.decode_run(b, side_steps, 3)
             points[f"decode_b{b}"] = round(v, 2)
             points[f"decode_b{b}_hbm_frac"] = round(bench.step_bytes(b, side_steps) / (bms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
