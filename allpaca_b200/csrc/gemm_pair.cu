@@ -14,8 +14,11 @@
 // so that pairs running side by side share weight tiles in L2.
 //
 // Roles in each CTA: warp 0 = TMA producer for this CTA's halves; warp 1 = in the first CTA
-// the MMA issuer, in the second the relay that tells the first CTA when a stage of the second
-// has landed (a TMA load signals a barrier of its own CTA only); warps 2..5 = epilogue.
+// the MMA issuer (idle in the second); warps 2..5 = epilogue.  The loads of both CTAs are
+// counted on the first CTA's barrier of the stage: the second CTA issues its loads with
+// .cta_group::2 and that barrier's address (no multicast: the data goes to the issuing CTA
+// only), and the first CTA expects the bytes of both.  (A relay thread in the second CTA,
+// forwarding "my stage has landed" by a remote arrival, cost 5 to 12 % of the product's time.)
 // A stage is freed, and an accumulator handed to the epilogue, in both CTAs at once by
 // tcgen05.commit with a multicast arrival.
 //
@@ -55,8 +58,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     uint8_t* a_tiles = smem + PAIR_STAGES * PAIR_W_BYTES;
     uint64_t* full = (uint64_t*)(smem + PAIR_STAGES * PAIR_STAGE_BYTES);
     uint64_t* empty = full + PAIR_STAGES;
-    uint64_t* peer_full = empty + PAIR_STAGES;       // first CTA: the second CTA's stage has landed
-    uint64_t* acc_full = peer_full + PAIR_STAGES;    // [2]
+    uint64_t* acc_full = empty + PAIR_STAGES;        // [2]
     uint64_t* acc_empty = acc_full + 2;              // [2], first CTA: both CTAs' epilogues are done with it
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     uint32_t* peer_tmem = tmem_slot + 1;             // first CTA: where the second CTA's tensor memory starts
@@ -75,7 +77,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         for (int s = 0; s < PAIR_STAGES; ++s) {
             tc::mbar_init(&full[s], 1);
             tc::mbar_init(&empty[s], 1);
-            tc::mbar_init(&peer_full[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             tc::mbar_init(&acc_full[b], 1);
@@ -122,12 +123,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                     first = false;
                     const int pre = min(PAIR_STAGES, nkb);
                     for (int i = 0; i < pre; ++i) {
-                        tc::mbar_expect_tx(&full[i], stage_bytes);
-                        tc::tma_load_2d(w_tiles + i * PAIR_W_BYTES, &tmap_w, i * PAIR_TILE_K, n0, &full[i]);
+                        if (rank == 0) {
+                            tc::mbar_expect_tx(&full[i], 2 * stage_bytes);       // both CTAs' halves
+                            tc::tma_load_2d(w_tiles + i * PAIR_W_BYTES, &tmap_w, i * PAIR_TILE_K, n0, &full[i]);
+                        } else {
+                            tc::tma_load_2d_signal_peer(w_tiles + i * PAIR_W_BYTES, &tmap_w, i * PAIR_TILE_K, n0,
+                                                        tc::map_to_rank(tc::smem_addr(&full[i]), 0u));
+                        }
                     }
                     ap_pdl_wait();
-                    for (int i = 0; i < pre; ++i)
-                        tc::tma_load_2d(a_tiles + i * PAIR_A_BYTES, &tmap_a, i * PAIR_TILE_K, m0, &full[i]);
+                    for (int i = 0; i < pre; ++i) {
+                        if (rank == 0)
+                            tc::tma_load_2d(a_tiles + i * PAIR_A_BYTES, &tmap_a, i * PAIR_TILE_K, m0, &full[i]);
+                        else
+                            tc::tma_load_2d_signal_peer(a_tiles + i * PAIR_A_BYTES, &tmap_a, i * PAIR_TILE_K, m0,
+                                                        tc::map_to_rank(tc::smem_addr(&full[i]), 0u));
+                    }
                     kb = pre;
                     idx = issued = pre;
                 }
@@ -140,9 +151,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                         atomicCAS(&g_pair_status, 0, PAIR_ERR_EMPTY);
                         break;
                     }
-                    tc::mbar_expect_tx(&full[s], stage_bytes);
-                    tc::tma_load_2d(w_tiles + s * PAIR_W_BYTES, &tmap_w, kb * PAIR_TILE_K, n0, &full[s]);
-                    tc::tma_load_2d(a_tiles + s * PAIR_A_BYTES, &tmap_a, kb * PAIR_TILE_K, m0, &full[s]);
+                    if (rank == 0) {
+                        tc::mbar_expect_tx(&full[s], 2 * stage_bytes);
+                        tc::tma_load_2d(w_tiles + s * PAIR_W_BYTES, &tmap_w, kb * PAIR_TILE_K, n0, &full[s]);
+                        tc::tma_load_2d(a_tiles + s * PAIR_A_BYTES, &tmap_a, kb * PAIR_TILE_K, m0, &full[s]);
+                    } else {
+                        const uint32_t leader = tc::map_to_rank(tc::smem_addr(&full[s]), 0u);
+                        tc::tma_load_2d_signal_peer(w_tiles + s * PAIR_W_BYTES, &tmap_w, kb * PAIR_TILE_K, n0, leader);
+                        tc::tma_load_2d_signal_peer(a_tiles + s * PAIR_A_BYTES, &tmap_a, kb * PAIR_TILE_K, m0, leader);
+                    }
                     issued = idx + 1;
                 }
             }
@@ -160,29 +177,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                     }
                 }
             }
-            if (*abort_flag) {
-                // let the loads that are still in flight land before the CTA's memory goes away
+            if (*abort_flag && rank == 0) {
+                // let the loads that are still in flight (of both CTAs: all are counted here) land before
+                // the CTAs' memory goes away; the second CTA leaves after the cluster barrier at the end
                 for (long long i = max(0LL, issued - PAIR_STAGES); i < issued; ++i)
                     tc::mbar_wait(&full[i % PAIR_STAGES], (uint32_t)((i / PAIR_STAGES) & 1), 200000000LL);
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && rank == 1) {
-            // relay: a stage of this CTA has landed -> one arrival on the first CTA's peer_full
-            long long idx = 0;
-            for (int tile = pair; tile < tiles_total && !*abort_flag; tile += pairs_in_grid) {
-                for (int kb = 0; kb < nkb; ++kb, ++idx) {
-                    const int s = (int)(idx % PAIR_STAGES);
-                    const uint32_t ph = (uint32_t)((idx / PAIR_STAGES) & 1);
-                    if (*abort_flag) break;
-                    if (!tc::mbar_wait(&full[s], ph)) {
-                        *abort_flag = 1;
-                        atomicCAS(&g_pair_status, 0, PAIR_ERR_FULL);
-                        break;
-                    }
-                    tc::mbar_arrive_remote(tc::map_to_rank(tc::smem_addr(&peer_full[s]), 0u));
-                }
-            }
+        if (rank == 1) {
+            // (the second CTA's tensor cores are driven from the first)
         } else if (lane == 0) {
             const uint32_t idesc = tc::instr_desc_bf16_f32(2 * PAIR_TILE_W, bn);
             bool ok = true;
@@ -205,7 +209,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                     const int s = (int)(idx % PAIR_STAGES);
                     const uint32_t ph = (uint32_t)((idx / PAIR_STAGES) & 1);
                     if (*abort_flag) { ok = false; break; }
-                    if (!tc::mbar_wait(&full[s], ph) || !tc::mbar_wait(&peer_full[s], ph)) {
+                    if (!tc::mbar_wait(&full[s], ph)) {             // both CTAs' halves of the stage have landed
                         *abort_flag = 1;
                         atomicCAS(&g_pair_status, 0, PAIR_ERR_FULL);
                         ok = false;
@@ -404,6 +408,22 @@ AP_EXPORT int ap_gemm_tc_pair(const void* a, const void* w, void* out, int out_d
     }
     return out_dtype == AP_F32 ? launch_pair<float, false>(mw, ma, out, M, N, K, ldc, bn, tiles_m, stream)
                                : launch_pair<bf16, false>(mw, ma, out, M, N, K, ldc, bn, tiles_m, stream);
+}
+
+// Whether this kernel is the one to use for a product of many rows.  Measured against the
+// persistent kernel (one SM to a tile of 128 x 256, which takes in 48 KB per block of K where a
+// CTA of a pair takes 32 KB) it is 3 to 12 % faster from 256 rows on, with two exceptions that the
+// caller's other rules cover: few tiles of a long K, which the persistent kernel shares out
+// along K (512 x 4096 x 14336: 76 against 80 us), and products for which the kernel with two
+// weight tiles to a CTA is chosen (2048 x 4096 x 14336: 173 against 184 us).
+extern "C" int ap_gemm_tc_prefers_persistent(int M, int N, int K);
+AP_EXPORT int ap_gemm_tc_prefers_pair(int M, int N, int K) {
+    if (M < 256 || N <= 0 || K <= 0 || K % 8) return 0;
+    if (!ap_gemm_tc_prefers_persistent(M, N, K)) return 0;            // the two-tile kernel's cases
+    const long long tiles = (long long)((N + PAIR_TILE_W - 1) / PAIR_TILE_W) * ((M + PAIR_MAX_BN - 1) / PAIR_MAX_BN);
+    const int nkb = (K + PAIR_TILE_K - 1) / PAIR_TILE_K;
+    if (tiles * 2 <= 148 && nkb >= 96) return 0;                      // shared out along K instead
+    return 1;
 }
 
 // 0 when every product on pairs of SMs so far ran to its end; else the code of the wait that

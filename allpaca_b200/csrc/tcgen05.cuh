@@ -89,6 +89,16 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         ::"r"(smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
         : "memory");
 }
+// The same load issued by a CTA of a pair (cta_group::2) whose completion is counted on a
+// barrier of the pair's other CTA: `bar_cluster_addr` is that barrier's address in the
+// cluster's shared window (map_to_rank).  No multicast: the data goes to this CTA only.
+__device__ __forceinline__ void tma_load_2d_signal_peer(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                        uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z,
                                             uint64_t* bar) {
     asm volatile(

@@ -680,6 +680,12 @@ def gemm_tc_prefers_dual(M: int, N: int, K: int) -> bool:
     return hasattr(lib, "ap_gemm_tc_prefers_dual") and bool(lib.ap_gemm_tc_prefers_dual(int(M), int(N), int(K)))
 
 
+def gemm_tc_prefers_pair(M: int, N: int, K: int) -> bool:
+    """Whether the kernel that pairs two SMs on a tile is the faster one for this shape (256 rows and more)."""
+    lib = core()
+    return hasattr(lib, "ap_gemm_tc_prefers_pair") and bool(lib.ap_gemm_tc_prefers_pair(int(M), int(N), int(K)))
+
+
 def gemm_tc_prefers_persistent(M: int, N: int, K: int) -> bool:
     """Whether the persistent kernel is the faster one for this shape (more than 64 rows)."""
     lib = core()

@@ -53,6 +53,7 @@ _OPTIONAL_CORE_SIGNATURES = {
     "ap_gemm_tc_persistent": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P, _L, _P],
     "ap_gemm_tc_plan": [_I, _I, _I],
     "ap_gemm_tc_prefers_dual": [_I, _I, _I],
+    "ap_gemm_tc_prefers_pair": [_I, _I, _I],
     "ap_gemm_tc_prefers_persistent": [_I, _I, _I],
     "ap_gemm_tc_status": [],
     "ap_gemm_tc_reset_status": [],

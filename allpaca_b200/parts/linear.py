@@ -101,6 +101,8 @@ class Linear:
         if tc and T > 64 and nsplit > 1:
             # up to 256 rows against few weight tiles: K slices in a cluster, as for decoding
             ops.gemm_tc(a, self.weight, target, nsplit, reduce=True)
+        elif tc and ops.gemm_tc_prefers_pair(T, N, self.in_features):
+            ops.gemm_tc_pair(a, self.weight, target)
         elif tc and T > 64 and ops.gemm_tc_prefers_persistent(T, N, self.in_features):
             ops.gemm_tc_persistent(a, self.weight, target)
         elif tc and nsplit == 1 and ops.gemm_tc_prefers_dual(T, N, self.in_features):
@@ -128,7 +130,10 @@ class Linear:
         if T > 128 and nsplit == 1:
             if scale is not None:
                 raise ValueError("a scale of the rows is only applied by the tensor-core kernel for few rows")
-            ops.gemm_tc_persistent(a, self.weight, out, pairs=True)
+            if ops.gemm_tc_prefers_pair(T, self.out_features, self.in_features):
+                ops.gemm_tc_pair(a, self.weight, out, pairs=True)
+            else:
+                ops.gemm_tc_persistent(a, self.weight, out, pairs=True)
         else:
             ops.gemm_tc(a, self.weight, out, nsplit, reduce=nsplit > 1, pairs=True, scale=scale)
         return out
