@@ -412,7 +412,7 @@ AP_EXPORT int ap_gemm_tc_pair(const void* a, const void* w, void* out, int out_d
 
 // Whether this kernel is the one to use for a product of many rows.  Measured against the
 // persistent kernel (one SM to a tile of 128 x 256, which takes in 48 KB per block of K where a
-// CTA of a pair takes 32 KB) it is 3 to 12 % faster from 256 rows on, with two exceptions that the
+// CTA of a pair takes 32 KB) it is 3 to 12 % faster from 256 rows on, with three exceptions, two of which the
 // caller's other rules cover: few tiles of a long K, which the persistent kernel shares out
 // along K (512 x 4096 x 14336: 76 against 80 us), and products for which the kernel with two
 // weight tiles to a CTA is chosen (2048 x 4096 x 14336: 173 against 184 us).
@@ -423,6 +423,10 @@ AP_EXPORT int ap_gemm_tc_prefers_pair(int M, int N, int K) {
     const long long tiles = (long long)((N + PAIR_TILE_W - 1) / PAIR_TILE_W) * ((M + PAIR_MAX_BN - 1) / PAIR_MAX_BN);
     const int nkb = (K + PAIR_TILE_K - 1) / PAIR_TILE_K;
     if (tiles * 2 <= 148 && nkb >= 96) return 0;                      // shared out along K instead
+    // fewer tiles of 256 x 256 than keep about half of the 74 pairs busy: one SM to a tile of 128 x 256
+    // puts as many SMs to work and is the faster (256 x 6144 x 4096: 28.4 against 30.6 us)
+    const long long pair_tiles = (long long)((N + 2 * PAIR_TILE_W - 1) / (2 * PAIR_TILE_W)) * ((M + PAIR_MAX_BN - 1) / PAIR_MAX_BN);
+    if (pair_tiles < 40) return 0;
     return 1;
 }
 
