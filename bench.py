@@ -235,7 +235,8 @@ class Workbench:
         return 2.0 * self.linear_elems + batch * ctx_mid * self.kv_per_token
 
     def prefill_run(self, tokens_n):
-        """(best ms, median ms, flops) of five prompts of ``tokens_n`` tokens, after one that warms up."""
+        """(best ms, median ms, flops) of five prompts of ``tokens_n`` tokens, after one that warms up and a
+        second of rest."""
         torch, runner, cfg = self.torch, self.runner, self.cfg
         from allpaca_b200.engine.batch import BatchEntry
         times = []
@@ -249,6 +250,12 @@ class Workbench:
             torch.cuda.synchronize()
             runner.finish(("prefill", i))
             times.append(round(start.elapsed_time(stop), 3))
+            if i == 0:
+                # the GPU comes here from the decode runs at the clock the power cap left it: a second of
+                # rest, so that the first timed run shows the burst clock (the peak it is set against is a
+                # burst figure too); the five runs follow one another at once, and their median shows
+                # what the power cap allows in the long run
+                time.sleep(1.0)
         print(f"[bench] prefill of {tokens_n} tokens, ms per run (the first warms up): {times}", file=sys.stderr, flush=True)
         flops = 2.0 * tokens_n * self.layers * self.per_layer + 2.0 * cfg.vocab_size * cfg.hidden_size \
             + self.layers * 4.0 * cfg.q_size * tokens_n * (tokens_n + 1) / 2
