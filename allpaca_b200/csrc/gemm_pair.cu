@@ -412,13 +412,13 @@ AP_EXPORT int ap_gemm_tc_pair(const void* a, const void* w, void* out, int out_d
 
 // Whether this kernel is the one to use for a product of many rows.  Measured against the
 // persistent kernel (one SM to a tile of 128 x 256, which takes in 48 KB per block of K where a
-// CTA of a pair takes 32 KB) it is 3 to 12 % faster from 256 rows on, with three exceptions, two of which the
+// CTA of a pair takes 32 KB) it is 3 to 12 % faster from 129 rows on, with three exceptions, two of which the
 // caller's other rules cover: few tiles of a long K, which the persistent kernel shares out
 // along K (512 x 4096 x 14336: 76 against 80 us), and products for which the kernel with two
 // weight tiles to a CTA is chosen (2048 x 4096 x 14336: 173 against 184 us).
 extern "C" int ap_gemm_tc_prefers_persistent(int M, int N, int K);
 AP_EXPORT int ap_gemm_tc_prefers_pair(int M, int N, int K) {
-    if (M < 256 || N <= 0 || K <= 0 || K % 8) return 0;
+    if (M <= 128 || N <= 0 || K <= 0 || K % 8) return 0;               // (160 x 28672 x 4096: 59 against 62 us)
     if (!ap_gemm_tc_prefers_persistent(M, N, K)) return 0;            // the two-tile kernel's cases
     const long long tiles = (long long)((N + PAIR_TILE_W - 1) / PAIR_TILE_W) * ((M + PAIR_MAX_BN - 1) / PAIR_MAX_BN);
     const int nkb = (K + PAIR_TILE_K - 1) / PAIR_TILE_K;

@@ -681,7 +681,7 @@ def gemm_tc_prefers_dual(M: int, N: int, K: int) -> bool:
 
 
 def gemm_tc_prefers_pair(M: int, N: int, K: int) -> bool:
-    """Whether the kernel that pairs two SMs on a tile is the faster one for this shape (256 rows and more)."""
+    """Whether the kernel that pairs two SMs on a tile is the faster one for this shape (more than 128 rows)."""
     lib = core()
     return hasattr(lib, "ap_gemm_tc_prefers_pair") and bool(lib.ap_gemm_tc_prefers_pair(int(M), int(N), int(K)))
 
