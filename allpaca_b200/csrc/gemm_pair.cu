@@ -44,14 +44,54 @@
 #define PAIR_ERR_ACCUM 3
 #define PAIR_ERR_TMEM 4
 
+#define PAIR_ERR_PEER 5
+#define PAIR_MAX_CTAS 256                                   // flags at the head of the scratch buffer
+#define PAIR_PARTIAL_FLOATS ((long long)PAIR_TILE_W * PAIR_MAX_BN)   // per CTA: [token][weight row]
+#define PAIR_MAX_SPLIT 4
+
 static __device__ int g_pair_status;
+
+// A pair's next piece of work: blocks [kb0, kb1) of K of one tile.  split == 1: whole tiles
+// pair, pair + pairs, ...  split > 1 (the grid holds tiles * split pairs): pair g takes range
+// g / tiles of tile g % tiles, and the pair of range 0 finishes the tile with what the others
+// hand over in global memory.
+struct PairWork { int tile, kb0, kb1, range; };
+__device__ __forceinline__ bool pair_next(int& it, int pair, int pairs_in_grid, int tiles_total, int nkb, int split,
+                                          PairWork& w) {
+    if (split > 1) {
+        if (it > 0 || pair >= tiles_total * split) return false;
+        it = 1;
+        w.range = pair / tiles_total;
+        w.tile = pair - w.range * tiles_total;
+        w.kb0 = (int)((long long)nkb * w.range / split);
+        w.kb1 = (int)((long long)nkb * (w.range + 1) / split);
+        return true;
+    }
+    const int tile = pair + it * pairs_in_grid;
+    if (tile >= tiles_total) return false;
+    ++it;
+    w.tile = tile;
+    w.kb0 = 0;
+    w.kb1 = nkb;
+    w.range = 0;
+    return true;
+}
+__device__ __forceinline__ int pair_ld_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void pair_st_release(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ void pair_epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <typename TO, bool PAIRS>
 __global__ void __launch_bounds__(192)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
-                    TO* __restrict__ out, int M, int N, int K, long long ldc, int tiles_m, int tiles_total, int bn) {
+                    TO* __restrict__ out, int M, int N, int K, long long ldc, int tiles_m, int tiles_total, int bn,
+                    int split, int* __restrict__ flags, float* __restrict__ partials) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* w_tiles = smem;
@@ -63,6 +103,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     uint32_t* peer_tmem = tmem_slot + 1;             // first CTA: where the second CTA's tensor memory starts
     volatile int* abort_flag = (volatile int*)(tmem_slot + 2);
+    volatile int* peer_ok = (volatile int*)(tmem_slot + 3);
+    uint64_t* xfer = acc_empty + 4;                  // [2]: other pairs' partial sums arriving in the idle ring
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc::cluster_ctarank();            // 0: issues the MMAs
@@ -81,6 +123,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         for (int b = 0; b < 2; ++b) {
             tc::mbar_init(&acc_full[b], 1);
             tc::mbar_init(&acc_empty[b], 2);              // one arrival from each CTA's epilogue
+            tc::mbar_init(&xfer[b], 1);
         }
         *abort_flag = skip ? 1 : 0;
         tc::fence_barrier_init();
@@ -114,35 +157,38 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         if (lane == 0) {
             long long idx = 0, issued = 0;
             bool first = true;
-            for (int tile = pair; tile < tiles_total && !*abort_flag; tile += pairs_in_grid) {
+            int it = 0;
+            PairWork wk;
+            while (!*abort_flag && pair_next(it, pair, pairs_in_grid, tiles_total, nkb, split, wk)) {
+                const int tile = wk.tile;
                 const int n0 = (tile / tiles_m) * 2 * PAIR_TILE_W + n_rank, m0 = (tile % tiles_m) * bn + m_rank;
-                int kb = 0;
+                int kb = wk.kb0;
                 if (first) {
                     // the weight does not depend on earlier kernels: fill the ring with weight blocks,
                     // then wait for the kernels that produce the activations
                     first = false;
-                    const int pre = min(PAIR_STAGES, nkb);
+                    const int pre = min(PAIR_STAGES, wk.kb1 - wk.kb0);
                     for (int i = 0; i < pre; ++i) {
                         if (rank == 0) {
                             tc::mbar_expect_tx(&full[i], 2 * stage_bytes);       // both CTAs' halves
-                            tc::tma_load_2d(w_tiles + i * PAIR_W_BYTES, &tmap_w, i * PAIR_TILE_K, n0, &full[i]);
+                            tc::tma_load_2d(w_tiles + i * PAIR_W_BYTES, &tmap_w, (kb + i) * PAIR_TILE_K, n0, &full[i]);
                         } else {
-                            tc::tma_load_2d_signal_peer(w_tiles + i * PAIR_W_BYTES, &tmap_w, i * PAIR_TILE_K, n0,
+                            tc::tma_load_2d_signal_peer(w_tiles + i * PAIR_W_BYTES, &tmap_w, (kb + i) * PAIR_TILE_K, n0,
                                                         tc::map_to_rank(tc::smem_addr(&full[i]), 0u));
                         }
                     }
                     ap_pdl_wait();
                     for (int i = 0; i < pre; ++i) {
                         if (rank == 0)
-                            tc::tma_load_2d(a_tiles + i * PAIR_A_BYTES, &tmap_a, i * PAIR_TILE_K, m0, &full[i]);
+                            tc::tma_load_2d(a_tiles + i * PAIR_A_BYTES, &tmap_a, (kb + i) * PAIR_TILE_K, m0, &full[i]);
                         else
-                            tc::tma_load_2d_signal_peer(a_tiles + i * PAIR_A_BYTES, &tmap_a, i * PAIR_TILE_K, m0,
+                            tc::tma_load_2d_signal_peer(a_tiles + i * PAIR_A_BYTES, &tmap_a, (kb + i) * PAIR_TILE_K, m0,
                                                         tc::map_to_rank(tc::smem_addr(&full[i]), 0u));
                     }
-                    kb = pre;
+                    kb += pre;
                     idx = issued = pre;
                 }
-                for (; kb < nkb; ++kb, ++idx) {
+                for (; kb < wk.kb1; ++kb, ++idx) {
                     const int s = (int)(idx % PAIR_STAGES);
                     const uint32_t ph = (uint32_t)((idx / PAIR_STAGES) & 1);
                     if (*abort_flag) break;
@@ -192,7 +238,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             bool ok = true;
             long long idx = 0;
             int j = 0;
-            for (int tile = pair; ok && tile < tiles_total; tile += pairs_in_grid, ++j) {
+            int it = 0;
+            PairWork wk;
+            for (; ok && pair_next(it, pair, pairs_in_grid, tiles_total, nkb, split, wk); ++j) {
                 const int b = j & 1;
                 // both CTAs' epilogue warps have read this buffer's tile of two rounds ago
                 if (*abort_flag || !tc::mbar_wait(&acc_empty[b], (uint32_t)(((j >> 1) & 1) ^ 1))) {
@@ -205,7 +253,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 }
                 tc::fence_after_sync();
                 const uint32_t acc = tmem_base + (uint32_t)(b * PAIR_MAX_BN);
-                for (int kb = 0; kb < nkb; ++kb, ++idx) {
+                for (int kb = wk.kb0; kb < wk.kb1; ++kb, ++idx) {
                     const int s = (int)(idx % PAIR_STAGES);
                     const uint32_t ph = (uint32_t)((idx / PAIR_STAGES) & 1);
                     if (*abort_flag) { ok = false; break; }
@@ -220,7 +268,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                     const uint64_t ad = tc::smem_desc_k_major_sw128(a_tiles + s * PAIR_A_BYTES);
 #pragma unroll
                     for (int k = 0; k < PAIR_TILE_K / 16; ++k)
-                        tc::mma_bf16_pair(acc, wd + 2 * k, ad + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        tc::mma_bf16_pair(acc, wd + 2 * k, ad + 2 * k, idesc, (kb > wk.kb0 || k > 0) ? 1u : 0u);
                     tc::mma_commit_pair(&empty[s]);              // the stage is free in both CTAs
                 }
                 if (ok) tc::mma_commit_pair(&acc_full[b]);       // both epilogues may read their halves
@@ -235,7 +283,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         bool ok = true;
         int j = 0;
         const uint32_t remote_empty0 = tc::map_to_rank(tc::smem_addr(&acc_empty[0]), 0u);
-        for (int tile = pair; ok && tile < tiles_total; tile += pairs_in_grid, ++j) {
+        int it = 0;
+        PairWork wk;
+        for (; ok && pair_next(it, pair, pairs_in_grid, tiles_total, nkb, split, wk); ++j) {
+            const int tile = wk.tile;
             const int n0 = (tile / tiles_m) * 2 * PAIR_TILE_W + n_rank, m0 = (tile % tiles_m) * bn;
             const int b = j & 1;
             // tcgen05.ld is warp-wide: the whole warp goes on, or none of it
@@ -251,11 +302,95 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * PAIR_MAX_BN);
             const int n = n0 + row;
             const int cols = min(bn, M - m0);           // token rows of this tile that exist
+            if (wk.range > 0) {
+                // a later range of a shared tile: this CTA's 128 rows of the partial sums go to global
+                // memory, [token][weight row], for the CTA of the same rank in the pair of range 0
+                float* mine = partials + (size_t)blockIdx.x * PAIR_PARTIAL_FLOATS;
+#pragma unroll 1
+                for (int c = 0; c < cols; c += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld_x32(acc + (uint32_t)c, v);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) mine[(size_t)(c + jj) * PAIR_TILE_W + row] = __uint_as_float(v[jj]);
+                }
+                __threadfence();
+                tc::fence_before_sync();
+                pair_epilogue_sync();
+                if (et == 0) {
+                    pair_st_release(&flags[blockIdx.x], 1);
+                    if (rank == 0) tc::mbar_arrive(&acc_empty[b]);
+                    else tc::mbar_arrive_remote(remote_empty0 + (uint32_t)b * 8u);
+                }
+                continue;
+            }
+            // Range 0 of a shared tile: the CTAs of the same rank in the pairs pair + tiles, pair + 2 tiles,
+            // ... hold the rest of K.  Their sums come through the operand ring, which is idle (this is
+            // the pair's only piece of work and its products are done): blocks of 32 tokens (16 KB a peer)
+            // arrive by bulk copy, two blocks in turn, and are added in the order of the ranges.
+            const int peers = split - 1;
+            constexpr uint32_t XFER_BYTES = 32 * PAIR_TILE_W * 4;
+            static_assert(2 * (PAIR_MAX_SPLIT - 1) * XFER_BYTES <= PAIR_STAGES * PAIR_STAGE_BYTES, "the ring holds the blocks");
+            float* xbuf = reinterpret_cast<float*>(smem);
+            auto peer_cta = [&](int pi) { return (int)blockIdx.x + 2 * (1 + pi) * tiles_total; };
+            auto fetch = [&](int block, int buf) {
+                tc::mbar_expect_tx(&xfer[buf], (uint32_t)peers * XFER_BYTES);
+                for (int pi = 0; pi < peers; ++pi)
+                    tc::bulk_load(xbuf + (size_t)(buf * (PAIR_MAX_SPLIT - 1) + pi) * 32 * PAIR_TILE_W,
+                                  partials + (size_t)peer_cta(pi) * PAIR_PARTIAL_FLOATS + (size_t)block * 32 * PAIR_TILE_W,
+                                  XFER_BYTES, &xfer[buf]);
+            };
+            if (peers > 0) {
+                if (et == 0) {
+                    int fine = 1;
+                    const long long t0 = clock64();
+                    for (int pi = 0; pi < peers && fine; ++pi) {
+                        while (pair_ld_acquire(&flags[peer_cta(pi)]) == 0) {
+                            if (clock64() - t0 > 2000000000LL || *abort_flag) { fine = 0; break; }
+                        }
+                        if (fine) flags[peer_cta(pi)] = 0;            // ready for the next product
+                    }
+                    *peer_ok = fine;
+                    if (fine) {
+                        tc::fence_proxy_async();
+                        fetch(0, 0);
+                        if (cols > 32) fetch(1, 1);
+                    }
+                }
+                pair_epilogue_sync();
+                if (!*peer_ok) {
+                    if (et == 0 && !*abort_flag) {
+                        *abort_flag = 1;
+                        atomicCAS(&g_pair_status, 0, PAIR_ERR_PEER);
+                    }
+                    ok = false;
+                    break;
+                }
+            }
 #pragma unroll 1
             for (int c = 0; c < cols; c += 32) {
                 uint32_t v[32];
                 tc::tmem_ld_x32(acc + (uint32_t)c, v);
                 tc::tmem_ld_wait();
+                if (peers > 0) {
+                    const int block = c >> 5, buf = block & 1;
+                    if (!__all_sync(0xffffffffu, tc::mbar_wait(&xfer[buf], (uint32_t)((block >> 1) & 1)))) {
+                        if (!*abort_flag) {
+                            *abort_flag = 1;
+                            atomicCAS(&g_pair_status, 0, PAIR_ERR_PEER);
+                        }
+                        ok = false;
+                        break;
+                    }
+                    for (int pi = 0; pi < peers; ++pi) {
+                        const float* theirs = xbuf + (size_t)(buf * (PAIR_MAX_SPLIT - 1) + pi) * 32 * PAIR_TILE_W + row;
+#pragma unroll
+                        for (int jj = 0; jj < 32; ++jj)
+                            v[jj] = __float_as_uint(__uint_as_float(v[jj]) + theirs[jj * PAIR_TILE_W]);
+                    }
+                    pair_epilogue_sync();                             // everybody has read this block
+                    if (et == 0 && c + 64 < cols) fetch(block + 2, buf);
+                }
                 if (PAIRS) {
                     // even lane: gate of column n/2, odd lane: up.  The even lane finishes rows
                     // c..c+15, the odd lane rows c+16..c+31, each with the other's half.
@@ -333,7 +468,7 @@ static bool pair_make_map(CUtensorMap* map, const void* base, long long rows, lo
 
 template <typename TO, bool PAIRS>
 static int launch_pair(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K, long long ldc,
-                       int bn, int tiles_m, cudaStream_t stream) {
+                       int bn, int tiles_m, void* scratch, long long scratch_bytes, cudaStream_t stream) {
     auto kern = gemm_tc_pair_kernel<TO, PAIRS>;
     static bool configured = false;
     static int sms = 0;
@@ -374,19 +509,45 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& ma, void* out, 
                    cudaGetErrorString(e));
         resident_pairs = n < sms / 2 ? n : sms / 2;
     }
-    const int pairs = (int)((long long)resident_pairs < tiles ? resident_pairs : tiles);
+    int pairs = (int)((long long)resident_pairs < tiles ? resident_pairs : tiles);
+    // Fewer tiles than half the pairs, a scratch buffer at hand and enough K: every tile is shared
+    // by up to four pairs, each taking an equal range of K (at least 24 blocks of it).
+    const int nkb = (K + PAIR_TILE_K - 1) / PAIR_TILE_K;
+    int split = 1;
+    int* flags = nullptr;
+    float* partials = nullptr;
+    if (scratch && tiles * 2 <= resident_pairs) {
+        split = (int)min((long long)PAIR_MAX_SPLIT, (long long)resident_pairs / tiles);
+        split = min(split, nkb / 24);
+        const long long need = (long long)PAIR_MAX_CTAS * 4 + 2LL * tiles * split * PAIR_PARTIAL_FLOATS * 4;
+        // (with a shorter K the hand-over costs more than the idle pairs would gain)
+        if (split < 2 || nkb < 96 || scratch_bytes < need || 2 * tiles * split > PAIR_MAX_CTAS) split = 1;
+    }
+    if (split > 1) {
+        AP_REQUIRE(((uintptr_t)scratch & 15) == 0, "gemm_tc_pair: the scratch buffer must be 16-byte aligned");
+        flags = (int*)scratch;
+        partials = (float*)((char*)scratch + PAIR_MAX_CTAS * 4);
+        pairs = (int)tiles * split;
+    }
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
     cfg.numAttrs = ap_pdl_enabled() ? 2 : 1;
     AP_CHECK_PDL_LAUNCH("gemm_tc_pair", cudaLaunchKernelEx(&cfg, kern, mw, ma, (TO*)out, M, N, K, ldc, tiles_m,
-                                                           (int)tiles, bn));
+                                                           (int)tiles, bn, split, flags, partials));
     return AP_OK;
 }
 
 // The product on pairs of SMs (see gemm_tc_pair_kernel), for products with many rows.
 //   pairs == 0: out[M, N] = a * w^T for w [N, K].
 //   pairs != 0: w [N, K] has gate and up rows alternating; out[M, N/2] = silu(gate) * up.
+//   scratch: null, or a zeroed buffer of ap_gemm_tc_pair_scratch_bytes() bytes that belongs to one
+//   stream (few tiles of a long K are then shared among several pairs; the kernel leaves the flags
+//   at its head zero again).  The persistent kernel's scratch buffer serves both.
+AP_EXPORT long long ap_gemm_tc_pair_scratch_bytes(void) {
+    return (long long)PAIR_MAX_CTAS * 4 + (long long)PAIR_MAX_CTAS * PAIR_PARTIAL_FLOATS * 4;
+}
 AP_EXPORT int ap_gemm_tc_pair(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K,
-                              long long lda, long long ldw, long long ldc, int pairs, cudaStream_t stream) {
+                              long long lda, long long ldw, long long ldc, int pairs, void* scratch,
+                              long long scratch_bytes, cudaStream_t stream) {
     AP_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tc_pair: bad sizes M=%d N=%d K=%d", M, N, K);
     if (M == 0) return AP_OK;
     AP_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
@@ -403,30 +564,30 @@ AP_EXPORT int ap_gemm_tc_pair(const void* a, const void* w, void* out, int out_d
     AP_REQUIRE(pair_make_map(&mw, w, N, K, ldw, PAIR_TILE_W), "gemm_tc_pair: cannot encode the weight's tensor map");
     AP_REQUIRE(pair_make_map(&ma, a, M, K, lda, bn / 2), "gemm_tc_pair: cannot encode the activations' tensor map");
     if (pairs) {
-        return out_dtype == AP_F32 ? launch_pair<float, true>(mw, ma, out, M, N, K, ldc, bn, tiles_m, stream)
-                                   : launch_pair<bf16, true>(mw, ma, out, M, N, K, ldc, bn, tiles_m, stream);
+        return out_dtype == AP_F32
+                   ? launch_pair<float, true>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, stream)
+                   : launch_pair<bf16, true>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, stream);
     }
-    return out_dtype == AP_F32 ? launch_pair<float, false>(mw, ma, out, M, N, K, ldc, bn, tiles_m, stream)
-                               : launch_pair<bf16, false>(mw, ma, out, M, N, K, ldc, bn, tiles_m, stream);
+    return out_dtype == AP_F32
+               ? launch_pair<float, false>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, stream)
+               : launch_pair<bf16, false>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, stream);
 }
 
 // Whether this kernel is the one to use for a product of many rows.  Measured against the
 // persistent kernel (one SM to a tile of 128 x 256, which takes in 48 KB per block of K where a
-// CTA of a pair takes 32 KB) it is 3 to 12 % faster from 129 rows on, with three exceptions, two of which the
-// caller's other rules cover: few tiles of a long K, which the persistent kernel shares out
-// along K (512 x 4096 x 14336: 76 against 80 us), and products for which the kernel with two
-// weight tiles to a CTA is chosen (2048 x 4096 x 14336: 173 against 184 us).
+// CTA of a pair takes 32 KB) it is 3 to 12 % faster from 129 rows on, with two exceptions: products for which the kernel with two
+// weight tiles to a CTA is chosen (2048 x 4096 x 14336: 173 against 184 us), and few tiles of a short K.
 extern "C" int ap_gemm_tc_prefers_persistent(int M, int N, int K);
 AP_EXPORT int ap_gemm_tc_prefers_pair(int M, int N, int K) {
     if (M <= 128 || N <= 0 || K <= 0 || K % 8) return 0;               // (160 x 28672 x 4096: 59 against 62 us)
     if (!ap_gemm_tc_prefers_persistent(M, N, K)) return 0;            // the two-tile kernel's cases
-    const long long tiles = (long long)((N + PAIR_TILE_W - 1) / PAIR_TILE_W) * ((M + PAIR_MAX_BN - 1) / PAIR_MAX_BN);
     const int nkb = (K + PAIR_TILE_K - 1) / PAIR_TILE_K;
-    if (tiles * 2 <= 148 && nkb >= 96) return 0;                      // shared out along K instead
-    // fewer tiles of 256 x 256 than keep about half of the 74 pairs busy: one SM to a tile of 128 x 256
-    // puts as many SMs to work and is the faster (256 x 6144 x 4096: 28.4 against 30.6 us)
+    // fewer tiles of 256 x 256 than keep about half of the 74 pairs busy: with a long K they are shared
+    // among several pairs (512 x 4096 x 14336: 61 us against the persistent kernel's 76, 544 x 2048 x
+    // 8192: 35 against 46); with a short K one SM to a tile of 128 x 256 puts as many SMs to work
+    // and is the faster (256 x 6144 x 4096: 28.4 against 30.6 us, 512 x 4096 x 4096: 30.7 against 34.7)
     const long long pair_tiles = (long long)((N + 2 * PAIR_TILE_W - 1) / (2 * PAIR_TILE_W)) * ((M + PAIR_MAX_BN - 1) / PAIR_MAX_BN);
-    if (pair_tiles < 40) return 0;
+    if (pair_tiles < 40) return (M > 256 && pair_tiles * 2 <= 74 && nkb >= 96) ? 1 : 0;
     return 1;
 }
 

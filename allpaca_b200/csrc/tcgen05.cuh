@@ -89,6 +89,12 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         ::"r"(smem_addr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
         : "memory");
 }
+// `bytes` (a multiple of 16) from global to shared memory, both 16-byte aligned; completes on `bar`
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
 // The same load issued by a CTA of a pair (cta_group::2) whose completion is counted on a
 // barrier of the pair's other CTA: `bar_cluster_addr` is that barrier's address in the
 // cluster's shared window (map_to_rank).  No multicast: the data goes to this CTA only.

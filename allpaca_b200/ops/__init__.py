@@ -369,9 +369,12 @@ def gemm_tc_dual(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
          M, N, K, K, K, N, stream_handle())
 
 
-def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pairs: bool = False) -> None:
+def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pairs: bool = False,
+                 share_tiles: bool = True) -> None:
     """The tensor-core product on pairs of SMs (``tcgen05.mma.cta_group::2``), for many rows: two
     CTAs share a tile of 256 weight rows x up to 256 rows of ``a``, each loading half of either.
+    With ``share_tiles`` a product of fewer tiles than half the pairs splits every tile's K among
+    up to four pairs.
 
     ``pairs`` False: ``out[M,N] = a[M,K] @ w[N,K]^T``.  True: the rows of ``w [N,K]`` alternate
     gate, up, gate, up ... and ``out[M,N/2] = silu(gate) * up``.
@@ -384,8 +387,10 @@ def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pairs: boo
     n_out = N // 2 if pairs else N
     if w.shape[1] != K or tuple(out.shape) != (M, n_out) or (pairs and N % 2):
         raise KernelError(f"gemm_tc_pair: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    scratch = _scratch_for_persistent(a.device) if share_tiles else None
     call(core(), "ap_gemm_tc_pair", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
-         M, N, K, K, K, n_out, 1 if pairs else 0, stream_handle())
+         M, N, K, K, K, n_out, 1 if pairs else 0, scratch.data_ptr() if scratch is not None else 0,
+         scratch.numel() if scratch is not None else 0, stream_handle())
 
 
 _persistent_scratch = {}

@@ -47,7 +47,7 @@ _OPTIONAL_CORE_SIGNATURES = {
     "ap_gemm_tc_rope": [_P, _P, _I, _I, _L, _L, _I, _P, _I, _F, _F, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I,
                         _L, _P],
     "ap_gemm_tc_dual": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
-    "ap_gemm_tc_pair": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P],
+    "ap_gemm_tc_pair": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P, _L, _P],
     "ap_gemm_tc_pair_status": [],
     "ap_gemm_tc_pair_reset_status": [],
     "ap_gemm_tc_persistent": [_P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _P, _L, _P],
