@@ -577,11 +577,18 @@ AP_EXPORT int ap_gemm_tc_pair(const void* a, const void* w, void* out, int out_d
 // persistent kernel (one SM to a tile of 128 x 256, which takes in 48 KB per block of K where a
 // CTA of a pair takes 32 KB) it is 3 to 12 % faster from 129 rows on, with two exceptions: products for which the kernel with two
 // weight tiles to a CTA is chosen (2048 x 4096 x 14336: 173 against 184 us), and few tiles of a short K.
-extern "C" int ap_gemm_tc_prefers_persistent(int M, int N, int K);
 AP_EXPORT int ap_gemm_tc_prefers_pair(int M, int N, int K) {
     if (M <= 128 || N <= 0 || K <= 0 || K % 8) return 0;               // (160 x 28672 x 4096: 59 against 62 us)
-    if (!ap_gemm_tc_prefers_persistent(M, N, K)) return 0;            // the two-tile kernel's cases
     const int nkb = (K + PAIR_TILE_K - 1) / PAIR_TILE_K;
+    {
+        // the two-tile kernel's case: a long K and few enough of its waves (see ap_gemm_tc_prefers_persistent;
+        // its other case, a badly filled last round of single tiles, is this kernel's: 2048 x 4096 x 4096
+        // 56 us against 59)
+        const long long rows = (M + PAIR_MAX_BN - 1) / PAIR_MAX_BN;
+        const long long single = (long long)((N + PAIR_TILE_W - 1) / PAIR_TILE_W) * rows;
+        const long long dual = (long long)((N + 2 * PAIR_TILE_W - 1) / (2 * PAIR_TILE_W)) * rows;
+        if (K >= 8192 && ((dual + 147) / 148) * 180 < ((single + 147) / 148) * 100) return 0;
+    }
     // fewer tiles of 256 x 256 than keep about half of the 74 pairs busy: with a long K they are shared
     // among several pairs (512 x 4096 x 14336: 61 us against the persistent kernel's 76, 544 x 2048 x
     // 8192: 35 against 46); with a short K one SM to a tile of 128 x 256 puts as many SMs to work
