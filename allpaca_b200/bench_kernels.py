@@ -67,7 +67,8 @@ def bench_gemm(args) -> dict:
         # a pair of CTAs to a tile of 256 weight rows (cta_group::2); with --swiglu the rows of w alternate
         kernel = "gemm_tc_pair"
         out = torch.empty(M, N // 2 if args.swiglu else N, device="cuda", dtype=odt)
-        fn = lambda i: ops.gemm_tc_pair(a, ws[i % copies], out, pairs=args.swiglu)   # noqa: E731
+        fn = lambda i: ops.gemm_tc_pair(a, ws[i % copies], out, pairs=args.swiglu,   # noqa: E731
+                                        share_tiles=not args.whole_tiles)
         S = 1
     elif args.dual:
         # two weight tiles per CTA
@@ -358,7 +359,7 @@ def main(argv=None) -> int:
             s.add_argument("--single", action="store_true", help="more than 64 rows: one tile per CTA, not persistent")
             s.add_argument("--persistent", action="store_true", help="the persistent kernel, whatever the plan says")
             s.add_argument("--whole-tiles", action="store_true",
-                           help="persistent kernel: never share a tile's K among several CTAs")
+                           help="persistent and pair kernel: never share a tile's K among several CTAs")
             s.add_argument("--swiglu", action="store_true", help="w holds gate and up rows: fused gated activation")
             s.add_argument("--residual", action="store_true",
                            help="few rows: add into a 32-bit residual in the epilogue (with its bfloat16 copy and sums of squares)")

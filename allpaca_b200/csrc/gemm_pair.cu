@@ -51,29 +51,31 @@
 
 static __device__ int g_pair_status;
 
-// A pair's next piece of work: blocks [kb0, kb1) of K of one tile.  split == 1: whole tiles
-// pair, pair + pairs, ...  split > 1 (the grid holds tiles * split pairs): pair g takes range
-// g / tiles of tile g % tiles, and the pair of range 0 finishes the tile with what the others
-// hand over in global memory.
+// A pair's next piece of work: blocks [kb0, kb1) of K of one tile.  The first tiles_total - shared
+// tiles go round robin to the pairs, whole (tile pair, pair + pairs, ...).  The last `shared`
+// tiles are each cut along K into `split` ranges: pair g < shared * split takes range g / shared
+// of tile (tiles_total - shared) + g % shared as its last piece of work, and the pair of range 0
+// finishes the tile with what the others hand over in global memory.
 struct PairWork { int tile, kb0, kb1, range; };
 __device__ __forceinline__ bool pair_next(int& it, int pair, int pairs_in_grid, int tiles_total, int nkb, int split,
-                                          PairWork& w) {
-    if (split > 1) {
-        if (it > 0 || pair >= tiles_total * split) return false;
-        it = 1;
-        w.range = pair / tiles_total;
-        w.tile = pair - w.range * tiles_total;
-        w.kb0 = (int)((long long)nkb * w.range / split);
-        w.kb1 = (int)((long long)nkb * (w.range + 1) / split);
+                                          int shared, PairWork& w) {
+    if (it < 0) return false;
+    const int whole = tiles_total - shared;
+    const int tile = pair + it * pairs_in_grid;
+    if (tile < whole) {
+        ++it;
+        w.tile = tile;
+        w.kb0 = 0;
+        w.kb1 = nkb;
+        w.range = 0;
         return true;
     }
-    const int tile = pair + it * pairs_in_grid;
-    if (tile >= tiles_total) return false;
-    ++it;
-    w.tile = tile;
-    w.kb0 = 0;
-    w.kb1 = nkb;
-    w.range = 0;
+    it = -1;
+    if (shared <= 0 || pair >= shared * split) return false;
+    w.range = pair / shared;
+    w.tile = whole + pair - w.range * shared;
+    w.kb0 = (int)((long long)nkb * w.range / split);
+    w.kb1 = (int)((long long)nkb * (w.range + 1) / split);
     return true;
 }
 __device__ __forceinline__ int pair_ld_acquire(const int* p) {
@@ -91,7 +93,7 @@ template <typename TO, bool PAIRS>
 __global__ void __launch_bounds__(192)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                     TO* __restrict__ out, int M, int N, int K, long long ldc, int tiles_m, int tiles_total, int bn,
-                    int split, int* __restrict__ flags, float* __restrict__ partials) {
+                    int split, int shared, int* __restrict__ flags, float* __restrict__ partials) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* w_tiles = smem;
@@ -159,7 +161,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             bool first = true;
             int it = 0;
             PairWork wk;
-            while (!*abort_flag && pair_next(it, pair, pairs_in_grid, tiles_total, nkb, split, wk)) {
+            while (!*abort_flag && pair_next(it, pair, pairs_in_grid, tiles_total, nkb, split, shared, wk)) {
                 const int tile = wk.tile;
                 const int n0 = (tile / tiles_m) * 2 * PAIR_TILE_W + n_rank, m0 = (tile % tiles_m) * bn + m_rank;
                 int kb = wk.kb0;
@@ -240,7 +242,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
             int j = 0;
             int it = 0;
             PairWork wk;
-            for (; ok && pair_next(it, pair, pairs_in_grid, tiles_total, nkb, split, wk); ++j) {
+            for (; ok && pair_next(it, pair, pairs_in_grid, tiles_total, nkb, split, shared, wk); ++j) {
                 const int b = j & 1;
                 // both CTAs' epilogue warps have read this buffer's tile of two rounds ago
                 if (*abort_flag || !tc::mbar_wait(&acc_empty[b], (uint32_t)(((j >> 1) & 1) ^ 1))) {
@@ -285,7 +287,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
         const uint32_t remote_empty0 = tc::map_to_rank(tc::smem_addr(&acc_empty[0]), 0u);
         int it = 0;
         PairWork wk;
-        for (; ok && pair_next(it, pair, pairs_in_grid, tiles_total, nkb, split, wk); ++j) {
+        for (; ok && pair_next(it, pair, pairs_in_grid, tiles_total, nkb, split, shared, wk); ++j) {
             const int tile = wk.tile;
             const int n0 = (tile / tiles_m) * 2 * PAIR_TILE_W + n_rank, m0 = (tile % tiles_m) * bn;
             const int b = j & 1;
@@ -324,15 +326,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                 }
                 continue;
             }
-            // Range 0 of a shared tile: the CTAs of the same rank in the pairs pair + tiles, pair + 2 tiles,
+            // Range 0 of a shared tile: the CTAs of the same rank in the pairs pair + shared, pair + 2 shared,
             // ... hold the rest of K.  Their sums come through the operand ring, which is idle (this is
-            // the pair's only piece of work and its products are done): blocks of 32 tokens (16 KB a peer)
+            // the pair's last piece of work and its products are done): blocks of 32 tokens (16 KB a peer)
             // arrive by bulk copy, two blocks in turn, and are added in the order of the ranges.
-            const int peers = split - 1;
+            const int peers = (wk.kb1 - wk.kb0 < nkb) ? split - 1 : 0;
             constexpr uint32_t XFER_BYTES = 32 * PAIR_TILE_W * 4;
             static_assert(2 * (PAIR_MAX_SPLIT - 1) * XFER_BYTES <= PAIR_STAGES * PAIR_STAGE_BYTES, "the ring holds the blocks");
             float* xbuf = reinterpret_cast<float*>(smem);
-            auto peer_cta = [&](int pi) { return (int)blockIdx.x + 2 * (1 + pi) * tiles_total; };
+            auto peer_cta = [&](int pi) { return (int)blockIdx.x + 2 * (1 + pi) * shared; };
             auto fetch = [&](int block, int buf) {
                 tc::mbar_expect_tx(&xfer[buf], (uint32_t)peers * XFER_BYTES);
                 for (int pi = 0; pi < peers; ++pi)
@@ -510,29 +512,32 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& ma, void* out, 
         resident_pairs = n < sms / 2 ? n : sms / 2;
     }
     int pairs = (int)((long long)resident_pairs < tiles ? resident_pairs : tiles);
-    // Fewer tiles than half the pairs, a scratch buffer at hand and enough K: every tile is shared
-    // by up to four pairs, each taking an equal range of K (at least 24 blocks of it).
+    // Fewer tiles than half the pairs, a scratch buffer at hand and a K of 6144 and more: every tile is
+    // shared by up to four pairs that take equal ranges of K (at least 24 blocks of it).  (Sharing out
+    // the tiles left over after whole rounds in the same way was measured too: the 8B gate+up
+    // product at 1024 to 4096 rows gains nothing from it, so whole rounds stay as they are.)
     const int nkb = (K + PAIR_TILE_K - 1) / PAIR_TILE_K;
-    int split = 1;
+    const int rounds = (int)(tiles / resident_pairs), left = (int)(tiles - (long long)rounds * resident_pairs);
+    int split = 1, shared = 0;
     int* flags = nullptr;
     float* partials = nullptr;
-    if (scratch && tiles * 2 <= resident_pairs) {
-        split = (int)min((long long)PAIR_MAX_SPLIT, (long long)resident_pairs / tiles);
+    if (scratch && rounds == 0 && left * 2 <= resident_pairs && nkb >= 96) {
+        split = min(PAIR_MAX_SPLIT, resident_pairs / left);
         split = min(split, nkb / 24);
-        const long long need = (long long)PAIR_MAX_CTAS * 4 + 2LL * tiles * split * PAIR_PARTIAL_FLOATS * 4;
-        // (with a shorter K the hand-over costs more than the idle pairs would gain)
-        if (split < 2 || nkb < 96 || scratch_bytes < need || 2 * tiles * split > PAIR_MAX_CTAS) split = 1;
+        const long long need = (long long)PAIR_MAX_CTAS * 4 + 2LL * resident_pairs * PAIR_PARTIAL_FLOATS * 4;
+        if (split < 2 || scratch_bytes < need || 2 * resident_pairs > PAIR_MAX_CTAS) split = 1;
     }
     if (split > 1) {
         AP_REQUIRE(((uintptr_t)scratch & 15) == 0, "gemm_tc_pair: the scratch buffer must be 16-byte aligned");
         flags = (int*)scratch;
         partials = (float*)((char*)scratch + PAIR_MAX_CTAS * 4);
-        pairs = (int)tiles * split;
+        shared = left;
+        if (rounds == 0) pairs = left * split;
     }
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
     cfg.numAttrs = ap_pdl_enabled() ? 2 : 1;
     AP_CHECK_PDL_LAUNCH("gemm_tc_pair", cudaLaunchKernelEx(&cfg, kern, mw, ma, (TO*)out, M, N, K, ldc, tiles_m,
-                                                           (int)tiles, bn, split, flags, partials));
+                                                           (int)tiles, bn, split, shared, flags, partials));
     return AP_OK;
 }
 

@@ -15,7 +15,9 @@ def rel_err(got, ref):
 SHAPES = [(256, 256, 64), (65, 128, 512), (300, 520, 1032), (129, 384, 1024), (1000, 384, 2048), (2048, 1024, 512),
           (257, 4096, 4096), (700, 1000, 320), (2048, 6144, 4096),
           # few tiles of a long K: every tile is shared by two to four pairs, which hand partial sums over
-          (512, 4096, 14336), (300, 1024, 8192), (200, 520, 6400)]
+          (512, 4096, 14336), (300, 1024, 8192), (200, 520, 6400),
+          # more tiles than pairs, the last round of them partly filled (6 of 80, 21 of 95)
+          (2048, 2560, 2048), (1100, 4864, 3072)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -37,7 +39,7 @@ def test_pair_plain(M, N, K, odtype):
 
 
 @pytest.mark.parametrize("M,I,K", [(65, 176, 64), (256, 128, 96), (300, 304, 1000), (513, 1000, 256), (2048, 896, 512),
-                                   (300, 512, 4096), (140, 200, 9000 // 8 * 8)])
+                                   (300, 512, 4096), (140, 200, 9000 // 8 * 8), (2048, 1280, 2048)])
 def test_pair_gated_activation(M, I, K):
     from allpaca_b200 import ops
     g = torch.Generator().manual_seed(I)
