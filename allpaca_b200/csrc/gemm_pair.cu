@@ -16,7 +16,7 @@
 // Roles in each CTA: warp 0 = TMA producer for this CTA's halves; warp 1 = in the first CTA
 // the MMA issuer (idle in the second); warps 2..5 = epilogue.  The loads of both CTAs are
 // counted on the first CTA's barrier of the stage: the second CTA issues its loads with
-// .cta_group::2 and that barrier's address (no multicast: the data goes to the issuing CTA
+// .cta_group::2 and that barrier's address (the data itself goes to the issuing CTA
 // only), and the first CTA expects the bytes of both.  (A relay thread in the second CTA,
 // forwarding "my stage has landed" by a remote arrival, cost 5 to 12 % of the product's time.)
 // A stage is freed, and an accumulator handed to the epilogue, in both CTAs at once by

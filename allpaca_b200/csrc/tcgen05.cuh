@@ -97,7 +97,7 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
 }
 // The same load issued by a CTA of a pair (cta_group::2) whose completion is counted on a
 // barrier of the pair's other CTA: `bar_cluster_addr` is that barrier's address in the
-// cluster's shared window (map_to_rank).  No multicast: the data goes to this CTA only.
+// cluster's shared window (map_to_rank).  The data goes to this CTA only.
 __device__ __forceinline__ void tma_load_2d_signal_peer(void* smem_dst, const CUtensorMap* map, int x, int y,
                                                         uint32_t bar_cluster_addr) {
     asm volatile(
